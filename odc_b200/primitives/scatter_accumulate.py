@@ -1,0 +1,117 @@
+"""``scatter_accumulate``: the producer adds its gradient rows straight into the owners' shards.
+
+Contract of the reference's ``ReductionService`` (odc/primitives/scatter_accumulate.py:494-749):
+``input`` is 1-D and rank-major ``[|pg|, shard]``; row p is ADDED into rank p's persistent
+accumulator for ``key``; accumulators have ``accumulation_dtype`` (default: the input dtype);
+the sum on an owner is complete only after ``sync`` on that owner; ``clear_accumulations``
+zeroes them (the caller fences with a barrier); ``get_accumulation`` returns the live tensor.
+
+What differs: there is no mailbox, no request/ack word and no watcher process
+(scatter_accumulate.py:267-491).  The producer's kernel issues vector ``red.global.add``
+through the peer mapping into the owner's accumulator — each gradient byte crosses NVLink once
+and is never staged — and finishes by bumping an arrival counter on every owner with a
+system-scope release.  ``sync`` exchanges the per-owner dispatch counts on the host and then
+runs one bounded device wait until the local counter has caught up.  The counter is cumulative
+and never reset, so no acknowledgement travels back to the producer and ``input`` may be reused
+as soon as the call's kernel has run (stream order).
+"""
+from __future__ import annotations
+
+import logging
+from typing import Dict, Hashable, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..runtime import control
+from ..runtime.registry import SymmBufferRegistry
+from ..runtime.transport import Transport, make_transport
+from ..utils.nvtx import nvtx_range
+
+logger = logging.getLogger("odc_b200")
+
+COUNTER_KEY = "odc_arrival_counter"
+
+
+def accumulation_key(key: Hashable) -> str:
+    return f"rs_accumulation_{key}"
+
+
+class ReductionService:
+    def __init__(self, accumulation_dtype: Optional[torch.dtype] = None, transport: Optional[Transport] = None):
+        self.registry = SymmBufferRegistry.get_instance()
+        self.transport = transport or make_transport(self.registry)
+        self.accumulation_dtype = accumulation_dtype
+        self.accumulations: Dict[Hashable, torch.Tensor] = {}
+        self.dispatched: Dict[int, int] = {}   # owner global rank -> contributions sent (cumulative)
+        self.expected_total = 0                 # contributions this rank has been told to expect
+        self.counter = self.registry.get_or_create_symm_buffer(COUNTER_KEY, (8,), torch.int64)
+        self.counter.zero_()
+        self._sync_device()
+        control.host_barrier()
+        self.calls = 0
+
+    def _sync_device(self):
+        if self.counter.is_cuda:
+            torch.cuda.current_stream().synchronize()
+
+    # -- registration (collective) ---------------------------------------------------------
+    def register(self, key: Hashable, shard_numel: int, input_dtype: torch.dtype,
+                 pg: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+        """Collective over all ranks: allocate and zero the accumulator of ``key``."""
+        if key in self.accumulations:
+            return self.accumulations[key]
+        acc_dtype = self.accumulation_dtype or input_dtype
+        acc = self.registry.get_or_create_symm_buffer(accumulation_key(key), (shard_numel,), acc_dtype)
+        acc.zero_()
+        self._sync_device()
+        control.host_barrier()
+        self.accumulations[key] = acc
+        return acc
+
+    # -- hot path ----------------------------------------------------------------------------
+    def scatter_accumulate(self, key: Hashable, input: torch.Tensor, pg: Optional[dist.ProcessGroup] = None,
+                           scale: float = 1.0) -> None:
+        ranks = control.group_ranks(pg)
+        n = len(ranks)
+        if input.dim() != 1:
+            input = input.reshape(-1)
+        if input.numel() % n != 0:
+            raise ValueError(f"input of {input.numel()} elements is not a multiple of the group size {n}")
+        shard = input.numel() // n
+        acc = self.accumulations.get(key)
+        if acc is None:
+            acc = self.register(key, shard, input.dtype, pg)  # first call per key is collective
+        if acc.numel() != shard:
+            raise ValueError(f"accumulator of {key!r} holds {acc.numel()} elements, input rows have {shard}")
+        me = control.rank()
+        my_index = ranks.index(me)
+        with nvtx_range("odc::scatter_accumulate"):
+            self.transport.scatter_add(input.view(n, shard), acc, self.counter, ranks, my_index, scale)
+        for r in ranks:
+            self.dispatched[r] = self.dispatched.get(r, 0) + 1
+        self.calls += 1
+
+    def get_accumulation(self, key: Hashable) -> torch.Tensor:
+        return self.accumulations[key]
+
+    def has_accumulation(self, key: Hashable) -> bool:
+        return key in self.accumulations
+
+    def clear_accumulations(self) -> None:
+        for acc in self.accumulations.values():
+            acc.zero_()
+
+    # -- once per minibatch ------------------------------------------------------------------
+    def sync(self, pg: Optional[dist.ProcessGroup] = None) -> None:
+        """Collective over all ranks: wait until every contribution addressed to this rank has landed."""
+        with nvtx_range("odc::scatter_accumulate_sync"):
+            me = control.rank()
+            everyone = control.all_gather_object(dict(self.dispatched))
+            self.expected_total = sum(d.get(me, 0) for d in everyone)
+            self.transport.wait_arrivals(self.counter, self.expected_total)
+
+    def stop(self) -> None:
+        self._sync_device()
+        control.host_barrier()
+        self.accumulations.clear()

@@ -1,0 +1,126 @@
+"""Host-side control plane: process-group helpers and the comm stream.
+
+The data plane never needs the peer's *process* to take part; the control plane is the
+handful of host collectives that remain (heap bootstrap, collective allocation, the
+once-per-minibatch count exchange).  They run on a gloo group so that they never enqueue
+work on, or synchronise with, a CUDA stream.
+
+Reference behaviour covered: odc/primitives/utils.py:175-209 (comm stream, local world
+size, per-node groups) and the NCCL object collectives listed at
+odc/primitives/scatter_accumulate.py:737-739.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import config
+
+_control_pg: Optional[dist.ProcessGroup] = None
+_comm_stream = None
+_local_world_pg = None
+
+
+def world_size() -> int:
+    return dist.get_world_size() if dist.is_initialized() else 1
+
+
+def rank() -> int:
+    return dist.get_rank() if dist.is_initialized() else 0
+
+
+def control_group() -> Optional[dist.ProcessGroup]:
+    """A gloo group spanning WORLD for host object collectives (None when world is 1)."""
+    global _control_pg
+    if not dist.is_initialized() or dist.get_world_size() == 1:
+        return None
+    if _control_pg is None:
+        if dist.get_backend() == "gloo":
+            _control_pg = dist.group.WORLD
+        else:
+            _control_pg = dist.new_group(backend="gloo")
+    return _control_pg
+
+
+def reset_control_group() -> None:
+    global _control_pg, _local_world_pg, _comm_stream
+    _control_pg = None
+    _local_world_pg = None
+    _comm_stream = None
+
+
+def all_gather_object(obj: Any) -> List[Any]:
+    pg = control_group()
+    if pg is None:
+        return [obj]
+    out: List[Any] = [None] * dist.get_world_size()
+    dist.all_gather_object(out, obj, group=pg)
+    return out
+
+
+def broadcast_object(obj: Any, src: int = 0) -> Any:
+    pg = control_group()
+    if pg is None:
+        return obj
+    box = [obj]
+    dist.broadcast_object_list(box, src=src, group=pg)
+    return box[0]
+
+
+def host_barrier() -> None:
+    """Barrier on the control group: orders host code only, touches no CUDA stream."""
+    pg = control_group()
+    if pg is not None:
+        dist.barrier(group=pg)
+
+
+def group_ranks(pg: Optional[dist.ProcessGroup]) -> List[int]:
+    """Global ranks of ``pg`` in group-rank order (WORLD when ``pg`` is None)."""
+    if not dist.is_initialized():
+        return [0]
+    if pg is None or pg is dist.group.WORLD:
+        return list(range(dist.get_world_size()))
+    return list(dist.get_process_group_ranks(pg))
+
+
+def get_local_world_size() -> int:
+    return config.local_world_size(world_size())
+
+
+def get_local_world_pg():
+    """Per-node process groups; ranks of one node are contiguous (utils.py:180-193)."""
+    global _local_world_pg
+    if _local_world_pg is None and dist.is_initialized():
+        lws = get_local_world_size()
+        ws = dist.get_world_size()
+        if ws % lws != 0:
+            raise ValueError(f"world size {ws} is not a multiple of the local world size {lws}")
+        mine = None
+        for node in range(ws // lws):
+            ranks = list(range(node * lws, (node + 1) * lws))
+            pg = dist.new_group(ranks=ranks)
+            if dist.get_rank() in ranks:
+                mine = pg
+        _local_world_pg = mine
+    return _local_world_pg
+
+
+def get_comm_stream():
+    """The one side stream on which on-demand transfers run (utils.py:175-178)."""
+    global _comm_stream
+    if not torch.cuda.is_available():
+        return None
+    if _comm_stream is None:
+        _comm_stream = torch.cuda.Stream(priority=-1)
+    return _comm_stream
+
+
+def job_token() -> str:
+    """A string shared by all ranks of this job and unique on the host (names shm files / sockets)."""
+    tok = None
+    if rank() == 0:
+        tok = f"{os.getpid()}_{int.from_bytes(os.urandom(4), 'little'):08x}"
+    return broadcast_object(tok, src=0)

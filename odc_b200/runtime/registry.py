@@ -1,0 +1,173 @@
+"""Process-wide registry of named symmetric buffers.
+
+Same contract as the reference's ``SymmBufferRegistry`` (odc/primitives/utils.py:88-172):
+``key -> local tensor`` plus ``key -> that buffer on every same-node peer``, collective
+allocation, allocate-on-first-use ``update_symm_buffer`` with an epoch ``flush``, reverse lookup
+from a local tensor to its peers, ``finalize`` and ``memory_allocated``.  Additions for the
+kernels: per-key device tables of peer addresses, so that one launch can reach every peer.
+"""
+from __future__ import annotations
+
+import logging
+import math
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import torch
+
+from . import control
+from .heap import SymmetricHeap, create_heap
+
+logger = logging.getLogger("odc_b200")
+
+
+class SymmBuffer:
+    __slots__ = ("key", "offset", "numel", "dtype", "shape", "local")
+
+    def __init__(self, key, offset, numel, dtype, shape, local):
+        self.key, self.offset, self.numel, self.dtype, self.shape, self.local = (
+            key, offset, numel, dtype, shape, local)
+
+    @property
+    def nbytes(self) -> int:
+        return self.numel * self.local.element_size()
+
+
+class SymmBufferRegistry:
+    _instance: Optional["SymmBufferRegistry"] = None
+
+    def __init__(self, heap: SymmetricHeap):
+        self.heap = heap
+        self.buffers: Dict[Hashable, SymmBuffer] = {}
+        self._by_offset: Dict[int, Hashable] = {}
+        self._updated: Dict[Hashable, bool] = {}
+        self._ptr_tables: Dict[tuple, torch.Tensor] = {}
+
+    # -- singleton -------------------------------------------------------------------------
+    @classmethod
+    def get_instance(cls) -> "SymmBufferRegistry":
+        if cls._instance is None:
+            raise RuntimeError("symmetric heap not initialised: call odc_b200.init_nvshmem() first")
+        return cls._instance
+
+    @classmethod
+    def is_initialized(cls) -> bool:
+        return cls._instance is not None
+
+    @classmethod
+    def initialize(cls, device=None, nbytes: Optional[int] = None) -> "SymmBufferRegistry":
+        if cls._instance is None:
+            if device is None:
+                device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu"
+            cls._instance = cls(create_heap(torch.device(device), nbytes))
+        return cls._instance
+
+    # -- allocation ------------------------------------------------------------------------
+    def allocate_symm_buffer(self, key, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        """Collective: every rank calls with the same key/shape/dtype in the same order."""
+        if key in self.buffers:
+            raise KeyError(f"symmetric buffer {key!r} already allocated")
+        shape = tuple(int(s) for s in shape)
+        numel = int(math.prod(shape))
+        esize = torch.empty((), dtype=dtype).element_size()
+        offset = self.heap.alloc(max(numel, 1) * esize)
+        local = self.heap.local(offset, numel, dtype).view(shape)
+        local._odc_is_symmetric = True
+        self.buffers[key] = SymmBuffer(key, offset, numel, dtype, shape, local)
+        self._by_offset[offset] = key
+        logger.info("symmetric buffer %r: %d x %s at offset %d (%.1f MiB in use)", key, numel, dtype,
+                    offset, self.memory_allocated() / 2**20)
+        return local
+
+    def get_or_create_symm_buffer(self, key, shape, dtype) -> torch.Tensor:
+        if key in self.buffers:
+            return self.buffers[key].local
+        return self.allocate_symm_buffer(key, shape, dtype)
+
+    def get_symm_buffer(self, key) -> torch.Tensor:
+        return self.buffers[key].local
+
+    def has_key(self, key) -> bool:
+        return key in self.buffers
+
+    def deallocate_symm_buffer(self, key) -> None:
+        buf = self.buffers.pop(key)
+        self._by_offset.pop(buf.offset, None)
+        self._updated.pop(key, None)
+        self._ptr_tables = {k: v for k, v in self._ptr_tables.items() if k[0] != buf.offset}
+        self.heap.free(buf.offset)
+
+    def update_symm_buffer(self, key, values: torch.Tensor) -> torch.Tensor:
+        """Allocate on first use, copy ``values`` in once per epoch, then a host barrier.
+
+        The barrier makes the freshly written shard visible before any peer may gather it
+        (odc/primitives/utils.py:106-116).
+        """
+        buf = self.get_or_create_symm_buffer(key, values.shape, values.dtype)
+        if not self._updated.get(key, False):
+            buf.copy_(values)
+            self._updated[key] = True
+            if buf.is_cuda:
+                torch.cuda.current_stream().synchronize()
+            control.host_barrier()
+        return buf
+
+    def flush(self) -> None:
+        """Start a new epoch: the next ``update_symm_buffer`` of every key copies again."""
+        for k in self._updated:
+            self._updated[k] = False
+
+    # -- peers -----------------------------------------------------------------------------
+    def key_of(self, tensor: torch.Tensor):
+        off = self.heap.offset_of(tensor)
+        if off is None:
+            return None, None
+        if off in self._by_offset:
+            return self._by_offset[off], 0
+        # a view that starts inside a registered buffer
+        for boff, key in self._by_offset.items():
+            buf = self.buffers[key]
+            if boff <= off < boff + max(buf.nbytes, 1):
+                return key, off - boff
+        return None, None
+
+    def offset_of(self, tensor: torch.Tensor) -> int:
+        off = self.heap.offset_of(tensor)
+        if off is None:
+            raise ValueError("tensor does not live in the symmetric heap")
+        return off
+
+    def get_peer_tensors(self, local_tensor: torch.Tensor) -> List[torch.Tensor]:
+        """The same buffer on every rank of the heap, indexed by global rank."""
+        off = self.offset_of(local_tensor)
+        n, dt = local_tensor.numel(), local_tensor.dtype
+        return [self.heap.peer(r, off, n, dt).view(local_tensor.shape) for r in range(self.heap.world)]
+
+    def peer_ptrs(self, local_tensor: torch.Tensor, ranks: Sequence[int]) -> List[int]:
+        off = self.offset_of(local_tensor)
+        return [self.heap.peer_ptr(r, off) for r in ranks]
+
+    def peer_ptr_table(self, local_tensor: torch.Tensor, ranks: Sequence[int]) -> torch.Tensor:
+        """Device int64 tensor with the address of this buffer on each of ``ranks`` (cached)."""
+        off = self.offset_of(local_tensor)
+        k = (off, tuple(ranks))
+        t = self._ptr_tables.get(k)
+        if t is None:
+            t = torch.tensor([self.heap.peer_ptr(r, off) for r in ranks], dtype=torch.int64,
+                             device=self.heap.device)
+            self._ptr_tables[k] = t
+        return t
+
+    # -- accounting / teardown -------------------------------------------------------------
+    def memory_allocated(self) -> int:
+        return sum(b.nbytes for b in self.buffers.values())
+
+    def memory_by_key(self) -> Dict[Hashable, int]:
+        return {k: b.nbytes for k, b in self.buffers.items()}
+
+    def finalize(self) -> None:
+        self.buffers.clear()
+        self._by_offset.clear()
+        self._updated.clear()
+        self._ptr_tables.clear()
+        self.heap.close()
+        SymmBufferRegistry._instance = None

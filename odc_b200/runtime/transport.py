@@ -1,0 +1,144 @@
+"""Transports: how bytes reach a peer's region of the symmetric heap.
+
+The primitives talk to this small interface, so the data plane can be swapped without
+touching the FSDP integration:
+
+* :class:`NvlinkP2PTransport` — same-node GPUs.  One kernel launch per call; CTAs issue
+  16-byte peer loads (gather) or vector ``red.global.add`` (scatter-accumulate) through the
+  heap's peer mappings over NVLink/NVSwitch, and bump the owners' arrival counters with a
+  system-scope release.
+* :class:`HostShmTransport` — CPU ranks over the ``/dev/shm`` heap; the functional model used
+  by the CPU/gloo tests.
+* :class:`InterNodeTransport` — placeholder for a NIC transport (the reference's NVSHMEM
+  get/put kernels, odc/primitives/gather.py:22-64 and scatter_accumulate.py:42-174); it only
+  states the interface and refuses to run.
+"""
+from __future__ import annotations
+
+import time
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import config
+from .heap import HostShmHeap, SymmetricHeap
+from .registry import SymmBufferRegistry
+from .status import OdcTimeoutError, check_status_word
+
+
+class Transport:
+    def gather(self, out2d: torch.Tensor, src_local: torch.Tensor, ranks: Sequence[int], my_index: int) -> None:
+        """``out2d[i] <- (buffer `src_local` on rank ranks[i])`` for every i, converting dtype."""
+        raise NotImplementedError
+
+    def scatter_add(self, inp2d: torch.Tensor, acc_local: torch.Tensor, counter_local: torch.Tensor,
+                    ranks: Sequence[int], my_index: int, scale: float = 1.0) -> None:
+        """``acc on ranks[i] += scale * inp2d[i]``, then one arrival on each owner's counter."""
+        raise NotImplementedError
+
+    def wait_arrivals(self, counter_local: torch.Tensor, expected: int) -> None:
+        """Return once the local arrival counter has reached ``expected`` (bounded)."""
+        raise NotImplementedError
+
+
+class HostShmTransport(Transport):
+    def __init__(self, registry: SymmBufferRegistry):
+        assert isinstance(registry.heap, HostShmHeap)
+        self.registry = registry
+        self.heap: HostShmHeap = registry.heap
+
+    def gather(self, out2d, src_local, ranks, my_index):
+        peers = self.registry.get_peer_tensors(src_local)
+        n = len(ranks)
+        for k in range(n):
+            i = (my_index + k) % n  # own shard first, rotated start (gather.py:121-122)
+            out2d[i].copy_(peers[ranks[i]].view(-1))
+
+    def scatter_add(self, inp2d, acc_local, counter_local, ranks, my_index, scale=1.0):
+        accs = self.registry.get_peer_tensors(acc_local)
+        ctrs = self.registry.get_peer_tensors(counter_local)
+        n = len(ranks)
+        for k in range(n):
+            i = (my_index + k) % n
+            r = ranks[i]
+            src = inp2d[i].to(accs[r].dtype)
+            with self.heap.owner_lock(r):
+                if scale != 1.0:
+                    accs[r].view(-1).add_(src, alpha=scale)
+                else:
+                    accs[r].view(-1).add_(src)
+                ctrs[r][0] += 1
+
+    def wait_arrivals(self, counter_local, expected):
+        deadline = time.monotonic() + config.wait_timeout_ms() / 1e3
+        while int(counter_local[0]) < expected:
+            if time.monotonic() > deadline:
+                raise OdcTimeoutError(
+                    f"rank {self.heap.rank}: {int(counter_local[0])} of {expected} gradient contributions "
+                    f"arrived within {config.wait_timeout_ms()} ms")
+            time.sleep(0.0002)
+
+
+class NvlinkP2PTransport(Transport):
+    def __init__(self, registry: SymmBufferRegistry):
+        from .. import _ext
+
+        self.ext = _ext.load()
+        self.registry = registry
+        self.heap: SymmetricHeap = registry.heap
+        # [0] error code, [1] detail, [2] observed value, [3] spare — written by kernels that give up
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.heap.device)
+        self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self.launches = 0
+
+    def gather(self, out2d, src_local, ranks, my_index):
+        table = self.registry.peer_ptr_table(src_local, ranks)
+        self.ext.gather(out2d, table, src_local.numel(), src_local.dtype, my_index, config.debug_bounds(),
+                        self.status)
+        self.launches += 1
+
+    def scatter_add(self, inp2d, acc_local, counter_local, ranks, my_index, scale=1.0):
+        acc_table = self.registry.peer_ptr_table(acc_local, ranks)
+        ctr_table = self.registry.peer_ptr_table(counter_local, ranks)
+        self.ext.scatter_accumulate(inp2d, acc_table, ctr_table, acc_local.numel(), acc_local.dtype,
+                                    my_index, float(scale), config.debug_bounds(), self.status)
+        self.launches += 1
+
+    def wait_arrivals(self, counter_local, expected):
+        self.ext.wait_counter(counter_local, int(expected), config.wait_timeout_ms(), self.status)
+        self.launches += 1
+        self.check()
+
+    def check(self) -> None:
+        """Read the device status word (one small D2H copy + stream sync) and raise if a kernel gave up."""
+        self._status_host.copy_(self.status, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        code = int(self._status_host[0])
+        if code != 0:
+            detail, seen = int(self._status_host[1]), int(self._status_host[2])
+            self.status.zero_()
+            check_status_word(code, detail, seen)
+
+
+class InterNodeTransport(Transport):
+    """Interface placeholder for peers that are not on this node's NVLink domain."""
+
+    def _no(self):
+        raise NotImplementedError(
+            "inter-node transport is not built: this build moves data only between GPUs of one "
+            "NVLink/NVSwitch domain")
+
+    def gather(self, *a, **k):
+        self._no()
+
+    def scatter_add(self, *a, **k):
+        self._no()
+
+    def wait_arrivals(self, *a, **k):
+        self._no()
+
+
+def make_transport(registry: SymmBufferRegistry) -> Transport:
+    if registry.heap.device.type == "cuda":
+        return NvlinkP2PTransport(registry)
+    return HostShmTransport(registry)

@@ -1,0 +1,1 @@
+from .nvtx import nvtx_range, nvtx_record_function

@@ -1,0 +1,59 @@
+"""Run a function on N CPU ranks (gloo) in child processes and collect the results."""
+import os
+import socket
+import tempfile
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, fn, args, outdir, env):
+    os.environ.update(env)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["RANK"] = str(rank)
+    os.environ["WORLD_SIZE"] = str(world)
+    os.environ.setdefault("LOCAL_WORLD_SIZE", str(world))
+    torch.set_num_threads(1)
+    try:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        out = fn(rank, world, *args)
+        torch.save(out, os.path.join(outdir, f"out_{rank}.pt"))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        with open(os.path.join(outdir, f"err_{rank}.txt"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+
+
+def run_ranks(fn, world, *args, env=None, timeout=240):
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    with tempfile.TemporaryDirectory() as outdir:
+        procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, outdir, env or {})) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout)
+        errs = []
+        for r, p in enumerate(procs):
+            if p.is_alive():
+                p.kill()
+                errs.append(f"rank {r} timed out")
+            ef = os.path.join(outdir, f"err_{r}.txt")
+            if os.path.exists(ef):
+                errs.append(open(ef).read())
+            elif p.exitcode not in (0, None):
+                errs.append(f"rank {r} exit code {p.exitcode}")
+        if errs:
+            raise RuntimeError("\n".join(errs))
+        return [torch.load(os.path.join(outdir, f"out_{r}.pt"), weights_only=False) for r in range(world)]
