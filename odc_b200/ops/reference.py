@@ -1,0 +1,105 @@
+"""Plain PyTorch statements of every op.
+
+These are the CPU implementations (autograd differentiates them) and the fp32 oracles that the
+CUDA kernels are tested against.  Shapes use packed variable-length layout: ``T`` tokens of all
+sequences of a microbatch concatenated, ``cu_seqlens`` giving sequence boundaries.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+
+def linear(x, w, bias=None):
+    return F.linear(x, w, bias)
+
+
+def rms_norm(x, weight, eps: float):
+    xf = x.float()
+    rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (xf * rstd * weight.float()).to(x.dtype)
+
+
+def layer_norm(x, weight, bias, eps: float):
+    return F.layer_norm(x.float(), (x.shape[-1],), weight.float(), None if bias is None else bias.float(),
+                        eps).to(x.dtype)
+
+
+def rope_tables(position_ids: torch.Tensor, head_dim: int, theta: float):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=position_ids.device) / head_dim))
+    ang = position_ids.float()[:, None] * inv[None, :]
+    return ang.cos(), ang.sin()
+
+
+def rope(x: torch.Tensor, position_ids: torch.Tensor, theta: float, inverse: bool = False):
+    """Rotate-half rotary embedding on ``x`` of shape ``[T, H, D]`` (HF Llama/Qwen convention)."""
+    d = x.shape[-1]
+    cos, sin = rope_tables(position_ids, d, theta)
+    if inverse:
+        sin = -sin
+    xf = x.float()
+    x1, x2 = xf[..., : d // 2], xf[..., d // 2:]
+    c, s = cos[:, None, :], sin[:, None, :]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1).to(x.dtype)
+
+
+def swiglu(gate_up: torch.Tensor):
+    """``silu(gate) * up`` with ``gate_up = [gate | up]`` along the last dim."""
+    f = gate_up.shape[-1] // 2
+    g, u = gate_up[..., :f].float(), gate_up[..., f:].float()
+    return (F.silu(g) * u).to(gate_up.dtype)
+
+
+def gelu(x):
+    return F.gelu(x)
+
+
+def varlen_attention(q, k, v, cu_seqlens, causal: bool = True, scale: Optional[float] = None):
+    """Attention over packed sequences.  ``q``: [T, Hq, D]; ``k``/``v``: [T, Hkv, D] (GQA)."""
+    T, hq, d = q.shape
+    hkv = k.shape[1]
+    rep = hq // hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    out = torch.empty_like(q)
+    bounds = cu_seqlens.tolist()
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        if e == s:
+            continue
+        qs = q[s:e].float().transpose(0, 1)                       # [Hq, L, D]
+        ks = k[s:e].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        vs = v[s:e].float().transpose(0, 1).repeat_interleave(rep, dim=0)
+        att = (qs @ ks.transpose(1, 2)) * scale
+        if causal:
+            L = e - s
+            mask = torch.ones(L, L, dtype=torch.bool, device=q.device).tril()
+            att = att.masked_fill(~mask, float("-inf"))
+        out[s:e] = (att.softmax(-1) @ vs).transpose(0, 1).to(q.dtype)
+    return out
+
+
+def linear_cross_entropy(h, w, labels, loss_scale=None, ignore_index: int = -100, chunk: int = 4096):
+    """``sum_t loss_scale[t] * CE(h[t] @ w.T, labels[t])`` without keeping ``[T, vocab]`` logits alive."""
+    total = h.new_zeros((), dtype=torch.float32)
+    for s in range(0, h.shape[0], chunk):
+        logits = F.linear(h[s:s + chunk], w).float()
+        lab = labels[s:s + chunk]
+        per_tok = F.cross_entropy(logits, lab, reduction="none", ignore_index=ignore_index)
+        if loss_scale is not None:
+            per_tok = per_tok * loss_scale[s:s + chunk].float()
+        total = total + per_tok.sum()
+    return total
+
+
+def adamw_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step, grad_scale: float = 1.0):
+    """In-place decoupled-weight-decay Adam on fp32 tensors (matches ``torch.optim.AdamW``)."""
+    g = g.float() * grad_scale
+    p.mul_(1 - lr * weight_decay)
+    m.mul_(beta1).add_(g, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+    p.addcdiv_(m, denom, value=-lr / bc1)

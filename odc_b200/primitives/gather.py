@@ -34,17 +34,23 @@ class GatherService:
     def gather_into_tensor(self, output: torch.Tensor, input: torch.Tensor,
                            pg: Optional[dist.ProcessGroup] = None, *, use_comm_stream: bool = False) -> None:
         ranks = control.group_ranks(pg)
+        if control.rank() not in ranks:
+            raise ValueError(f"rank {control.rank()} is not a member of the group {ranks}")
+        self.gather_ranks(output, input, ranks, use_comm_stream=use_comm_stream)
+
+    def gather_ranks(self, output: torch.Tensor, input: torch.Tensor, ranks, *,
+                     use_comm_stream: bool = False) -> None:
+        """Pull buffer ``input`` from an explicit list of global ranks (this rank need not be one of them)."""
+        ranks = list(ranks)
         n = len(ranks)
         me = control.rank()
-        if me not in ranks:
-            raise ValueError(f"rank {me} is not a member of the group {ranks}")
         if output.numel() != input.numel() * n:
             raise ValueError(f"output has {output.numel()} elements, expected {input.numel()} x {n}")
         if not output.is_contiguous():
             raise ValueError("output must be contiguous")
         if self.registry.heap.offset_of(input) is None:
             raise ValueError("input must be a tensor in the symmetric heap (see SymmBufferRegistry)")
-        my_index = ranks.index(me)
+        my_index = ranks.index(me) if me in ranks else me % n
         out2d = output.view(n, -1)
         with nvtx_range("odc::gather"):
             stream = control.get_comm_stream() if (use_comm_stream and output.is_cuda) else None

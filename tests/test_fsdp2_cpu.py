@@ -1,0 +1,103 @@
+"""FSDP2 with on-demand communication against stock FSDP2, on CPU ranks (gloo)."""
+import pytest
+import torch
+
+from _mp import run_ranks
+
+
+def _make_batches(rank, step, n_micro, vocab=1024):
+    from odc_b200.data import LengthSpec, make_minibatch
+    return make_minibatch(rank, step, vocab, LengthSpec("uniform", lo=16, hi=128), n_micro, 128, seed=7)
+
+
+def _train(rank, world, mode, steps, uneven, mesh_shape, hpz, mp):
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+    from odc_b200.models import DecoderLM, get_config
+
+    torch.manual_seed(0)
+    model = DecoderLM(get_config("tiny"))
+    model.reset_parameters(seed=0)
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 256 << 20)
+        fsdp2.patch_fsdp2(enable_hpz=bool(hpz))
+    mesh = init_device_mesh("cpu", mesh_shape, mesh_dim_names=("rep", "shard")[-len(mesh_shape):])
+    kw = dict(mesh=mesh)
+    if mp:
+        kw["mp_policy"] = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    raf = hpz if hpz else True
+    for layer in model.layers:
+        fully_shard(layer, reshard_after_forward=raf, **kw)
+    fully_shard(model, reshard_after_forward=raf, **kw)
+    if mode == "odc":
+        for m in list(model.layers) + [model]:
+            fsdp2.patch_lazy_init(m)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for step in range(steps):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        n_micro = (2 + rank) if uneven else 2
+        if uneven and mode == "stock":
+            n_micro = 2 + world - 1  # lock-step FSDP must run the same count: pad with empty work below
+        total = torch.zeros(())
+        for i in range(n_micro):
+            real = i < ((2 + rank) if uneven else 2)
+            mb = _make_batches(rank, step, (2 + rank) if uneven else 2)[i if real else 0]
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"],
+                         labels=mb["labels"], loss_scale=mb["loss_scale"])
+            if not real:
+                loss = loss * 0.0
+            loss.backward()
+            total += loss.detach()
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+        dist.all_reduce(total)
+        losses.append(float(total))
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    breakdown = fsdp2.get_symm_buffer_memory_breakdown() if mode == "odc" else None
+    if mode == "odc":
+        fsdp2.stop()
+    return losses, full, breakdown
+
+
+def _compare(world, **kw):
+    a = run_ranks(_train, world, "stock", 4, kw.get("uneven", False), kw.get("mesh", (world,)), 0, kw.get("mp", False))
+    b = run_ranks(_train, world, "odc", 4, kw.get("uneven", False), kw.get("mesh", (world,)), kw.get("hpz", 0),
+                  kw.get("mp", False))
+    la, lb = a[0][0], b[0][0]
+    tol = 2e-2 if kw.get("mp") else 1e-4
+    assert la == pytest.approx(lb, rel=tol), (la, lb)
+    assert all(x == x for x in lb)
+    for k in a[0][1]:
+        torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=max(tol, 5e-3), atol=max(tol * 0.1, 2e-4))
+    return b
+
+
+def test_fsdp2_loss_parity_world2():
+    b = _compare(2)
+    assert b[0][2]["fsdp_params"] > 0 and b[0][2]["accumulation"] > 0
+
+
+def test_fsdp2_uneven_microbatches():
+    _compare(2, uneven=True)
+
+
+def test_fsdp2_mixed_precision():
+    b = _compare(2, mp=True)
+    assert b[0][2]["lowp_replica"] > 0
+
+
+def test_fsdp2_hsdp():
+    _compare(4, mesh=(2, 2))
+
+
+def test_fsdp2_hpz():
+    b = _compare(4, hpz=2)
+    assert b[0][2]["hpz_buffer"] > 0
