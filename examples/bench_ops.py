@@ -1,0 +1,154 @@
+"""Device-timed micro-benchmarks of this package's kernels on one GPU.
+
+    python examples/bench_ops.py gemm            # tcgen05 GEMM vs torch.matmul (cuBLAS), three layouts
+    python examples/bench_ops.py elementwise     # RMSNorm / RoPE / SwiGLU / CE / AdamW achieved GB/s
+    python examples/bench_ops.py comm            # gather / scatter_accumulate with peers emulated on one GPU
+    python examples/bench_ops.py attention       # varlen attention fwd/bwd vs flash-attn
+
+Timing: CUDA events on the launching stream, >= 3 warm-up runs, an L2 flush (256 MB write) between
+timed iterations, median of the timed runs.  Fractions are of the measured peaks in MEASURED_PEAKS.json
+when that file is present.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+_flush = None
+
+
+def timed(fn, iters=10, warmup=3):
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def bench_gemm():
+    from odc_b200 import _ext
+    ext = _ext.load()
+    hbm, tf, kind = peaks()
+    shapes = [(8192, 8192, 8192), (16384, 3072, 2048), (16384, 2048, 2048), (16384, 16384, 2048),
+              (16384, 2048, 8192), (4096, 128256, 2048), (16384, 6144, 4096), (16384, 28672, 4096)]
+    print(f"{'layout':6} {'M':>6} {'N':>6} {'K':>6} {'ours ms':>9} {'TFLOP/s':>8} {'frac':>6} {'cublas ms':>10} {'ratio':>6}")
+    for (M, N, K) in shapes:
+        for layout in ("nt", "nn", "tn"):
+            A = torch.randn(M, K, device="cuda").bfloat16()
+            B = torch.randn(K, N, device="cuda").bfloat16()
+            a = A.t().contiguous() if layout == "tn" else A
+            b = B.t().contiguous() if layout == "nt" else B
+            c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            t = timed(lambda: ext.gemm(a, b, c, layout, None, False))
+            Ar = a.t() if layout == "tn" else a
+            Br = b.t() if layout == "nt" else b
+            tr = timed(lambda: torch.matmul(Ar, Br, out=c))
+            fl = 2.0 * M * N * K / (t * 1e-3) / 1e12
+            print(f"{layout:6} {M:6d} {N:6d} {K:6d} {t:9.3f} {fl:8.1f} {fl / tf:6.2f} {tr:10.3f} {tr / t:6.2f}   (frac of {kind} {tf:.0f} TFLOP/s)")
+            del A, B, a, b, c
+
+
+def bench_elementwise():
+    from odc_b200 import _ext, ops
+    ext = _ext.load()
+    hbm, _, kind = peaks()
+    T, H, F, V = 16384, 2048, 8192, 128256
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda").bfloat16()
+    t = timed(lambda: ext.rmsnorm_fwd(x, w, 1e-5))
+    print(f"rmsnorm_fwd  {T}x{H}: {t:.3f} ms  {2 * x.numel() * 2 / t / 1e6:.0f} GB/s ({2 * x.numel() * 2 / t / 1e6 / hbm:.2f} of {kind})")
+    y, rstd = ext.rmsnorm_fwd(x, w, 1e-5)
+    t = timed(lambda: ext.rmsnorm_bwd(y, x, w, rstd))
+    print(f"rmsnorm_bwd  {T}x{H}: {t:.3f} ms  {3 * x.numel() * 2 / t / 1e6:.0f} GB/s ({3 * x.numel() * 2 / t / 1e6 / hbm:.2f})")
+    gu = torch.randn(T, 2 * F, device="cuda").bfloat16()
+    t = timed(lambda: ext.swiglu_fwd(gu))
+    print(f"swiglu_fwd   {T}x{F}: {t:.3f} ms  {3 * T * F * 2 / t / 1e6:.0f} GB/s ({3 * T * F * 2 / t / 1e6 / hbm:.2f})")
+    dy = torch.randn(T, F, device="cuda").bfloat16()
+    t = timed(lambda: ext.swiglu_bwd(dy, gu))
+    print(f"swiglu_bwd   {T}x{F}: {t:.3f} ms  {5 * T * F * 2 / t / 1e6:.0f} GB/s ({5 * T * F * 2 / t / 1e6 / hbm:.2f})")
+    qkv = torch.randn(T, 3072, device="cuda").bfloat16()
+    pos = torch.arange(T, device="cuda") % 4096
+    t = timed(lambda: ext.rope_qkv(qkv, pos, 32, 8, 64, 500000.0, False))
+    print(f"rope_qkv     {T}x3072: {t:.3f} ms  {2 * qkv.numel() * 2 / t / 1e6:.0f} GB/s ({2 * qkv.numel() * 2 / t / 1e6 / hbm:.2f})")
+    lg = torch.randn(4096, V, device="cuda").bfloat16()
+    lab = torch.randint(0, V, (4096,), device="cuda")
+    loss = torch.zeros((), device="cuda")
+    t = timed(lambda: ext.ce_fwd_bwd(lg, lab, None, loss, -100))
+    print(f"ce_fwd_bwd   4096x{V}: {t:.3f} ms  {3 * lg.numel() * 2 / t / 1e6:.0f} GB/s (3 passes; {3 * lg.numel() * 2 / t / 1e6 / hbm:.2f})")
+    n = 256 << 20
+    p, g, m, v = (torch.randn(n, device="cuda") for _ in range(4))
+    low = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    t = timed(lambda: ext.adamw_step(p, g, m, v, low, 1e-3, 0.9, 0.95, 1e-8, 0.01, 1, 1.0))
+    print(f"adamw        {n}: {t:.3f} ms  {n * 30 / t / 1e6:.0f} GB/s ({n * 30 / t / 1e6 / hbm:.2f})")
+
+
+def bench_comm():
+    from odc_b200 import _ext
+    ext = _ext.load()
+    hbm, _, kind = peaks()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for world in (2, 8):
+        for mib in (1, 16, 128):
+            n = mib * (1 << 20) // 2
+            shards = [torch.randn(n, device="cuda").bfloat16() for _ in range(world)]
+            table = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64, device="cuda")
+            out = torch.empty(world, n, dtype=torch.bfloat16, device="cuda")
+            t = timed(lambda: ext.gather(out, table, n, torch.bfloat16, 0, False, status))
+            gb = 2 * out.numel() * 2 / t / 1e6
+            accs = [torch.zeros(n, device="cuda") for _ in range(world)]
+            ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+            at = torch.tensor([s.data_ptr() for s in accs], dtype=torch.int64, device="cuda")
+            ct = torch.tensor([s.data_ptr() for s in ctrs], dtype=torch.int64, device="cuda")
+            t2 = timed(lambda: ext.scatter_accumulate(out, at, ct, n, torch.float32, 0, 1.0, False, status))
+            gb2 = out.numel() * (2 + 8) / t2 / 1e6
+            print(f"world {world} shard {mib:4d} MiB: gather {t:.3f} ms {gb:.0f} GB/s ({gb / hbm:.2f} of {kind} HBM; local emulation)"
+                  f" | scatter_acc {t2:.3f} ms {gb2:.0f} GB/s ({gb2 / hbm:.2f})")
+
+
+def bench_attention():
+    from odc_b200 import ops
+    from flash_attn import flash_attn_varlen_func
+    _, tf, kind = peaks()
+    for (T, seqs, hq, hkv, d) in [(16384, 16, 32, 8, 64), (16384, 2, 32, 8, 128), (32768, 1, 32, 8, 128)]:
+        L = T // seqs
+        cu = torch.arange(0, T + 1, L, device="cuda", dtype=torch.int32)
+        q = torch.randn(T, hq, d, device="cuda").bfloat16().requires_grad_()
+        k = torch.randn(T, hkv, d, device="cuda").bfloat16().requires_grad_()
+        v = torch.randn(T, hkv, d, device="cuda").bfloat16().requires_grad_()
+        flops = 4.0 * hq * d * seqs * L * L / 2
+        t_f = timed(lambda: ops.varlen_attention(q, k, v, cu, L))
+        t_r = timed(lambda: flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True))
+        o = ops.varlen_attention(q, k, v, cu, L)
+        do = torch.randn_like(o)
+        t_b = timed(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True))
+        o2 = flash_attn_varlen_func(q, k, v, cu, cu, L, L, causal=True)
+        t_rb = timed(lambda: torch.autograd.grad(o2, (q, k, v), do, retain_graph=True))
+        print(f"T={T} seqs={seqs} hq={hq} d={d}: fwd {t_f:.3f} ms {flops / t_f / 1e9:.0f} TFLOP/s ({flops / t_f / 1e9 / tf:.2f} of {kind}) "
+              f"[flash-attn {t_r:.3f} ms] | bwd {t_b:.3f} ms {2.5 * flops / t_b / 1e9:.0f} TFLOP/s [flash-attn {t_rb:.3f} ms]")
+
+
+if __name__ == "__main__":
+    which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    {"gemm": bench_gemm, "elementwise": bench_elementwise, "comm": bench_comm, "attention": bench_attention}[which]()

@@ -1,0 +1,311 @@
+// Python bindings: tensors in, raw pointers + current stream out to the launchers in kernels/api.h.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../heap/symm_heap.h"
+#include "../kernels/api.h"
+
+namespace py = pybind11;
+using torch::Tensor;
+
+namespace {
+
+void check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+
+int sm_count() {
+  static int n = [] {
+    int dev = 0, v = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+    return v > 0 ? v : 148;
+  }();
+  return n;
+}
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int kind_of(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return odc::kF32;
+    case at::kBFloat16: return odc::kBF16;
+    case at::kHalf: return odc::kF16;
+    default: TORCH_CHECK(false, "unsupported dtype ", t);
+  }
+}
+
+// ring of self-resetting completion counters used by scatter_accumulate launches
+unsigned int* next_done_slot(int device) {
+  static std::mutex mu;
+  static std::unordered_map<int, Tensor> rings;
+  static std::unordered_map<int, unsigned long long> seq;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = rings.find(device);
+  if (it == rings.end()) {
+    auto t = torch::zeros({1024}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+    it = rings.emplace(device, t).first;
+    seq[device] = 0;
+  }
+  unsigned long long s = seq[device]++;
+  return reinterpret_cast<unsigned int*>(it->second.data_ptr<int>()) + (s % 1024);
+}
+
+// ---------------------------------------------------------------------------------------- heap
+uintptr_t heap_create(int rank, int world, int device, size_t bytes, const std::string& mode,
+                      const std::string& token) {
+  return reinterpret_cast<uintptr_t>(odc::heap_create(rank, world, device, bytes, mode, token));
+}
+odc::Heap* H(uintptr_t h) { return reinterpret_cast<odc::Heap*>(h); }
+
+Tensor tensor_from_ptr(uintptr_t ptr, int64_t numel, at::ScalarType dtype, int device) {
+  auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, device);
+  return torch::from_blob(reinterpret_cast<void*>(ptr), {numel}, [](void*) {}, opts);
+}
+
+py::bytes get_ipc_handle(const Tensor& t) {
+  TORCH_CHECK(t.is_cuda(), "get_ipc_handle expects a CUDA tensor");
+  c10::cuda::CUDAGuard g(t.device());
+  return py::bytes(odc::ipc_export(t.data_ptr()));
+}
+
+Tensor reconstruct_tensor(const std::string& blob, std::vector<int64_t> shape, at::ScalarType dtype) {
+  void* p = odc::ipc_import(blob);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  auto opts = torch::TensorOptions().dtype(dtype).device(torch::kCUDA, dev);
+  return torch::from_blob(p, shape, [](void*) {}, opts);
+}
+
+// ---------------------------------------------------------------------------------------- comm
+void gather(Tensor out2d, Tensor table, int64_t n, at::ScalarType src_dtype, int my_index, bool checkb,
+            Tensor status) {
+  c10::cuda::CUDAGuard g(out2d.device());
+  const int nranks = static_cast<int>(table.numel());
+  TORCH_CHECK(out2d.is_contiguous() && out2d.numel() == n * nranks, "gather: bad output shape");
+  const int ssz = static_cast<int>(c10::elementSize(src_dtype));
+  const int dsz = static_cast<int>(out2d.element_size());
+  const bool narrow = (src_dtype == at::kFloat && out2d.scalar_type() == at::kBFloat16);
+  TORCH_CHECK(narrow || src_dtype == out2d.scalar_type(), "gather: only same-dtype or fp32->bf16");
+  check(odc::launch_gather(table.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(table.data_ptr<int64_t>()) : nullptr,
+                           out2d.data_ptr(), static_cast<size_t>(n), ssz, dsz, narrow, nranks, my_index, checkb,
+                           status.data_ptr<int>(), sm_count(), cur_stream()),
+        "gather launch");
+}
+
+void scatter_accumulate(Tensor inp2d, Tensor acc_table, Tensor ctr_table, int64_t n, at::ScalarType acc_dtype,
+                        int my_index, double scale, bool checkb, Tensor status) {
+  c10::cuda::CUDAGuard g(inp2d.device());
+  const int nranks = static_cast<int>(acc_table.numel());
+  TORCH_CHECK(inp2d.is_contiguous() && inp2d.numel() == n * nranks, "scatter_accumulate: bad input shape");
+  (void)checkb;
+  (void)status;
+  check(odc::launch_scatter_accumulate(inp2d.data_ptr(), kind_of(inp2d.scalar_type()),
+                                       reinterpret_cast<const long long*>(acc_table.data_ptr<int64_t>()),
+                                       kind_of(acc_dtype),
+                                       reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()),
+                                       static_cast<size_t>(n), nranks, my_index, static_cast<float>(scale),
+                                       next_done_slot(inp2d.get_device()), sm_count(), cur_stream()),
+        "scatter_accumulate launch");
+}
+
+void wait_counter(Tensor counter, int64_t expected, int64_t timeout_ms, Tensor status) {
+  c10::cuda::CUDAGuard g(counter.device());
+  check(odc::launch_wait_counter(counter.data_ptr(), static_cast<unsigned long long>(expected),
+                                 static_cast<unsigned long long>(timeout_ms) * 1000000ull, status.data_ptr<int>(),
+                                 cur_stream()),
+        "wait_counter launch");
+}
+
+// ---------------------------------------------------------------------------------------- ops
+std::tuple<Tensor, Tensor> rmsnorm_fwd(Tensor x, Tensor w, double eps) {
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "rmsnorm: x must be [T,H] bf16");
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.is_contiguous(), "rmsnorm: weight must be bf16");
+  auto y = torch::empty_like(x);
+  auto rstd = torch::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  check(odc::launch_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(),
+                                static_cast<int>(x.size(0)), static_cast<int>(x.size(1)), static_cast<float>(eps),
+                                sm_count(), cur_stream()),
+        "rmsnorm_fwd");
+  return {y, rstd};
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) {
+  c10::cuda::CUDAGuard g(x.device());
+  const int rows = static_cast<int>(x.size(0)), cols = static_cast<int>(x.size(1));
+  auto dx = torch::empty_like(x);
+  const int grid = odc::rmsnorm_bwd_grid(rows, sm_count());
+  auto partial = torch::empty({grid, cols}, x.options().dtype(at::kFloat));
+  auto dw = torch::empty({cols}, x.options().dtype(at::kFloat));
+  check(odc::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                                partial.data_ptr<float>(), dw.data_ptr<float>(), rows, cols, grid, cur_stream()),
+        "rmsnorm_bwd");
+  return {dx, dw};
+}
+
+Tensor rope_qkv(Tensor qkv, Tensor pos, int n_q, int n_kv, int head_dim, double theta, bool inverse) {
+  c10::cuda::CUDAGuard g(qkv.device());
+  TORCH_CHECK(qkv.dim() == 2 && qkv.is_contiguous() && qkv.scalar_type() == at::kBFloat16, "rope: qkv [T,W] bf16");
+  TORCH_CHECK(qkv.size(1) == int64_t(n_q + 2 * n_kv) * head_dim, "rope: width mismatch");
+  TORCH_CHECK(pos.scalar_type() == at::kLong && pos.numel() == qkv.size(0), "rope: position_ids int64 [T]");
+  auto out = torch::empty_like(qkv);
+  check(odc::launch_rope_qkv(qkv.data_ptr(), out.data_ptr(), reinterpret_cast<const long long*>(pos.data_ptr<int64_t>()),
+                             static_cast<int>(qkv.size(0)), n_q, n_kv, head_dim, static_cast<float>(theta), inverse,
+                             cur_stream()),
+        "rope_qkv");
+  return out;
+}
+
+Tensor swiglu_fwd(Tensor gu) {
+  c10::cuda::CUDAGuard g(gu.device());
+  TORCH_CHECK(gu.is_contiguous() && gu.scalar_type() == at::kBFloat16, "swiglu: bf16 contiguous");
+  const int f = static_cast<int>(gu.size(-1) / 2);
+  auto sizes = gu.sizes().vec();
+  sizes.back() = f;
+  auto out = torch::empty(sizes, gu.options());
+  check(odc::launch_swiglu_fwd(gu.data_ptr(), out.data_ptr(), gu.numel() / (2 * f), f, sm_count(), cur_stream()),
+        "swiglu_fwd");
+  return out;
+}
+
+Tensor swiglu_bwd(Tensor dy, Tensor gu) {
+  c10::cuda::CUDAGuard g(gu.device());
+  const int f = static_cast<int>(gu.size(-1) / 2);
+  auto out = torch::empty_like(gu);
+  check(odc::launch_swiglu_bwd(dy.data_ptr(), gu.data_ptr(), out.data_ptr(), gu.numel() / (2 * f), f, sm_count(),
+                               cur_stream()),
+        "swiglu_bwd");
+  return out;
+}
+
+void ce_fwd_bwd(Tensor logits, Tensor labels, c10::optional<Tensor> loss_scale, Tensor loss, int64_t ignore_index) {
+  c10::cuda::CUDAGuard g(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kBFloat16, "ce: logits bf16");
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous(), "ce: labels int64");
+  const float* ls = nullptr;
+  if (loss_scale.has_value()) {
+    TORCH_CHECK(loss_scale->scalar_type() == at::kFloat && loss_scale->is_contiguous(), "ce: loss_scale fp32");
+    ls = loss_scale->data_ptr<float>();
+  }
+  check(odc::launch_ce_fwd_bwd(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()), ls,
+                               loss.data_ptr<float>(), static_cast<int>(logits.size(0)),
+                               static_cast<int>(logits.size(1)), ignore_index, cur_stream()),
+        "ce_fwd_bwd");
+}
+
+void adamw_step(Tensor p, Tensor g, Tensor m, Tensor v, c10::optional<Tensor> p_lowp, double lr, double beta1,
+                double beta2, double eps, double wd, int64_t step, double grad_scale) {
+  c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat,
+              "adamw: fp32 master state");
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous");
+  void* lp = nullptr;
+  if (p_lowp.has_value()) {
+    TORCH_CHECK(p_lowp->scalar_type() == at::kBFloat16 && p_lowp->numel() == p.numel(), "adamw: bf16 replica");
+    lp = p_lowp->data_ptr();
+  }
+  const float bc1 = 1.f - std::pow(static_cast<float>(beta1), static_cast<float>(step));
+  const float bc2 = 1.f - std::pow(static_cast<float>(beta2), static_cast<float>(step));
+  check(odc::launch_adamw(p.data_ptr<float>(), g.data_ptr(), kind_of(g.scalar_type()), m.data_ptr<float>(),
+                          v.data_ptr<float>(), lp, static_cast<size_t>(p.numel()), static_cast<float>(lr),
+                          static_cast<float>(beta1), static_cast<float>(beta2), static_cast<float>(eps),
+                          static_cast<float>(wd), bc1, bc2, static_cast<float>(grad_scale), sm_count(), cur_stream()),
+        "adamw");
+}
+
+void cast_f32_to_bf16(Tensor in, Tensor out) {
+  c10::cuda::CUDAGuard g(in.device());
+  TORCH_CHECK(in.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 && in.numel() == out.numel() &&
+                  in.is_contiguous() && out.is_contiguous(), "cast: fp32 -> bf16, same numel, contiguous");
+  check(odc::launch_cast_f32_to_bf16(in.data_ptr<float>(), out.data_ptr(), static_cast<size_t>(in.numel()), sm_count(),
+                                     cur_stream()),
+        "cast");
+}
+
+void sumsq(Tensor x, Tensor out) {
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(x.is_contiguous() && out.scalar_type() == at::kFloat, "sumsq: contiguous input, fp32 output");
+  check(odc::launch_sumsq(x.data_ptr(), kind_of(x.scalar_type()), static_cast<size_t>(x.numel()), out.data_ptr<float>(),
+                          sm_count(), cur_stream()),
+        "sumsq");
+}
+
+Tensor& gemm_status(int device) {
+  static std::mutex mu;
+  static std::unordered_map<int, Tensor> st;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = st.find(device);
+  if (it == st.end()) it = st.emplace(device, torch::zeros({4}, torch::dtype(torch::kInt32).device(torch::kCUDA, device))).first;
+  return it->second;
+}
+
+Tensor kernel_status() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return gemm_status(dev);
+}
+
+void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional<Tensor> bias, bool accumulate) {
+  c10::cuda::CUDAGuard g(a.device());
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2, "gemm: 2-D operands");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: bf16 inputs");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && c.stride(1) == 1, "gemm: innermost stride must be 1");
+  int lay, M, N, K;
+  if (layout == "nt") {
+    lay = 0; M = a.size(0); K = a.size(1); N = b.size(0);
+    TORCH_CHECK(b.size(1) == K, "gemm nt: K mismatch");
+  } else if (layout == "nn") {
+    lay = 1; M = a.size(0); K = a.size(1); N = b.size(1);
+    TORCH_CHECK(b.size(0) == K, "gemm nn: K mismatch");
+  } else if (layout == "tn") {
+    lay = 2; K = a.size(0); M = a.size(1); N = b.size(1);
+    TORCH_CHECK(b.size(0) == K, "gemm tn: K mismatch");
+  } else {
+    TORCH_CHECK(false, "gemm: unknown layout ", layout);
+  }
+  TORCH_CHECK(c.size(0) == M && c.size(1) == N, "gemm: output shape mismatch");
+  const void* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm: bias bf16 [N]");
+    bias_ptr = bias->data_ptr();
+  }
+  check(odc::gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), kind_of(c.scalar_type()), bias_ptr, M, N, K, lay,
+                       accumulate, a.stride(0), b.stride(0), c.stride(0), gemm_status(a.get_device()).data_ptr<int>(),
+                       sm_count(), cur_stream()),
+        "gemm");
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("heap_create", &heap_create);
+  m.def("heap_grow", [](uintptr_t h, size_t n) { odc::heap_grow(H(h), n); }, py::call_guard<py::gil_scoped_release>());
+  m.def("heap_ipc_handle", [](uintptr_t h) { return py::bytes(odc::heap_ipc_handle(H(h))); });
+  m.def("heap_ipc_open", [](uintptr_t h, int r, const std::string& b) { odc::heap_ipc_open(H(h), r, b); });
+  m.def("heap_base", [](uintptr_t h, int r) { return odc::heap_base(H(h), r); });
+  m.def("heap_mapped", [](uintptr_t h) { return odc::heap_mapped(H(h)); });
+  m.def("heap_destroy", [](uintptr_t h) { odc::heap_destroy(H(h)); });
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("get_ipc_handle", &get_ipc_handle);
+  m.def("reconstruct_tensor", &reconstruct_tensor);
+  m.def("gather", &gather);
+  m.def("scatter_accumulate", &scatter_accumulate);
+  m.def("wait_counter", &wait_counter);
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rope_qkv", &rope_qkv);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("adamw_step", &adamw_step);
+  m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
+  m.def("sumsq", &sumsq);
+  m.def("gemm", &gemm);
+  m.def("kernel_status", &kernel_status);
+  m.def("sm_count", &sm_count);
+}

@@ -1,0 +1,63 @@
+// Host-callable launchers of every kernel in this package.  Plain pointers + stream: no PyTorch
+// headers, so kernel files compile in seconds; the binding layer converts tensors.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace odc {
+
+enum DType : int { kF32 = 0, kBF16 = 1, kF16 = 2 };
+
+// ---- communication -------------------------------------------------------------------------
+cudaError_t launch_gather(const long long* peers, void* out, size_t n, int src_elem_size, int dst_elem_size,
+                          bool src_is_f32_dst_is_bf16, int nranks, int start, bool check, int* status,
+                          int sm_count, cudaStream_t stream);
+cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long long* accs, int acc_kind,
+                                      const long long* ctrs, size_t n, int nranks, int start, float scale,
+                                      unsigned int* done_slot, int sm_count, cudaStream_t stream);
+cudaError_t launch_wait_counter(const void* ctr, unsigned long long expected, unsigned long long budget_ns,
+                                int* status, cudaStream_t stream);
+
+// ---- elementwise / normalisation (bf16 activations, fp32 math) -----------------------------
+cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps,
+                               int sm_count, cudaStream_t stream);
+// partial: [grid, cols] fp32 scratch, dw: [cols] fp32
+cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                               float* partial, float* dw, int rows, int cols, int grid, cudaStream_t stream);
+int rmsnorm_bwd_grid(int rows, int sm_count);
+cudaError_t launch_rope_qkv(const void* in, void* out, const long long* pos, int tokens, int n_q, int n_kv,
+                            int head_dim, float theta, bool inverse, cudaStream_t stream);
+cudaError_t launch_swiglu_fwd(const void* gate_up, void* out, long long rows, int f, int sm_count,
+                              cudaStream_t stream);
+cudaError_t launch_swiglu_bwd(const void* dy, const void* gate_up, void* dgate_up, long long rows, int f,
+                              int sm_count, cudaStream_t stream);
+// logits [rows, vocab] bf16 are overwritten by scale * (softmax - onehot); loss += sum scale * nll
+cudaError_t launch_ce_fwd_bwd(void* logits, const long long* labels, const float* loss_scale, float* loss,
+                              int rows, int vocab, long long ignore_index, cudaStream_t stream);
+cudaError_t launch_adamw(float* p, const void* g, int g_kind, float* m, float* v, void* p_lowp, size_t n, float lr,
+                         float beta1, float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
+                         int sm_count, cudaStream_t stream);
+cudaError_t launch_cast_f32_to_bf16(const float* in, void* out, size_t n, int sm_count, cudaStream_t stream);
+cudaError_t launch_sumsq(const void* x, int kind, size_t n, float* out, int sm_count, cudaStream_t stream);
+
+// ---- tcgen05 GEMM ----------------------------------------------------------------------------
+// layout: 0 = "nt" C[M,N] = A[M,K] B[N,K]^T ; 1 = "nn" C = A[M,K] B[K,N] ; 2 = "tn" C = A[K,M]^T B[K,N]
+// All operands row-major bf16; C is bf16 or fp32; bias (bf16, length N) optional; accumulate adds into C.
+struct GemmPlan;
+cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const void* bias, int M, int N, int K,
+                      int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
+                      int sm_count, cudaStream_t stream);
+
+// ---- varlen attention ------------------------------------------------------------------------
+cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
+                     int num_seqs, int total_tokens, int max_seqlen, int n_q, int n_kv, int head_dim,
+                     long long q_stride, long long kv_stride, long long o_stride, float scale, bool causal,
+                     int* status, int sm_count, cudaStream_t stream);
+cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                     void* dq, void* dk, void* dv, float* delta, float* dq_acc, const int* cu_seqlens, int num_seqs,
+                     int total_tokens, int max_seqlen, int n_q, int n_kv, int head_dim, long long q_stride,
+                     long long kv_stride, long long o_stride, float scale, bool causal, int* status, int sm_count,
+                     cudaStream_t stream);
+
+}  // namespace odc

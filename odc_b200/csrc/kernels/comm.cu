@@ -1,0 +1,279 @@
+// gather / scatter_accumulate / arrival wait: the two on-demand primitives as single launches.
+//
+// gather: CTAs are striped over (peer, tile) pairs, so all peers' links are busy at once; each
+// thread keeps several 16-byte peer loads in flight and may narrow fp32 -> bf16 on the way.
+// Replaces the reference's serial per-peer Tensor.copy_ plus separate cast
+// (odc/primitives/gather.py:121-127, odc/fsdp/fsdp2.py:339-351).
+//
+// scatter_accumulate: rows of the local gradient go to their owners as 16-byte vector
+// reductions into the fp32 accumulator (no mailbox, no second pass on the owner); the last CTA
+// to finish bumps every owner's arrival counter with a system-scope release.  Replaces mailbox
+// copy + request/ack kernels + watcher add (odc/primitives/scatter_accumulate.py:649-691,369-395).
+#include "api.h"
+#include "odc_device.cuh"
+
+namespace odc {
+
+namespace {
+
+constexpr int kThreads = 512;
+constexpr int kVecPerThread = 4;                        // 16-byte accesses in flight per thread
+constexpr size_t kTileVecs = size_t(kThreads) * kVecPerThread;  // 16-byte vectors per tile (32 KiB)
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t u) { return __uint_as_float(u << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+
+// ---------------------------------------------------------------- gather, same dtype ----------
+// bytes-per-row copy; src rows are peers' buffers, dst rows are consecutive in `out`.
+__global__ void __launch_bounds__(kThreads)
+gather_copy_kernel(const long long* __restrict__ peers, unsigned char* __restrict__ out, size_t row_bytes,
+                   int nranks, int start, int vec_ok, int check, int* status) {
+  if (check) {  // debug build of the launch: refuse null or misaligned peer addresses instead of faulting
+    for (int p = 0; p < nranks; ++p) {
+      if (peers[p] == 0 || (vec_ok && (peers[p] & 15) != 0)) {
+        if (threadIdx.x == 0) report(status, kErrBounds, p, 0);
+        return;
+      }
+    }
+  }
+  const size_t nvec = vec_ok ? row_bytes / 16 : 0;
+  const size_t tiles_per_row = (nvec + kTileVecs - 1) / kTileVecs;
+  const size_t total_tiles = tiles_per_row * nranks;
+  for (size_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const int peer = (static_cast<int>(t % nranks) + start) % nranks;
+    const size_t tile = t / nranks;
+    const uint4* src = reinterpret_cast<const uint4*>(peers[peer]);
+    uint4* dst = reinterpret_cast<uint4*>(out + size_t(peer) * row_bytes);
+    const size_t v0 = tile * kTileVecs + threadIdx.x;
+    uint4 r[kVecPerThread];
+#pragma unroll
+    for (int k = 0; k < kVecPerThread; ++k) {
+      const size_t v = v0 + size_t(k) * kThreads;
+      if (v < nvec) r[k] = ld_stream_v4(src + v);
+    }
+#pragma unroll
+    for (int k = 0; k < kVecPerThread; ++k) {
+      const size_t v = v0 + size_t(k) * kThreads;
+      if (v < nvec) dst[v] = r[k];
+    }
+  }
+  // bytes not covered by whole vectors (everything when rows are not 16-byte aligned)
+  const size_t tail0 = nvec * 16;
+  const size_t tail = row_bytes - tail0;
+  const size_t total_tail = tail * nranks;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total_tail; i += size_t(gridDim.x) * blockDim.x) {
+    const int p = static_cast<int>(i / tail);
+    const size_t j = tail0 + i % tail;
+    out[size_t(p) * row_bytes + j] = reinterpret_cast<const unsigned char*>(peers[p])[j];
+  }
+}
+
+// ---------------------------------------------------------------- gather, fp32 -> bf16 --------
+__global__ void __launch_bounds__(kThreads)
+gather_f32_to_bf16_kernel(const long long* __restrict__ peers, __nv_bfloat16* __restrict__ out, size_t n,
+                          int nranks, int start) {
+  const size_t nvec = n / 8;  // 8 floats in (2 x 16 B), 8 bf16 out (16 B)
+  constexpr size_t kTile = size_t(kThreads) * 2;
+  const size_t tiles_per_row = (nvec + kTile - 1) / kTile;
+  const size_t total_tiles = tiles_per_row * nranks;
+  const bool aligned = (n % 8) == 0;  // row starts stay 16-byte aligned in the output
+  if (aligned) {
+    for (size_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int peer = (static_cast<int>(t % nranks) + start) % nranks;
+      const size_t tile = t / nranks;
+      const uint4* src = reinterpret_cast<const uint4*>(peers[peer]);
+      uint4* dst = reinterpret_cast<uint4*>(out + size_t(peer) * n);
+      uint4 a[2], b[2];
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const size_t v = tile * kTile + threadIdx.x + size_t(k) * kThreads;
+        if (v < nvec) {
+          a[k] = ld_stream_v4(src + 2 * v);
+          b[k] = ld_stream_v4(src + 2 * v + 1);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        const size_t v = tile * kTile + threadIdx.x + size_t(k) * kThreads;
+        if (v < nvec) {
+          uint4 o;
+          o.x = pack_bf16x2(__uint_as_float(a[k].x), __uint_as_float(a[k].y));
+          o.y = pack_bf16x2(__uint_as_float(a[k].z), __uint_as_float(a[k].w));
+          o.z = pack_bf16x2(__uint_as_float(b[k].x), __uint_as_float(b[k].y));
+          o.w = pack_bf16x2(__uint_as_float(b[k].z), __uint_as_float(b[k].w));
+          dst[v] = o;
+        }
+      }
+    }
+  } else {
+    const size_t total = n * nranks;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+      const int peer = static_cast<int>(i / n);
+      const size_t j = i % n;
+      out[i] = __float2bfloat16(reinterpret_cast<const float*>(peers[peer])[j]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- scatter-accumulate ---------
+// Completion: every thread's reductions -> __threadfence_system -> block barrier -> one thread
+// counts the CTA done; the last CTA releases one arrival on each owner's counter.
+__device__ __forceinline__ void finish_and_signal(const long long* ctrs, int nranks, unsigned int* done_slot) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(done_slot, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_slot = 0;  // self-reset: the slot is reusable by a later launch
+      __threadfence_system();
+      for (int p = 0; p < nranks; ++p)
+        signal_add_release_sys(reinterpret_cast<unsigned long long*>(ctrs[p]), 1ull);
+    }
+  }
+}
+
+template <typename InT>
+__global__ void __launch_bounds__(kThreads)
+scatter_acc_f32_kernel(const InT* __restrict__ inp, const long long* __restrict__ accs,
+                       const long long* __restrict__ ctrs, size_t n, int nranks, int start, float scale,
+                       unsigned int* done_slot, int vec_ok) {
+  constexpr int kPerVec = 4;  // one 16-byte reduction = 4 floats
+  const size_t nvec = n / kPerVec;
+  const bool aligned = vec_ok != 0;
+  if (aligned) {
+    const size_t tiles_per_row = (nvec + kTileVecs - 1) / kTileVecs;
+    const size_t total_tiles = tiles_per_row * nranks;
+    for (size_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const int peer = (static_cast<int>(t % nranks) + start) % nranks;
+      const size_t tile = t / nranks;
+      float* acc = reinterpret_cast<float*>(accs[peer]);
+      const InT* row = inp + size_t(peer) * n;
+      float4 r[kVecPerThread];
+#pragma unroll
+      for (int k = 0; k < kVecPerThread; ++k) {
+        const size_t v = tile * kTileVecs + threadIdx.x + size_t(k) * kThreads;
+        if (v < nvec) {
+          if constexpr (sizeof(InT) == 4) {
+            r[k] = *reinterpret_cast<const float4*>(row + v * 4);
+          } else {
+            const uint2 u = *reinterpret_cast<const uint2*>(row + v * 4);
+            r[k] = make_float4(bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y));
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kVecPerThread; ++k) {
+        const size_t v = tile * kTileVecs + threadIdx.x + size_t(k) * kThreads;
+        if (v < nvec) red_add_v4_f32(acc + v * 4, r[k].x * scale, r[k].y * scale, r[k].z * scale, r[k].w * scale);
+      }
+    }
+    // tail of each row (n % 4 elements; only reachable with nranks == 1 here)
+    if (blockIdx.x == 0) {
+      for (size_t j = nvec * 4 + threadIdx.x; j < n; j += blockDim.x)
+        for (int p = 0; p < nranks; ++p)
+          red_add_f32(reinterpret_cast<float*>(accs[p]) + j, float(inp[size_t(p) * n + j]) * scale);
+    }
+  } else {
+    const size_t total = n * nranks;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+      const int peer = static_cast<int>(i / n);
+      red_add_f32(reinterpret_cast<float*>(accs[peer]) + (i % n), float(inp[i]) * scale);
+    }
+  }
+  finish_and_signal(ctrs, nranks, done_slot);
+}
+
+// bf16 gradients into bf16 accumulators (accumulation_dtype left at the input dtype)
+__global__ void __launch_bounds__(kThreads)
+scatter_acc_bf16_kernel(const __nv_bfloat16* __restrict__ inp, const long long* __restrict__ accs,
+                        const long long* __restrict__ ctrs, size_t n, int nranks, int start, float scale,
+                        unsigned int* done_slot) {
+  const bool aligned = (n % 2) == 0;
+  const size_t total = n * nranks;
+  if (aligned) {
+    const size_t pairs = total / 2;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < pairs; i += size_t(gridDim.x) * blockDim.x) {
+      const size_t e = i * 2;
+      const int peer = (static_cast<int>(e / n) + start) % nranks;
+      const size_t j = e % n;
+      const uint32_t u = *reinterpret_cast<const uint32_t*>(inp + size_t(peer) * n + j);
+      const uint32_t s = pack_bf16x2(bf16_lo(u) * scale, bf16_hi(u) * scale);
+      red_add_bf16x2(reinterpret_cast<__nv_bfloat16*>(accs[peer]) + j, s);
+    }
+  } else {
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+      const int peer = static_cast<int>(i / n);
+      atomicAdd(reinterpret_cast<__nv_bfloat16*>(accs[peer]) + (i % n),
+                __float2bfloat16(__bfloat162float(inp[i]) * scale));
+    }
+  }
+  finish_and_signal(ctrs, nranks, done_slot);
+}
+
+__global__ void wait_counter_kernel(const unsigned long long* ctr, unsigned long long expected,
+                                    unsigned long long budget_ns, int* status) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) bounded_wait_ge(ctr, expected, budget_ns, status, /*detail=*/0);
+}
+
+int grid_for(size_t tiles, int sm_count) {
+  size_t cap = size_t(sm_count) * 2;
+  size_t g = tiles < cap ? tiles : cap;
+  return g < 1 ? 1 : static_cast<int>(g);
+}
+
+}  // namespace
+
+cudaError_t launch_gather(const long long* peers, void* out, size_t n, int src_elem_size, int dst_elem_size,
+                          bool src_is_f32_dst_is_bf16, int nranks, int start, bool check, int* status,
+                          int sm_count, cudaStream_t stream) {
+  if (n == 0 || nranks == 0) return cudaSuccess;
+  if (src_is_f32_dst_is_bf16) {
+    const size_t tiles = ((n / 8 + kThreads * 2 - 1) / (kThreads * 2) + 1) * nranks;
+    gather_f32_to_bf16_kernel<<<grid_for(tiles, sm_count), kThreads, 0, stream>>>(
+        peers, static_cast<__nv_bfloat16*>(out), n, nranks, start);
+  } else {
+    if (src_elem_size != dst_elem_size) return cudaErrorInvalidValue;
+    const size_t row_bytes = n * src_elem_size;
+    const int vec_ok = ((row_bytes % 16) == 0 || nranks == 1) && (reinterpret_cast<uintptr_t>(out) % 16) == 0;
+    const size_t tiles = ((row_bytes / 16 + kTileVecs - 1) / kTileVecs + 1) * nranks;
+    gather_copy_kernel<<<grid_for(tiles, sm_count), kThreads, 0, stream>>>(
+        peers, static_cast<unsigned char*>(out), row_bytes, nranks, start, vec_ok, check ? 1 : 0, status);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long long* accs, int acc_kind,
+                                      const long long* ctrs, size_t n, int nranks, int start, float scale,
+                                      unsigned int* done_slot, int sm_count, cudaStream_t stream) {
+  if (nranks == 0) return cudaSuccess;
+  const size_t tiles = ((n / 4 + kTileVecs - 1) / kTileVecs + 1) * nranks;
+  const int grid = grid_for(tiles, sm_count);
+  const int vec_ok = ((n % 4) == 0 || nranks == 1) && (reinterpret_cast<uintptr_t>(inp) % 16) == 0;
+  if (acc_kind == kF32 && in_kind == kF32) {
+    scatter_acc_f32_kernel<float><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(inp), accs, ctrs, n,
+                                                                 nranks, start, scale, done_slot, vec_ok);
+  } else if (acc_kind == kF32 && in_kind == kBF16) {
+    scatter_acc_f32_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(inp), accs, ctrs, n, nranks, start, scale, done_slot, vec_ok);
+  } else if (acc_kind == kBF16 && in_kind == kBF16) {
+    scatter_acc_bf16_kernel<<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(inp), accs, ctrs, n,
+                                                          nranks, start, scale, done_slot);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_counter(const void* ctr, unsigned long long expected, unsigned long long budget_ns,
+                                int* status, cudaStream_t stream) {
+  wait_counter_kernel<<<1, 32, 0, stream>>>(static_cast<const unsigned long long*>(ctr), expected, budget_ns,
+                                            status);
+  return cudaGetLastError();
+}
+
+}  // namespace odc

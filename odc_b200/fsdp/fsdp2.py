@@ -66,6 +66,7 @@ class _GroupInfo:
     hpz_ranks: List[int] = field(default_factory=list)
     reduce_calls: int = 0
     divide: Dict[str, Any] = field(default_factory=dict)
+    replica_fresh: bool = False               # the optimizer already wrote the low-precision copy
 
     @property
     def acc_key(self) -> str:
@@ -341,8 +342,8 @@ def pre_minibatch_start(model) -> None:
     with nvtx_range("odc::pre_minibatch_start"):
         _S.reduction.clear_accumulations()
         for info in infos:
-            if info.replica is not None:
-                info.replica.copy_(info.master)
+            if info.replica is not None and not info.replica_fresh:
+                _copy_to_replica(info)
         _device_sync()
         control.host_barrier()
         hpz = [i for i in infos if i.hpz is not None]
@@ -351,6 +352,14 @@ def pre_minibatch_start(model) -> None:
                 _refresh_secondary_shards(info)
             _device_sync()
             control.host_barrier()
+
+
+def _copy_to_replica(info: _GroupInfo) -> None:
+    if info.master.is_cuda and info.master.dtype == torch.float32 and info.replica.dtype == torch.bfloat16:
+        from .. import _ext
+        _ext.load().cast_f32_to_bf16(info.master, info.replica)
+    else:
+        info.replica.copy_(info.master)
 
 
 def _refresh_secondary_shards(info: _GroupInfo) -> None:
@@ -365,14 +374,49 @@ def _refresh_secondary_shards(info: _GroupInfo) -> None:
 
 
 @torch.no_grad()
-def pre_optimizer_step(model) -> None:
-    """Wait for every contribution to this rank's shards and turn them into ``.grad`` (collective)."""
+def pre_optimizer_step(model, materialize_grads: bool = True) -> None:
+    """Wait for every contribution to this rank's shards and turn them into ``.grad`` (collective).
+
+    ``materialize_grads=False`` stops after the synchronisation (and the HSDP all-reduce): the
+    summed gradients stay in the accumulators, where :class:`FusedAdamW` consumes them directly.
+    """
     _require_patched()
     infos = _infos_of(model)
     _S.reduction.sync()
     for info in infos:
         with nvtx_range(f"odc::update_gradients:{info.group._module_fqn}"):
-            _update_gradients(info)
+            if materialize_grads:
+                _update_gradients(info)
+            else:
+                _reduce_replicas_in_place(info)
+    for info in infos:
+        info.replica_fresh = False
+
+
+def _divide_factor(info: _GroupInfo) -> float:
+    group = info.group
+    mesh_info = group.mesh_info
+    replicate_pg = mesh_info.replicate_process_group if isinstance(mesh_info, DDPMeshInfo) else None
+    dp = mesh_info.shard_mesh_size * (replicate_pg.size() if replicate_pg is not None else 1)
+    return group.gradient_divide_factor if group.gradient_divide_factor is not None else float(dp)
+
+
+def _reduce_replicas_in_place(info: _GroupInfo) -> None:
+    if info.acc_numel == 0:
+        return
+    mesh_info = info.group.mesh_info
+    if isinstance(mesh_info, DDPMeshInfo) and info.group.all_reduce_grads:
+        acc = _S.reduction.get_accumulation(info.acc_key)
+        dist.all_reduce(acc, group=mesh_info.replicate_process_group, op=dist.ReduceOp.SUM)
+
+
+def transport_launches() -> int:
+    """Kernels launched by the communication services so far (benchmark accounting)."""
+    n = 0
+    for svc in (_S.gather, _S.reduction):
+        if svc is not None:
+            n += getattr(svc.transport, "launches", 0)
+    return n
 
 
 def _update_gradients(info: _GroupInfo) -> None:
@@ -510,3 +554,91 @@ def get_symm_buffer_memory_breakdown() -> Dict[str, float]:
             out["other"] += gib
     out["total"] = sum(out.values())
     return out
+
+
+# ------------------------------------------------------------------------------------------
+# optimizer on the flat shards
+# ------------------------------------------------------------------------------------------
+class FusedAdamW:
+    """AdamW that runs once per parameter group directly on the flat symmetric shard.
+
+    The reference steps ``torch.optim.AdamW`` over DTensor shards that alias symmetric memory
+    (examples/llm_training/torch_fsdp2.py:322).  Here one kernel per group reads the summed
+    gradient straight from the accumulator (folding the divide factor and the clipping scale),
+    updates the fp32 master shard and moments, and writes the compute-precision copy that peers
+    gather, so no ``.grad`` tensor and no separate cast pass exist.  Use with
+    ``pre_optimizer_step(model, materialize_grads=False)``.
+    """
+
+    def __init__(self, model, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01):
+        self.model, self.lr, self.betas, self.eps, self.weight_decay = model, lr, betas, eps, weight_decay
+        self.step_count = 0
+        self.state: Dict[int, Dict[str, torch.Tensor]] = {}
+        self._clip_scale = 1.0
+
+    def _groups(self) -> List[_GroupInfo]:
+        infos = _infos_of(self.model)
+        for info in infos:
+            if len(info.trainable) != len(info.numels):
+                raise NotImplementedError("FusedAdamW needs every parameter of a group to be trainable")
+            if info.master.dtype != torch.float32:
+                raise NotImplementedError("FusedAdamW keeps fp32 master shards")
+        return infos
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float) -> torch.Tensor:
+        """Global L2 norm of the averaged gradient; the clipping scale is applied inside the next ``step``."""
+        infos = self._groups()
+        dev = infos[0].master.device
+        total = torch.zeros((), dtype=torch.float32, device=dev)
+        for info in infos:
+            acc = _S.reduction.get_accumulation(info.acc_key)
+            f = 1.0 / _divide_factor(info)
+            if acc.is_cuda:
+                from .. import _ext
+                part = torch.zeros((), dtype=torch.float32, device=dev)
+                _ext.load().sumsq(acc, part)
+                total += part * (f * f)
+            else:
+                total += (acc.float() * f).pow(2).sum()
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            # shards of one group are disjoint across its shard group; replicas hold identical sums
+            rep = 1
+            mi = infos[0].group.mesh_info
+            if isinstance(mi, DDPMeshInfo):
+                rep = mi.replicate_process_group.size()
+            dist.all_reduce(total)
+            total = total / rep
+        norm = total.sqrt()
+        self._clip_scale = float(min(1.0, max_norm / (float(norm) + 1e-6)))
+        return norm
+
+    @torch.no_grad()
+    def step(self) -> None:
+        from .. import ops
+        self.step_count += 1
+        for info in self._groups():
+            acc = _S.reduction.get_accumulation(info.acc_key)
+            st = self.state.get(info.index)
+            if st is None:
+                st = {"m": torch.zeros_like(info.master), "v": torch.zeros_like(info.master)}
+                self.state[info.index] = st
+            ops.fused_adamw_(info.master, acc, st["m"], st["v"], info.replica, self.lr, self.betas[0],
+                             self.betas[1], self.eps, self.weight_decay, self.step_count,
+                             self._clip_scale / _divide_factor(info))
+            info.replica_fresh = info.replica is not None
+        self._clip_scale = 1.0
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for p in self.model.parameters():
+            p.grad = None
+
+    def state_dict(self) -> Dict[str, Any]:
+        return {"step": self.step_count, "state": {k: {n: t.clone() for n, t in v.items()} for k, v in self.state.items()},
+                "hyper": dict(lr=self.lr, betas=self.betas, eps=self.eps, weight_decay=self.weight_decay)}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        self.step_count = sd["step"]
+        self.state = {k: {n: t.clone() for n, t in v.items()} for k, v in sd["state"].items()}
+        for k, v in sd.get("hyper", {}).items():
+            setattr(self, k, v)

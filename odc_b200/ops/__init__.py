@@ -269,7 +269,9 @@ def linear_cross_entropy(h, w, labels, loss_scale=None, ignore_index: int = -100
     """Summed (optionally per-token weighted) cross-entropy of ``h @ w.T`` against ``labels``."""
     if not h.is_cuda:
         return ref.linear_cross_entropy(h, w, labels, loss_scale, ignore_index, chunk)
-    return _LinearCrossEntropy.apply(h.contiguous(), w, labels, loss_scale, ignore_index, chunk)
+    if loss_scale is not None and loss_scale.dtype != torch.float32:
+        loss_scale = loss_scale.float()  # FSDP's mixed-precision input cast may have narrowed it
+    return _LinearCrossEntropy.apply(h.contiguous(), w, labels.contiguous(), loss_scale, ignore_index, chunk)
 
 
 # ------------------------------------------------------------------------------------------

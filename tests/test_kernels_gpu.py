@@ -1,0 +1,230 @@
+"""CUDA kernels against plain PyTorch fp32 references (single GPU; peers emulated by local buffers)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from odc_b200 import _ext
+    return _ext.load()
+
+
+def _table(tensors):
+    return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device="cuda")
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("n", [8, 1000, 4096 * 33 + 8, 1 << 20])
+@pytest.mark.parametrize("src,dst", [(torch.bfloat16, torch.bfloat16), (torch.float32, torch.float32),
+                                     (torch.float32, torch.bfloat16), (torch.int64, torch.int64)])
+def test_gather_emulated_ranks(ext, world, n, src, dst):
+    g = torch.Generator(device="cuda").manual_seed(n + world)
+    if src == torch.int64:
+        shards = [torch.randint(-2**40, 2**40, (n,), device="cuda", generator=g) for _ in range(world)]
+    else:
+        shards = [torch.randn(n, device="cuda", generator=g).to(src) for _ in range(world)]
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for me in range(world):
+        out = torch.empty(world, n, dtype=dst, device="cuda")
+        ext.gather(out, _table(shards), n, src, me, True, status)
+        want = torch.stack(shards).to(dst)
+        assert torch.equal(out, want)
+    assert int(status[0]) == 0
+
+
+def test_gather_unaligned_rows(ext):
+    world, n = 3, 1001  # 2002-byte rows: not a multiple of 16
+    shards = [torch.randn(n, device="cuda").bfloat16() for _ in range(world)]
+    out = torch.empty(world, n, dtype=torch.bfloat16, device="cuda")
+    ext.gather(out, _table(shards), n, torch.bfloat16, 1, False, torch.zeros(4, dtype=torch.int32, device="cuda"))
+    assert torch.equal(out, torch.stack(shards))
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("n", [4, 1000, 4096 * 9 + 4, 1 << 19, 1001])
+@pytest.mark.parametrize("in_dtype,acc_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                                (torch.bfloat16, torch.bfloat16)])
+def test_scatter_accumulate_emulated_ranks(ext, world, n, in_dtype, acc_dtype):
+    """Every emulated rank adds its [world, n] rows into the owners; sums are exactly representable."""
+    if n % 2 and acc_dtype == torch.bfloat16 and world > 1:
+        pytest.skip("odd bf16 rows use the scalar path tested with world 1")
+    g = torch.Generator(device="cuda").manual_seed(7)
+    accs = [torch.zeros(n, dtype=acc_dtype, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    inputs = [torch.randint(-4, 5, (world, n), device="cuda", generator=g).to(in_dtype) for _ in range(world)]
+    for rounds in range(2):
+        for me in range(world):
+            ext.scatter_accumulate(inputs[me], _table(accs), _table(ctrs), n, acc_dtype, me, 1.0, True, status)
+    want = 2 * torch.stack(inputs).float().sum(0)  # [world, n]: row p belongs to owner p
+    for p in range(world):
+        assert torch.equal(accs[p].float(), want[p]), (p, (accs[p].float() - want[p]).abs().max())
+        assert int(ctrs[p][0]) == 2 * world
+    # the arrival wait succeeds at the dispatched count ...
+    ext.wait_counter(ctrs[0], 2 * world, 1000, status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0
+    # ... and a count that nothing will ever deliver runs out of budget and reports, instead of hanging
+    ext.wait_counter(ctrs[0], 2 * world + 1, 50, status)
+    torch.cuda.synchronize()
+    assert status[:3].tolist() == [1, 0, 2 * world]
+    from odc_b200.runtime.status import OdcTimeoutError, check_status_word
+    with pytest.raises(OdcTimeoutError):
+        check_status_word(*status[:3].tolist())
+
+
+def test_scatter_accumulate_scale(ext):
+    n, world = 4096, 4
+    accs = [torch.zeros(n, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    x = torch.randint(-8, 8, (world, n), device="cuda").float()
+    ext.scatter_accumulate(x, _table(accs), _table(ctrs), n, torch.float32, 0, 0.25, False,
+                           torch.zeros(4, dtype=torch.int32, device="cuda"))
+    assert torch.equal(torch.stack(accs), x * 0.25)
+
+
+# ------------------------------------------------------------------------------------ elementwise
+@pytest.mark.parametrize("rows,cols", [(1, 256), (333, 2048), (4096, 5120), (17, 8192)])
+def test_rmsnorm(rows, cols):
+    from odc_b200 import ops
+    from odc_b200.ops import reference as ref
+    x = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).bfloat16().requires_grad_()
+    y = ops.rms_norm(x, w, 1e-5)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = ref.rms_norm(xr, wr, 1e-5)
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=2e-2 * math.sqrt(rows))
+
+
+@pytest.mark.parametrize("nq,nkv,d", [(4, 4, 64), (32, 8, 64), (40, 8, 128)])
+def test_rope(nq, nkv, d):
+    from odc_b200 import ops
+    from odc_b200.ops import reference as ref
+    T = 257
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device="cuda").bfloat16().requires_grad_()
+    pos = torch.randint(0, 30000, (T,), device="cuda")
+    out = ops.rope_qkv(qkv, pos, nq, nkv, d, 500000.0)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    x = qkv.detach().float().cpu().requires_grad_()
+    q, k, v = x.split([nq * d, nkv * d, nkv * d], dim=-1)
+    want = torch.cat([ref.rope(q.reshape(T, nq, d), pos.cpu(), 500000.0).reshape(T, -1),
+                      ref.rope(k.reshape(T, nkv, d), pos.cpu(), 500000.0).reshape(T, -1), v], dim=-1)
+    want.backward(dout.float().cpu())
+    torch.testing.assert_close(out.float().cpu(), want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(qkv.grad.float().cpu(), x.grad, rtol=2e-2, atol=2e-2)
+
+
+def test_swiglu():
+    from odc_b200 import ops
+    from odc_b200.ops import reference as ref
+    gu = torch.randn(513, 2 * 1376, device="cuda").bfloat16().requires_grad_()
+    y = ops.swiglu(gu)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    g = gu.detach().float().requires_grad_()
+    yr = ref.swiglu(g)
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(gu.grad.float(), g.grad, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("T,V", [(100, 1024), (300, 128256)])
+def test_ce_fwd_bwd(ext, T, V):
+    logits = (3 * torch.randn(T, V, device="cuda")).bfloat16()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[5] = -100
+    scale = torch.rand(T, device="cuda")
+    lf = logits.float().requires_grad_()
+    keep = labels != -100
+    want = (torch.nn.functional.cross_entropy(lf, labels, reduction="none", ignore_index=-100) * scale).sum()
+    want.backward()
+    loss = torch.zeros((), device="cuda")
+    ext.ce_fwd_bwd(logits, labels, scale, loss, -100)
+    torch.testing.assert_close(loss, want.detach(), rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(logits.float(), lf.grad, rtol=2e-2, atol=1e-4)
+    assert float(logits[~keep].abs().sum()) == 0.0
+
+
+def test_adamw_matches_torch(ext):
+    n = 100003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v, low = torch.zeros_like(p), torch.zeros_like(p), torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    for step in range(1, 4):
+        ref_p.grad = g * step
+        opt.step()
+        ext.adamw_step(p, g * step, m, v, low, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 1.0)
+    torch.testing.assert_close(p, ref_p.detach(), rtol=1e-5, atol=1e-6)
+    assert torch.equal(low, p.bfloat16())
+
+
+# ------------------------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 1376, 200), (1000, 264, 1032),
+                                   (4096, 2048, 4096)])
+def test_gemm_layouts(ext, layout, M, N, K):
+    K = (K + 7) // 8 * 8 if layout != "tn" else K
+    M = (M + 7) // 8 * 8 if layout == "tn" else M
+    torch.manual_seed(M + N + K)
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = torch.randn(K, N, device="cuda").bfloat16()
+    want = A.float() @ B.float()
+    a = A.t().contiguous() if layout == "tn" else A
+    b = B.t().contiguous() if layout == "nt" else B
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ext.gemm(a, b, c, layout, None, False)
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0
+    torch.testing.assert_close(c.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    # fp32 output with accumulation and bias
+    bias = torch.randn(N, device="cuda").bfloat16()
+    c32 = torch.ones(M, N, device="cuda")
+    ext.gemm(a, b, c32, layout, bias, True)
+    torch.testing.assert_close(c32, want + 1 + bias.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
+
+
+def test_linear_autograd_matches_reference():
+    from odc_b200 import ops
+    x = torch.randn(3, 100, 512, device="cuda").bfloat16().requires_grad_()
+    w = (0.05 * torch.randn(768, 512, device="cuda")).bfloat16().requires_grad_()
+    b = torch.randn(768, device="cuda").bfloat16().requires_grad_()
+    y = ops.linear(x, w, b)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, rtol=2e-2, atol=5e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=2e-2, atol=5e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=2e-2, atol=0.5)
+    torch.testing.assert_close(b.grad.float(), br.grad, rtol=2e-2, atol=0.5)
+
+
+def test_linear_cross_entropy_matches_reference():
+    from odc_b200 import ops
+    from odc_b200.ops import reference as ref
+    T, H, V = 700, 256, 1024
+    h = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    w = (0.05 * torch.randn(V, H, device="cuda")).bfloat16().requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    scale = torch.rand(T, device="cuda") / T
+    loss = ops.linear_cross_entropy(h, w, labels, scale, chunk=256)
+    (loss * 2.0).backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr_ = ref.linear_cross_entropy(hr, wr, labels, scale)
+    (lr_ * 2.0).backward()
+    torch.testing.assert_close(loss, lr_.detach(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(h.grad.float(), hr.grad, rtol=5e-2, atol=2e-4)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=5e-2, atol=2e-4)
