@@ -280,6 +280,27 @@ void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional
         "gemm");
 }
 
+std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, bool causal,
+                                    double scale) {
+  c10::cuda::CUDAGuard g(q.device());
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "attention: q/k/v are [T, H, D]");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16,
+              "attention: bf16 inputs");
+  const int T = q.size(0), hq = q.size(1), d = q.size(2), hkv = k.size(1);
+  TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == d && k.stride(2) == 1 && k.stride(1) == d && v.stride(2) == 1 &&
+                  v.stride(1) == d, "attention: heads must be packed within a token");
+  TORCH_CHECK(k.stride(0) == v.stride(0), "attention: k and v must share a row stride");
+  TORCH_CHECK(cu_seqlens.scalar_type() == at::kInt && cu_seqlens.is_contiguous(), "attention: cu_seqlens int32");
+  auto o = torch::empty({T, hq, d}, q.options());
+  auto lse = torch::empty({hq, T}, q.options().dtype(at::kFloat));
+  check(odc::attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
+                      cu_seqlens.data_ptr<int>(), static_cast<int>(cu_seqlens.numel() - 1), T, max_seqlen, hq, hkv, d,
+                      q.stride(0), k.stride(0), o.stride(0), static_cast<float>(scale), causal,
+                      gemm_status(q.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+        "attn_fwd");
+  return {o, lse};
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -306,6 +327,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm);
+  m.def("attn_fwd", &attn_fwd);
   m.def("kernel_status", &kernel_status);
   m.def("sm_count", &sm_count);
 }

@@ -1,0 +1,407 @@
+// Causal attention over packed variable-length sequences on tcgen05 tensor cores (sm_100a).
+//
+// Forward: one CTA per (128 query rows of one sequence, query head).
+//   warp 0     TMA producer: Q tile once, then K/V tiles of 128 keys through a small ring
+//   warp 1     MMA issuer:   S = Q K^T into one of two TMEM buffers, then O += P V
+//   warps 2-5  softmax:      one query row per thread; S from TMEM, online softmax in base 2 with
+//                            lazy rescaling of O (only when a row maximum grows by more than 2^8),
+//                            P written to shared memory as a 128-byte-swizzled bf16 operand
+// S(j+1) is issued before P(j) is consumed, so the tensor core computes the next score tile while
+// the softmax warps work on the current one.  K and V tiles share one TMA box shape: K is read as
+// a K-major operand (Q K^T) and V as an N-major operand (P V), so nothing is transposed in memory.
+// Rows/keys outside the sequence are masked; grouped-query attention maps query head h to
+// key/value head h / (Hq/Hkv).
+//
+// Backward: a pre-pass computes delta = rowsum(dO * O); the main kernel owns one (128 keys, kv
+// head) tile, keeps dK and dV in TMEM across all query tiles and query heads of the group, and
+// recomputes P from the saved log-sum-exp.  dQ tiles are reduced into an fp32 buffer with vector
+// atomics and converted to bf16 by a post-pass.
+//
+// The reference calls flash-attn 2 for this op (examples/llm_training/torch_fsdp2.py:85-103).
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <mutex>
+
+#include "api.h"
+#include "sm100_ptx.cuh"
+#include "tensor_map.h"
+
+namespace odc {
+
+using namespace sm100;
+
+namespace {
+
+constexpr int kBlockQ = 128, kBlockKV = 128;
+constexpr uint64_t kWaitBudgetNs = 4000000000ull;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// byte offset of element (row, col) inside a [128 rows][128 cols] bf16 operand stored as two
+// 128-byte-swizzled slabs of 64 columns (the layout TMA produces and the K-major descriptor reads)
+__device__ __forceinline__ uint32_t swz_chunk_offset(int row, int chunk16 /*0..15*/) {
+  const int slab = chunk16 >> 3, ch = chunk16 & 7;
+  return slab * 16384 + row * 128 + ((ch ^ (row & 7)) << 4);
+}
+
+struct FwdParams {
+  const int* cu_seqlens;
+  int num_seqs;
+  int n_q, n_kv;
+  __nv_bfloat16* o;
+  long long o_stride;
+  float* lse;  // [n_q, total_tokens]
+  int total_tokens;
+  float scale_log2;
+  int causal;
+  int* status;
+};
+
+// find (sequence, query block) of a linear block index; returns false if out of range
+__device__ __forceinline__ bool locate_block(const int* cu, int num_seqs, int blk, int block_rows, int* seq,
+                                             int* start, int* len, int* q0) {
+  int acc = 0;
+  for (int s = 0; s < num_seqs; ++s) {
+    const int b = cu[s], e = cu[s + 1];
+    const int nb = (e - b + block_rows - 1) / block_rows;
+    if (blk < acc + nb) {
+      *seq = s; *start = b; *len = e - b; *q0 = (blk - acc) * block_rows;
+      return true;
+    }
+    acc += nb;
+  }
+  return false;
+}
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kStages = (D == 64) ? 3 : 2;
+  static constexpr int kQBytes = kBlockQ * D * 2;
+  static constexpr int kKBytes = kBlockKV * D * 2;
+  static constexpr int kStageBytes = 2 * kKBytes;
+  static constexpr int kPBytes = kBlockQ * kBlockKV * 2;
+  static constexpr int kSmem = kQBytes + kStages * kStageBytes + kPBytes + 1024 + 256;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
+  using C = FwdCfg<D>;
+  int seq, seq_start, seq_len, q0;
+  if (!locate_block(p.cu_seqlens, p.num_seqs, blockIdx.x, kBlockQ, &seq, &seq_start, &seq_len, &q0)) return;
+  const int head = blockIdx.y;
+  const int kv_head = head / (p.n_q / p.n_kv);
+  const int kv_end = p.causal ? min(seq_len, q0 + kBlockQ) : seq_len;
+  const int n_blocks = (kv_end + kBlockKV - 1) / kBlockKV;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t q_smem = base;
+  const uint32_t kv_smem = q_smem + C::kQBytes;
+  const uint32_t p_smem = kv_smem + C::kStages * C::kStageBytes;
+  uint8_t* p_ptr = smem + C::kQBytes + C::kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_ptr + C::kPBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0;
+  const uint32_t kv_full0 = bar0 + 8;                      // [kStages]
+  const uint32_t kv_empty0 = kv_full0 + 8 * C::kStages;    // [kStages]
+  const uint32_t s_full0 = kv_empty0 + 8 * C::kStages;     // [2]
+  const uint32_t s_empty0 = s_full0 + 16;                  // [2]
+  const uint32_t p_full = s_empty0 + 16;
+  const uint32_t p_empty = p_full + 8;
+  const uint32_t o_ready = p_empty + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitCtx wc{abort_flag, p.status, kWaitBudgetNs};
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(kv_full0 + 8 * s, 1);
+      mbar_init(kv_empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(s_full0 + 8 * b, 1);
+      mbar_init(s_empty0 + 8 * b, 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(p_empty, 1);
+    mbar_init(o_ready, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_arrive_expect_tx(q_full, C::kQBytes);
+#pragma unroll
+      for (int s = 0; s < D / 64; ++s) tma_load_2d(q_smem + s * 16384, &tmap_q, q_full, head * D + 64 * s, seq_start + q0);
+      bool ok = true;
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        const int st = j % C::kStages;
+        const uint32_t ph = (j / C::kStages) & 1;
+        if (!(ok = mbar_wait(kv_empty0 + 8 * st, ph ^ 1, wc, 11))) break;
+        const uint32_t bar = kv_full0 + 8 * st;
+        mbar_arrive_expect_tx(bar, C::kStageBytes);
+        const uint32_t k_dst = kv_smem + st * C::kStageBytes, v_dst = k_dst + C::kKBytes;
+        const int row = seq_start + j * kBlockKV;
+#pragma unroll
+        for (int s = 0; s < D / 64; ++s) {
+          tma_load_2d(k_dst + s * 16384, &tmap_k, bar, kv_head * D + 64 * s, row);
+          tma_load_2d(v_dst + s * 16384, &tmap_v, bar, kv_head * D + 64 * s, row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(kBlockQ, kBlockKV, false, false);
+      const uint32_t idesc_o = make_idesc_bf16(kBlockQ, D, false, true);
+      bool ok = mbar_wait(q_full, 0, wc, 12);
+      auto issue_s = [&](int j) {
+        const int st = j % C::kStages;
+        const uint32_t k_src = kv_smem + st * C::kStageBytes;
+        const uint32_t d = tmem_s0 + (j & 1) * 128;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_f16(d, make_smem_desc(q_smem + off, 16, 1024), make_smem_desc(k_src + off, 16, 1024), idesc_s,
+                   k > 0 ? 1u : 0u);
+        }
+        umma_commit(s_full0 + 8 * (j & 1));
+      };
+      if (ok && n_blocks > 0) {
+        ok = mbar_wait(kv_full0, 0, wc, 13);
+        if (ok) { tc_fence_after(); issue_s(0); }
+      }
+      for (int j = 0; j < n_blocks && ok; ++j) {
+        if (j + 1 < n_blocks) {
+          const int st1 = (j + 1) % C::kStages;
+          if (!(ok = mbar_wait(kv_full0 + 8 * st1, ((j + 1) / C::kStages) & 1, wc, 14))) break;
+          if (j + 1 >= 2) {  // S buffer (j+1)&1 was last read by the softmax of block j-1
+            if (!(ok = mbar_wait(s_empty0 + 8 * ((j + 1) & 1), (((j + 1) >> 1) - 1) & 1, wc, 15))) break;
+          }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!(ok = mbar_wait(p_full, j & 1, wc, 16))) break;
+        tc_fence_after();
+        const int st = j % C::kStages;
+        const uint32_t v_src = kv_smem + st * C::kStageBytes + C::kKBytes;
+#pragma unroll
+        for (int k = 0; k < kBlockKV / 16; ++k) {
+          const uint64_t da = make_smem_desc(p_smem + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc(v_src + k * 2048, 16384, 1024);
+          umma_f16(tmem_o, da, db, idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(kv_empty0 + 8 * st);
+        umma_commit(p_empty);
+        umma_commit(o_ready);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;            // query row within the tile
+    const int q_rel = q0 + row;                  // position inside the sequence
+    const bool row_valid = q_rel < seq_len;
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_blocks && ok; ++j) {
+      if (!(ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, wc, 17))) break;
+      tc_fence_after();
+      const uint32_t t_s = tmem_s0 + (j & 1) * 128 + lane_sel;
+      const int kv0 = j * kBlockKV;
+      const bool need_mask = (kv0 + kBlockKV > seq_len) || (p.causal && kv0 + kBlockKV > q0);
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_s + c * 32, r);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kv = kv0 + c * 32 + i;
+            const bool okk = kv < seq_len && (!p.causal || kv <= q_rel);
+            mx = fmaxf(mx, okk ? __uint_as_float(r[i]) : -INFINITY);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      const float m_new = fmaxf(m_used, mx * p.scale_log2);
+      // lazy rescale of the running output (exact: P and l keep using m_used until it is bumped)
+      const bool bump = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_new > -INFINITY);
+      if (j == 0) {
+        m_used = m_new;
+      } else if (__any_sync(0xffffffffu, bump)) {
+        if (!(ok = mbar_wait(o_ready, (j - 1) & 1, wc, 18))) break;
+        tc_fence_after();
+        const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_used - m_new);
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + lane_sel + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st_32x16(tmem_o + lane_sel + c * 32, r);
+          tmem_st_32x16(tmem_o + lane_sel + c * 32 + 16, r + 16);
+        }
+        tmem_st_wait();
+        l *= alpha;
+        m_used = m_new;
+      }
+      // P may be overwritten once the previous P V has finished reading it
+      if (j > 0) {
+        if (!(ok = mbar_wait(p_empty, (j - 1) & 1, wc, 19))) break;
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_s + c * 32, r);
+        tmem_ld_wait();
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(r[i]) * p.scale_log2 - m_sub;
+          if (need_mask) {
+            const int kv = kv0 + c * 32 + i;
+            const bool okk = kv < seq_len && (!p.causal || kv <= q_rel);
+            s = okk ? s : -INFINITY;
+          }
+          f[i] = exp2f(s);
+          sum += f[i];
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 o;
+          o.x = pack2(f[8 * v], f[8 * v + 1]);
+          o.y = pack2(f[8 * v + 2], f[8 * v + 3]);
+          o.z = pack2(f[8 * v + 4], f[8 * v + 5]);
+          o.w = pack2(f[8 * v + 6], f[8 * v + 7]);
+          *reinterpret_cast<uint4*>(p_ptr + swz_chunk_offset(row, c * 4 + v)) = o;
+        }
+      }
+      l += sum;
+      // S buffer free for block j+2; P visible to the tensor core (async proxy)
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(s_empty0 + 8 * (j & 1));
+        mbar_arrive(p_full);
+      }
+    }
+    // epilogue: O / l -> bf16, log-sum-exp
+    if (ok && n_blocks > 0) ok = mbar_wait(o_ready, (n_blocks - 1) & 1, wc, 20);
+    if (ok) {
+      tc_fence_after();
+      const float inv = (l > 0.f) ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.o + static_cast<long long>(seq_start + q_rel) * p.o_stride + head * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        if (n_blocks > 0) {
+          tmem_ld_32x32(tmem_o + lane_sel + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0;
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack2(__uint_as_float(r[8 * v]) * inv, __uint_as_float(r[8 * v + 1]) * inv);
+            o.y = pack2(__uint_as_float(r[8 * v + 2]) * inv, __uint_as_float(r[8 * v + 3]) * inv);
+            o.z = pack2(__uint_as_float(r[8 * v + 4]) * inv, __uint_as_float(r[8 * v + 5]) * inv);
+            o.w = pack2(__uint_as_float(r[8 * v + 6]) * inv, __uint_as_float(r[8 * v + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = o;
+          }
+        }
+      }
+      if (row_valid)
+        p.lse[static_cast<long long>(head) * p.total_tokens + seq_start + q_rel] =
+            (l > 0.f) ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace
+
+cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
+                     int num_seqs, int total_tokens, int max_seqlen, int n_q, int n_kv, int head_dim,
+                     long long q_stride, long long kv_stride, long long o_stride, float scale, bool causal,
+                     int* status, int sm_count, cudaStream_t stream) {
+  (void)max_seqlen;
+  (void)sm_count;
+  if (total_tokens == 0 || num_seqs == 0) return cudaSuccess;
+  if (head_dim != 64 && head_dim != 128) return cudaErrorInvalidValue;
+  if (n_q % n_kv != 0) return cudaErrorInvalidValue;
+  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8)) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(o)) & 15)
+    return cudaErrorMisalignedAddress;
+  CUtensorMap tq, tk, tv;
+  if (!encode_tile_map_2d(&tq, q, static_cast<uint64_t>(n_q) * head_dim, total_tokens, q_stride * 2, 64, kBlockQ) ||
+      !encode_tile_map_2d(&tk, k, static_cast<uint64_t>(n_kv) * head_dim, total_tokens, kv_stride * 2, 64, kBlockKV) ||
+      !encode_tile_map_2d(&tv, v, static_cast<uint64_t>(n_kv) * head_dim, total_tokens, kv_stride * 2, 64, kBlockKV))
+    return cudaErrorInvalidValue;
+  FwdParams p;
+  p.cu_seqlens = cu_seqlens; p.num_seqs = num_seqs; p.n_q = n_q; p.n_kv = n_kv;
+  p.o = static_cast<__nv_bfloat16*>(o); p.o_stride = o_stride; p.lse = lse; p.total_tokens = total_tokens;
+  p.scale_log2 = scale * kLog2e; p.causal = causal ? 1 : 0; p.status = status;
+  const int blocks = (total_tokens + kBlockQ - 1) / kBlockQ + num_seqs;
+  dim3 grid(blocks, n_q);
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FwdCfg<64>::kSmem);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      FwdCfg<128>::kSmem);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  if (head_dim == 64)
+    attn_fwd_kernel<64><<<grid, 192, FwdCfg<64>::kSmem, stream>>>(tq, tk, tv, p);
+  else
+    attn_fwd_kernel<128><<<grid, 192, FwdCfg<128>::kSmem, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace odc

@@ -1,0 +1,37 @@
+"""Varlen causal attention kernels against the fp32 PyTorch statement of the op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(lens, hq, hkv, d, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    T = sum(lens)
+    width = (hq + 2 * hkv) * d
+    qkv = torch.randn(T, width, device="cuda", generator=g).bfloat16()
+    q = qkv[:, : hq * d].view(T, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].view(T, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].view(T, hkv, d)
+    cu = torch.tensor([0] + lens, device="cuda").cumsum(0).int()
+    return q, k, v, cu
+
+
+@pytest.mark.parametrize("lens,hq,hkv,d", [([128], 1, 1, 64), ([256], 2, 1, 64), ([100, 29, 300], 4, 2, 64),
+                                           ([128], 1, 1, 128), ([513, 7, 1000, 128], 8, 2, 128),
+                                           ([2048, 77], 4, 4, 64)])
+def test_attention_forward(lens, hq, hkv, d):
+    from odc_b200 import _ext
+    from odc_b200.ops import reference as ref
+    ext = _ext.load()
+    q, k, v, cu = _case(lens, hq, hkv, d)
+    o, lse = ext.attn_fwd(q, k, v, cu, max(lens), True, d ** -0.5)
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
+    want = ref.varlen_attention(q.float(), k.float(), v.float(), cu.cpu(), True, d ** -0.5)
+    torch.testing.assert_close(o.float(), want, rtol=2e-2, atol=2e-2)
+    # log-sum-exp of the first sequence, first head
+    L = lens[0]
+    s = (q[:L, 0].float() @ k[:L, 0].float().t()) * d ** -0.5
+    s = s.masked_fill(~torch.ones(L, L, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+    torch.testing.assert_close(lse[0, :L], torch.logsumexp(s, -1), rtol=1e-2, atol=1e-2)
