@@ -301,6 +301,28 @@ std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seql
   return {o, lse};
 }
 
+std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse,
+                                            Tensor cu_seqlens, int max_seqlen, bool causal, double scale) {
+  c10::cuda::CUDAGuard g(q.device());
+  const int T = q.size(0), hq = q.size(1), d = q.size(2), hkv = k.size(1);
+  TORCH_CHECK(dout.is_contiguous() && dout.scalar_type() == at::kBFloat16, "attention bwd: dout contiguous bf16");
+  TORCH_CHECK(o.stride(2) == 1 && o.stride(1) == d, "attention bwd: o heads packed");
+  TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == d && k.stride(2) == 1 && k.stride(1) == d && v.stride(2) == 1 &&
+                  v.stride(1) == d && k.stride(0) == v.stride(0), "attention bwd: q/k/v layout");
+  auto dq = torch::empty({T, hq, d}, q.options());
+  auto dk = torch::empty({T, hkv, d}, q.options());
+  auto dv = torch::empty({T, hkv, d}, q.options());
+  auto delta = torch::empty({hq, T}, q.options().dtype(at::kFloat));
+  auto dq_acc = torch::empty({T, hq, d}, q.options().dtype(at::kFloat));
+  check(odc::attn_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
+                      dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
+                      cu_seqlens.data_ptr<int>(), static_cast<int>(cu_seqlens.numel() - 1), T, max_seqlen, hq, hkv, d,
+                      q.stride(0), k.stride(0), o.stride(0), static_cast<float>(scale), causal,
+                      gemm_status(q.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+        "attn_bwd");
+  return {dq, dk, dv};
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -328,6 +350,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm);
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
   m.def("kernel_status", &kernel_status);
   m.def("sm_count", &sm_count);
 }

@@ -362,6 +362,323 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
+
+// =================================================================================== backward
+struct BwdParams {
+  const int* cu_seqlens;
+  int num_seqs;
+  int n_q, n_kv;
+  const float* lse;    // [n_q, total_tokens]
+  const float* delta;  // [n_q, total_tokens]
+  float* dq_acc;       // [total_tokens, n_q, D] fp32, zero-initialised
+  __nv_bfloat16* dk;   // [total_tokens, n_kv, D]
+  __nv_bfloat16* dv;
+  int total_tokens;
+  float scale, scale_log2;
+  int causal;
+  int* status;
+};
+
+template <int D>
+struct BwdCfg {
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kTile = 128 * D * 2;            // one [128][D] bf16 operand
+  static constexpr int kStageBytes = 2 * kTile;        // Q_i and dO_i
+  static constexpr int kPBytes = 128 * 128 * 2;
+  static constexpr int kSmem = 2 * kTile + kStages * kStageBytes + 2 * kPBytes + 1024 + 256;
+};
+
+__device__ __forceinline__ void red_add_v4_gpu(float* p, float a, float b, float c, float d) {
+  asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                const BwdParams p) {
+  using C = BwdCfg<D>;
+  int seq, seq_start, seq_len, kv0;
+  if (!locate_block(p.cu_seqlens, p.num_seqs, blockIdx.x, 128, &seq, &seq_start, &seq_len, &kv0)) return;
+  const int kv_head = blockIdx.y;
+  const int rep = p.n_q / p.n_kv;
+  const int n_qblocks = (seq_len + 127) / 128;
+  const int i_first = p.causal ? kv0 / 128 : 0;
+  const int iters_per_head = n_qblocks - i_first;
+  const int total_iters = iters_per_head * rep;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  const uint32_t k_smem = base, v_smem = base + C::kTile;
+  const uint32_t ring = v_smem + C::kTile;
+  const uint32_t p_smem = ring + C::kStages * C::kStageBytes;
+  const uint32_t ds_smem = p_smem + C::kPBytes;
+  uint8_t* p_ptr = smem + 2 * C::kTile + C::kStages * C::kStageBytes;
+  uint8_t* ds_ptr = p_ptr + C::kPBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + C::kPBytes);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t kv_full = bar0;
+  const uint32_t qdo_full0 = bar0 + 8;                      // [kStages]
+  const uint32_t qdo_empty0 = qdo_full0 + 8 * C::kStages;   // [kStages]
+  const uint32_t sdp_full = qdo_empty0 + 8 * C::kStages;
+  const uint32_t pds_full = sdp_full + 8;
+  const uint32_t dq_full = pds_full + 8;
+  const uint32_t dq_read = dq_full + 8;
+  const uint32_t dkv_full = dq_read + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WaitCtx wc{abort_flag, p.status, kWaitBudgetNs};
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < C::kStages; ++s) {
+      mbar_init(qdo_full0 + 8 * s, 1);
+      mbar_init(qdo_empty0 + 8 * s, 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_read, 4);
+    mbar_init(dkv_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 256 + D;
+  const uint32_t tm_dq = tm_s;  // dQ_i reuses the score columns once the scores have been consumed
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
+      mbar_arrive_expect_tx(kv_full, 2 * C::kTile);
+#pragma unroll
+      for (int s = 0; s < D / 64; ++s) {
+        tma_load_2d(k_smem + s * 16384, &tmap_k, kv_full, kv_head * D + 64 * s, seq_start + kv0);
+        tma_load_2d(v_smem + s * 16384, &tmap_v, kv_full, kv_head * D + 64 * s, seq_start + kv0);
+      }
+      bool ok = true;
+      for (int it = 0; it < total_iters && ok; ++it) {
+        const int head = kv_head * rep + it / iters_per_head;
+        const int i = i_first + it % iters_per_head;
+        const int st = it % C::kStages;
+        if (!(ok = mbar_wait(qdo_empty0 + 8 * st, ((it / C::kStages) & 1) ^ 1, wc, 31))) break;
+        const uint32_t bar = qdo_full0 + 8 * st;
+        mbar_arrive_expect_tx(bar, C::kStageBytes);
+        const uint32_t q_dst = ring + st * C::kStageBytes, do_dst = q_dst + C::kTile;
+        const int row = seq_start + i * 128;
+#pragma unroll
+        for (int s = 0; s < D / 64; ++s) {
+          tma_load_2d(q_dst + s * 16384, &tmap_q, bar, head * D + 64 * s, row);
+          tma_load_2d(do_dst + s * 16384, &tmap_do, bar, head * D + 64 * s, row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // S, dP: both operands K-major
+      const uint32_t idesc_tt = make_idesc_bf16(128, D, true, true);      // dV, dK: A^T (MN-major) x MN-major
+      const uint32_t idesc_dq = make_idesc_bf16(128, D, false, true);     // dQ: K-major x MN-major
+      bool ok = mbar_wait(kv_full, 0, wc, 32);
+      for (int it = 0; it < total_iters && ok; ++it) {
+        const int st = it % C::kStages;
+        const uint32_t q_src = ring + st * C::kStageBytes, do_src = q_src + C::kTile;
+        if (!(ok = mbar_wait(qdo_full0 + 8 * st, (it / C::kStages) & 1, wc, 33))) break;
+        if (it > 0) {  // the score columns still hold dQ of the previous tile until it has been read out
+          if (!(ok = mbar_wait(dq_read, (it - 1) & 1, wc, 34))) break;
+        }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_f16(tm_s, make_smem_desc(q_src + off, 16, 1024), make_smem_desc(k_smem + off, 16, 1024), idesc_s,
+                   k > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+          umma_f16(tm_dp, make_smem_desc(do_src + off, 16, 1024), make_smem_desc(v_smem + off, 16, 1024), idesc_s,
+                   k > 0 ? 1u : 0u);
+        }
+        umma_commit(sdp_full);
+        if (!(ok = mbar_wait(pds_full, it & 1, wc, 35))) break;
+        tc_fence_after();
+        // dV += P^T dO ; dK += dS^T Q   (reduction over the 128 query rows, 16 at a time)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          umma_f16(tm_dv, make_smem_desc(p_smem + k * 2048, 16384, 1024), make_smem_desc(do_src + k * 2048, 16384, 1024),
+                   idesc_tt, (it > 0 || k > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          umma_f16(tm_dk, make_smem_desc(ds_smem + k * 2048, 16384, 1024), make_smem_desc(q_src + k * 2048, 16384, 1024),
+                   idesc_tt, (it > 0 || k > 0) ? 1u : 0u);
+        }
+        // dQ_i = dS K   (reduction over the 128 keys)
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          umma_f16(tm_dq, make_smem_desc(ds_smem + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
+                   make_smem_desc(k_smem + k * 2048, 16384, 1024), idesc_dq, k > 0 ? 1u : 0u);
+        }
+        umma_commit(qdo_empty0 + 8 * st);
+        umma_commit(dq_full);
+      }
+      if (ok) umma_commit(dkv_full);
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < total_iters && ok; ++it) {
+      const int head = kv_head * rep + it / iters_per_head;
+      const int i = i_first + it % iters_per_head;
+      const int q_rel = i * 128 + row;
+      const bool q_valid = q_rel < seq_len;
+      const long long tok = seq_start + q_rel;
+      const float lse2 = q_valid ? p.lse[static_cast<long long>(head) * p.total_tokens + tok] * kLog2e : 0.f;
+      const float dlt = q_valid ? p.delta[static_cast<long long>(head) * p.total_tokens + tok] : 0.f;
+      if (!(ok = mbar_wait(sdp_full, it & 1, wc, 36))) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(tm_s + lane_sel + c * 32, rs);
+        tmem_ld_32x32(tm_dp + lane_sel + c * 32, rd);
+        tmem_ld_wait();
+        float pf[32], df[32];
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const int kv = kv0 + c * 32 + x;
+          const bool okk = q_valid && kv < seq_len && (!p.causal || kv <= q_rel);
+          const float pv = okk ? exp2f(__uint_as_float(rs[x]) * p.scale_log2 - lse2) : 0.f;
+          pf[x] = pv;
+          df[x] = pv * (__uint_as_float(rd[x]) - dlt) * p.scale;
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          uint4 a, b;
+          a.x = pack2(pf[8 * v], pf[8 * v + 1]); a.y = pack2(pf[8 * v + 2], pf[8 * v + 3]);
+          a.z = pack2(pf[8 * v + 4], pf[8 * v + 5]); a.w = pack2(pf[8 * v + 6], pf[8 * v + 7]);
+          b.x = pack2(df[8 * v], df[8 * v + 1]); b.y = pack2(df[8 * v + 2], df[8 * v + 3]);
+          b.z = pack2(df[8 * v + 4], df[8 * v + 5]); b.w = pack2(df[8 * v + 6], df[8 * v + 7]);
+          const uint32_t off = swz_chunk_offset(row, c * 4 + v);
+          *reinterpret_cast<uint4*>(p_ptr + off) = a;
+          *reinterpret_cast<uint4*>(ds_ptr + off) = b;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      // dQ tile -> global accumulator
+      if (!(ok = mbar_wait(dq_full, it & 1, wc, 37))) break;
+      tc_fence_after();
+      float* dq_row = p.dq_acc + (tok * p.n_q + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tm_dq + lane_sel + c * 32, r);
+        tmem_ld_wait();
+        if (q_valid) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            red_add_v4_gpu(dq_row + c * 32 + 4 * v, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                           __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_read);
+    }
+    // dK / dV of this key tile
+    if (ok) ok = mbar_wait(dkv_full, 0, wc, 38);
+    if (ok) {
+      tc_fence_after();
+      const int kv_rel = kv0 + row;
+      const bool kv_valid = kv_rel < seq_len;
+      const long long off = (static_cast<long long>(seq_start + kv_rel) * p.n_kv + kv_head) * D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + off;
+        const uint32_t src = (which == 0 ? tm_dv : tm_dk) + lane_sel;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          if (total_iters > 0) {
+            tmem_ld_32x32(src + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) r[x] = 0;
+          }
+          if (kv_valid) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+              o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head)
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ o, float* __restrict__ delta,
+                  int total_tokens, int n_q, int d, long long do_stride, long long o_stride) {
+  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= static_cast<long long>(total_tokens) * n_q) return;
+  const int t = static_cast<int>(w / n_q), h = static_cast<int>(w % n_q);
+  const __nv_bfloat16* a = dout + t * do_stride + h * d;
+  const __nv_bfloat16* b = o + t * o_stride + h * d;
+  float s = 0.f;
+  for (int i = lane * 2; i < d; i += 64) {
+    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(a + i);
+    const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(b + i);
+    s += __bfloat162float(x.x) * __bfloat162float(y.x) + __bfloat162float(x.y) * __bfloat162float(y.y);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (lane == 0) delta[static_cast<long long>(h) * total_tokens + t] = s;
+}
+
+__global__ void __launch_bounds__(256)
+cast_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long n8) {
+  for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < n8;
+       v += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 a = *reinterpret_cast<const float4*>(acc + v * 8);
+    const float4 b = *reinterpret_cast<const float4*>(acc + v * 8 + 4);
+    *reinterpret_cast<uint4*>(dq + v * 8) =
+        make_uint4(pack2(a.x, a.y), pack2(a.z, a.w), pack2(b.x, b.y), pack2(b.z, b.w));
+  }
+}
+
 }  // namespace
 
 cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
@@ -401,6 +718,63 @@ cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float
     attn_fwd_kernel<64><<<grid, 192, FwdCfg<64>::kSmem, stream>>>(tq, tk, tv, p);
   else
     attn_fwd_kernel<128><<<grid, 192, FwdCfg<128>::kSmem, stream>>>(tq, tk, tv, p);
+  return cudaGetLastError();
+}
+
+}  // namespace odc
+
+namespace odc {
+
+cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                     void* dq, void* dk, void* dv, float* delta, float* dq_acc, const int* cu_seqlens, int num_seqs,
+                     int total_tokens, int max_seqlen, int n_q, int n_kv, int head_dim, long long q_stride,
+                     long long kv_stride, long long o_stride, float scale, bool causal, int* status, int sm_count,
+                     cudaStream_t stream) {
+  (void)max_seqlen;
+  if (total_tokens == 0 || num_seqs == 0) return cudaSuccess;
+  if (head_dim != 64 && head_dim != 128) return cudaErrorInvalidValue;
+  if (n_q % n_kv != 0) return cudaErrorInvalidValue;
+  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8)) return cudaErrorInvalidValue;
+  // dout, dq are contiguous [T, n_q, D]; dk, dv contiguous [T, n_kv, D]
+  const long long do_stride = static_cast<long long>(n_q) * head_dim;
+  {
+    const long long warps = static_cast<long long>(total_tokens) * n_q;
+    const int grid = static_cast<int>((warps * 32 + 255) / 256);
+    attn_delta_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dout),
+                                                static_cast<const __nv_bfloat16*>(o), delta, total_tokens, n_q,
+                                                head_dim, do_stride, o_stride);
+  }
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, sizeof(float) * static_cast<size_t>(total_tokens) * n_q * head_dim, stream);
+  if (e != cudaSuccess) return e;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!encode_tile_map_2d(&tq, q, static_cast<uint64_t>(n_q) * head_dim, total_tokens, q_stride * 2, 64, 128) ||
+      !encode_tile_map_2d(&tk, k, static_cast<uint64_t>(n_kv) * head_dim, total_tokens, kv_stride * 2, 64, 128) ||
+      !encode_tile_map_2d(&tv, v, static_cast<uint64_t>(n_kv) * head_dim, total_tokens, kv_stride * 2, 64, 128) ||
+      !encode_tile_map_2d(&tdo, dout, static_cast<uint64_t>(n_q) * head_dim, total_tokens, do_stride * 2, 64, 128))
+    return cudaErrorInvalidValue;
+  BwdParams p;
+  p.cu_seqlens = cu_seqlens; p.num_seqs = num_seqs; p.n_q = n_q; p.n_kv = n_kv; p.lse = lse; p.delta = delta;
+  p.dq_acc = dq_acc; p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
+  p.total_tokens = total_tokens; p.scale = scale; p.scale_log2 = scale * kLog2e; p.causal = causal ? 1 : 0;
+  p.status = status;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(attn_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg<64>::kSmem);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(attn_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      BwdCfg<128>::kSmem);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  dim3 grid((total_tokens + 127) / 128 + num_seqs, n_kv);
+  if (head_dim == 64)
+    attn_bwd_kernel<64><<<grid, 192, BwdCfg<64>::kSmem, stream>>>(tq, tk, tv, tdo, p);
+  else
+    attn_bwd_kernel<128><<<grid, 192, BwdCfg<128>::kSmem, stream>>>(tq, tk, tv, tdo, p);
+  const long long n8 = static_cast<long long>(total_tokens) * n_q * head_dim / 8;
+  long long g = (n8 + 255) / 256;
+  if (g > sm_count * 16) g = sm_count * 16;
+  cast_dq_kernel<<<static_cast<int>(g), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
   return cudaGetLastError();
 }
 

@@ -35,3 +35,24 @@ def test_attention_forward(lens, hq, hkv, d):
     s = (q[:L, 0].float() @ k[:L, 0].float().t()) * d ** -0.5
     s = s.masked_fill(~torch.ones(L, L, dtype=torch.bool, device="cuda").tril(), float("-inf"))
     torch.testing.assert_close(lse[0, :L], torch.logsumexp(s, -1), rtol=1e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("lens,hq,hkv,d", [([128], 1, 1, 64), ([256], 2, 1, 64), ([100, 29, 300], 4, 2, 64),
+                                           ([128], 1, 1, 128), ([513, 7, 1000, 128], 8, 2, 128)])
+def test_attention_backward(lens, hq, hkv, d):
+    from odc_b200 import ops
+    from odc_b200.ops import reference as ref
+    q, k, v, cu = _case(lens, hq, hkv, d, seed=3)
+    q, k, v = (t.detach().clone().requires_grad_() for t in (q, k, v))
+    o = ops.varlen_attention(q, k, v, cu, max(lens))
+    do = torch.randn_like(o)
+    o.backward(do)
+    from odc_b200 import _ext
+    assert _ext.load().kernel_status()[0].item() == 0
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    want = ref.varlen_attention(qr, kr, vr, cu.cpu(), True, d ** -0.5)
+    want.backward(do.float())
+    for name, got, exp in (("dq", q.grad, qr.grad), ("dk", k.grad, kr.grad), ("dv", v.grad, vr.grad)):
+        err = (got.float() - exp).abs().max().item()
+        ref_mag = exp.abs().max().item()
+        assert err <= 3e-2 * max(ref_mag, 1.0), (name, err, ref_mag)
