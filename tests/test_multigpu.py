@@ -1,0 +1,155 @@
+"""Real peer access over NVLink: needs >= 2 GPUs in one box (skipped otherwise).
+
+Ranks are child processes, one per GPU, NCCL for the bootstrap; NVLS is switched off so that a
+rank leaving early can never be holding a switch-multicast binding.
+"""
+import os
+import socket
+import subprocess
+import sys
+import textwrap
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _ngpu():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(body: str, world: int, timeout=300, env=None):
+    script = textwrap.dedent("""
+        import os, sys, torch, torch.distributed as dist
+        sys.path.insert(0, %r)
+        rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+        torch.cuda.set_device(rank)
+        dev = torch.device("cuda", rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        import odc_b200 as odc
+    """ % REPO) + textwrap.dedent(body) + "\ndist.destroy_process_group()\nprint('RANK_OK', rank)\n"
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        e = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1",
+                 MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0", LOCAL_WORLD_SIZE=str(world))
+        e.update(env or {})
+        procs.append(subprocess.Popen([sys.executable, "-c", script], env=e, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n<timed out>"
+        outs.append(out)
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "RANK_OK" in out, f"rank {r} failed:\n{out[-3000:]}"
+    return outs
+
+
+PRIMS = """
+reg = odc.init_nvshmem(dev, 4 << 30)
+g = odc.GatherService()
+red = odc.ReductionService(accumulation_dtype=torch.float32)
+for n in (1000, 1 << 20, (1 << 22) + 8):
+    shard = reg.allocate_symm_buffer(f"w{n}", (n,), torch.float32)
+    shard.copy_(torch.arange(n, device=dev, dtype=torch.float32) % 1024 + 4096 * rank)
+    torch.cuda.synchronize(); dist.barrier()
+    out = torch.empty(world * n, dtype=torch.bfloat16, device=dev)
+    g.gather_into_tensor(out, shard)
+    want = torch.cat([torch.arange(n, device=dev, dtype=torch.float32) % 1024 + 4096 * r for r in range(world)]).bfloat16()
+    assert torch.equal(out, want), n
+    rounds = rank + 1                      # ranks contribute different numbers of microbatches
+    red.register(f"g{n}", n, torch.bfloat16)
+    for _ in range(rounds):
+        x = torch.full((world * n,), float(rank + 1), dtype=torch.bfloat16, device=dev)
+        red.scatter_accumulate(f"g{n}", x)
+    red.sync()
+    total = float(sum((r + 1) * (r + 1) for r in range(world)))
+    acc = red.get_accumulation(f"g{n}")
+    assert torch.equal(acc, torch.full((n,), total, device=dev)), (n, acc[:4], total)
+    torch.cuda.synchronize(); dist.barrier()
+red.stop()
+odc.finalize_distributed()
+"""
+
+
+@pytest.mark.parametrize("mode", ["vmm", "ipc"])
+def test_primitives_over_nvlink(mode):
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(PRIMS, min(_ngpu(), 4), env={"ODC_HEAP_MODE": mode, "ODC_IPC_SLAB_SIZE": "2G"})
+
+
+FSDP = """
+from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+from odc_b200.fsdp import fsdp2
+from odc_b200.models import DecoderLM, get_config
+from odc_b200.data import LengthSpec, make_minibatch, to_device
+
+def run(use_odc):
+    cfg = get_config("tiny", hidden_size=512, intermediate_size=1536, num_heads=8, num_kv_heads=2, vocab_size=4096)
+    with torch.device(dev):
+        model = DecoderLM(cfg)
+    model.reset_parameters(seed=0)
+    if use_odc:
+        fsdp2.patch_fsdp2()
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    for layer in model.layers:
+        fully_shard(layer, mp_policy=mp)
+    fully_shard(model, mp_policy=mp)
+    if use_odc:
+        for m in list(model.layers) + [model]:
+            fsdp2.patch_lazy_init(m)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for step in range(3):
+        if use_odc:
+            fsdp2.pre_minibatch_start(model)
+        n_micro = 2 + (rank if use_odc else world - 1)
+        tot = torch.zeros((), device=dev)
+        for i in range(n_micro):
+            real = i < 2 + rank
+            mb = to_device(make_minibatch(rank, step, cfg.vocab_size, LengthSpec("uniform", lo=32, hi=300), 2 + rank, 1024, seed=5)[i if real else 0], dev)
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"], loss_scale=mb["loss_scale"])
+            if not real:
+                loss = loss * 0.0
+            loss.backward()
+            tot += loss.detach()
+        if use_odc:
+            fsdp2.pre_optimizer_step(model)
+        opt.step(); opt.zero_grad()
+        dist.all_reduce(tot)
+        losses.append(float(tot))
+    sd = {k: v.full_tensor().float().cpu() for k, v in model.state_dict().items()}
+    if use_odc:
+        fsdp2.unpatch_fsdp2()
+    return losses, sd
+
+odc.init_nvshmem(dev, 4 << 30)
+l_odc, sd_odc = run(True)
+l_ref, sd_ref = run(False)
+for a, b in zip(l_odc, l_ref):
+    assert abs(a - b) <= 2e-2 * abs(b), (l_odc, l_ref)
+for k in sd_ref:
+    torch.testing.assert_close(sd_odc[k], sd_ref[k], rtol=5e-2, atol=5e-3)
+odc.finalize_distributed()
+"""
+
+
+def test_fsdp2_uneven_microbatches_matches_stock_over_nvlink():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(FSDP, 2, timeout=600)
