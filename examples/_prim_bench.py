@@ -1,0 +1,63 @@
+"""Shared code of the two primitive micro-benchmarks (launched with torch.distributed.run)."""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (900 nominal)
+
+
+def setup():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    return rank, world, dev
+
+
+def device_time_ms(fn, iters: int, warmup: int = 3) -> float:
+    """Median over iterations of the max-over-ranks device time of ``fn`` (CUDA events)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); fn(); b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ts.append(float(t))
+    return statistics.median(ts)
+
+
+def sizes_from_argv(default_lo=64 << 10, default_hi=1 << 30):
+    lo, hi = default_lo, default_hi
+    for a in sys.argv[1:]:
+        if a.startswith("--min="):
+            lo = int(a.split("=")[1])
+        if a.startswith("--max="):
+            hi = int(a.split("=")[1])
+    out, s = [], lo
+    while s <= hi:
+        out.append(s)
+        s *= 2
+    return out
+
+
+def emit(rank, rows, name):
+    if rank != 0:
+        return
+    os.makedirs("gpurun_out", exist_ok=True)
+    with open(os.path.join("gpurun_out", name), "w") as f:
+        json.dump(rows, f, indent=1)

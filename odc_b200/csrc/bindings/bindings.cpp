@@ -280,6 +280,44 @@ void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional
         "gemm");
 }
 
+void gemm_wgrad_scatter(Tensor dy, Tensor x, Tensor acc_table, Tensor ctr_table, int64_t acc_offset,
+                        int64_t rows_per_rank, double scale) {
+  c10::cuda::CUDAGuard g(dy.device());
+  TORCH_CHECK(dy.dim() == 2 && x.dim() == 2 && dy.size(0) == x.size(0), "wgrad_scatter: dy [T,N], x [T,K]");
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16, "wgrad_scatter: bf16 inputs");
+  TORCH_CHECK(dy.stride(1) == 1 && x.stride(1) == 1, "wgrad_scatter: innermost stride must be 1");
+  check(odc::gemm_wgrad_scatter(dy.data_ptr(), x.data_ptr(), dy.size(0), dy.size(1), x.size(1), dy.stride(0),
+                                x.stride(0), reinterpret_cast<const long long*>(acc_table.data_ptr<int64_t>()),
+                                reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()), acc_offset,
+                                static_cast<int>(rows_per_rank), static_cast<int>(acc_table.numel()),
+                                static_cast<float>(scale), next_done_slot(dy.get_device()),
+                                gemm_status(dy.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+        "gemm_wgrad_scatter");
+}
+
+Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<Tensor> bias, int64_t rows_per_rank,
+                   int start_rank) {
+  c10::cuda::CUDAGuard g(x.device());
+  TORCH_CHECK(x.dim() == 2 && w_local.dim() == 2 && x.size(1) == w_local.size(1), "gemm_gather: x [M,K], w_local [N,K]");
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w_local.scalar_type() == at::kBFloat16 && w_local.is_contiguous() &&
+                  x.stride(1) == 1, "gemm_gather: bf16, contiguous weight buffer");
+  const int M = x.size(0), K = x.size(1), N = w_local.size(0);
+  auto y = torch::empty({M, N}, x.options());
+  auto flags = torch::empty({(N + 255) / 256}, x.options().dtype(at::kInt));
+  const void* bias_ptr = nullptr;
+  if (bias.has_value()) {
+    TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N, "gemm_gather: bias bf16 [N]");
+    bias_ptr = bias->data_ptr();
+  }
+  check(odc::gemm_gather_nt(x.data_ptr(), reinterpret_cast<const long long*>(shard_table.data_ptr<int64_t>()),
+                            w_local.data_ptr(), y.data_ptr(), bias_ptr, M, N, K, x.stride(0), y.stride(0),
+                            static_cast<int>(rows_per_rank), static_cast<int>(shard_table.numel()), start_rank,
+                            reinterpret_cast<unsigned int*>(flags.data_ptr<int>()),
+                            gemm_status(x.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+        "gemm_gather");
+  return y;
+}
+
 std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, bool causal,
                                     double scale) {
   c10::cuda::CUDAGuard g(q.device());
@@ -349,6 +387,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm);
+  m.def("gemm_wgrad_scatter", &gemm_wgrad_scatter);
+  m.def("gemm_gather", &gemm_gather);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
   m.def("kernel_status", &kernel_status);

@@ -49,6 +49,20 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
                       int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
                       int sm_count, cudaStream_t stream);
 
+// ---- GEMMs fused with the on-demand primitives ---------------------------------------------------
+// dW[n_out, k_in] = dY[tokens, n_out]^T X[tokens, k_in]; row r of dW is added (x scale) into
+// accumulator acc_ptrs[r / rows_per_rank] at element acc_offset + (r % rows_per_rank) * k_in.
+cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
+                               long long ld_x, const long long* acc_ptrs, const long long* ctr_ptrs,
+                               long long acc_offset, int rows_per_rank, int nranks, float scale,
+                               unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream);
+// Y[M, N] = X[M, K] W[N, K]^T with rank r holding rows [r * rows_per_rank, ...) of W at shard_ptrs[r];
+// w_local [N, K] receives the gathered weight; panel_flags needs ceil(N / 256) words.
+cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_local, void* y, const void* bias,
+                           int M, int N, int K, long long ldx, long long ldy, int rows_per_rank, int nranks,
+                           int start_rank, unsigned int* panel_flags, int* status, int sm_count,
+                           cudaStream_t stream);
+
 // ---- varlen attention ------------------------------------------------------------------------
 cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,
                      int num_seqs, int total_tokens, int max_seqlen, int n_q, int n_kv, int head_dim,

@@ -1,0 +1,353 @@
+// Kernel body shared by the plain GEMM and its two communication-fused variants (see
+// gemm_tcgen05.cu for the design of the main loop).
+//   kModePlain   : C is written (or accumulated) locally.
+//   kModeScatter : weight-gradient GEMM whose epilogue issues 16-byte red.add.f32 straight into the
+//                  fp32 accumulator of the rank that owns each output row, then signals arrival.
+//   kModeGather  : forward GEMM whose B operand (a row-sharded weight) is pulled from the owners'
+//                  shards into local memory by two extra warps per CTA while the tensor cores work
+//                  on panels that have already landed; TMA only ever reads this GPU's own memory.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include "api.h"
+#include "sm100_ptx.cuh"
+
+namespace odc {
+namespace gemm_impl {
+
+using namespace sm100;
+
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kATile = BM * BK * 2;           // 16 KiB
+constexpr int kBTile = BN * BK * 2;           // 32 KiB
+constexpr int kStageBytes = kATile + kBTile;  // 48 KiB
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint64_t kWaitBudgetNs = 4000000000ull;
+
+struct Params {
+  void* c;
+  const __nv_bfloat16* bias;
+  int M, N, K;
+  long long ldc;
+  int c_is_f32;
+  int accumulate;
+  int a_mn, b_mn;  // operand is MN-major
+  int tiles_m, tiles_n;
+  int* status;
+  // --- kModeScatter: the epilogue adds the tile into the owners' fp32 accumulators ---
+  const long long* acc_ptrs;   // [nranks] base address of the accumulator on each owner
+  const long long* ctr_ptrs;   // [nranks] arrival counters
+  long long acc_offset;        // element offset of this parameter inside an accumulator
+  int rows_per_rank;           // output rows owned by one rank
+  int nranks;
+  float scale;
+  unsigned int* done_slot;     // self-resetting CTA completion counter (scratch)
+  // --- kModeGather: operand B is assembled from the owners' shards while the GEMM runs ---
+  const long long* shard_ptrs; // [nranks] base address of each owner's [rows_per_rank, K] bf16 shard
+  unsigned char* b_local;      // local [N, K] bf16 buffer the shards are gathered into (tensor map B covers it)
+  unsigned int* panel_flags;   // [tiles_n] chunks landed per 256-row panel (zeroed before launch)
+  int start_rank;
+};
+
+constexpr int kModePlain = 0, kModeScatter = 1, kModeGather = 2;
+constexpr int kFetchChunkBytes = 16384;
+
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int kMode>
+__global__ void __launch_bounds__(kMode == kModeGather ? kThreads + 64 : kThreads, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw);
+  // barrier block lives after the stage ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  const uint32_t full0 = smem_u32(bars);                    // [kStages]
+  const uint32_t empty0 = full0 + 8 * kStages;              // [kStages]
+  const uint32_t tfull0 = empty0 + 8 * kStages;             // [2]
+  const uint32_t tempty0 = tfull0 + 16;                     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitCtx wc{abort_flag, p.status, kWaitBudgetNs};
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull0 + 8 * a, 1);
+      mbar_init(tempty0 + 8 * a, 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * BM;
+        const int n0 = (tile / p.tiles_m) * BN;
+        if constexpr (kMode == kModeGather) {
+          // the 256 rows of B this tile multiplies must have landed in local memory first
+          const int panel = tile / p.tiles_m;
+          const long long panel_bytes = static_cast<long long>(min(BN, p.N - panel * BN)) * p.K * 2;
+          const unsigned int target = static_cast<unsigned int>((panel_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * 2u;
+          const uint64_t t0 = globaltimer_ns();
+          unsigned int seen;
+          while (true) {
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.panel_flags + panel) : "memory");
+            if (seen >= target) break;
+            if (*abort_flag) { ok = false; break; }
+            if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+              *abort_flag = 1;
+              report(p.status, kErrPipelineTimeout, 5, panel);
+              ok = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+          if (!ok) break;
+          asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> visible to TMA reads
+        }
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, wc, 1))) break;
+          const uint32_t sa = base + s * kStageBytes;
+          const uint32_t sb = sa + kATile;
+          const uint32_t bar = full0 + 8 * s;
+          mbar_arrive_expect_tx(bar, kStageBytes);
+          const int k0 = kb * BK;
+          if (!p.a_mn) {
+            tma_load_2d(sa, &tmap_a, bar, k0, m0);                 // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmap_a, bar, m0 + 64 * i, k0);
+          }
+          if (!p.b_mn) {
+            tma_load_2d(sb, &tmap_b, bar, k0, n0);                 // box {64 k, 256 rows}
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmap_b, bar, n0 + 64 * i, k0);
+          }
+        }
+      }
+      if (!ok) {
+        // aborting: give copies already in flight a bounded chance to land before smem is released
+        for (int s = 0; s < kStages; ++s) {
+          for (int spin = 0; spin < 20000; ++spin)
+            if (mbar_try_wait(full0 + 8 * s, 0) || mbar_try_wait(full0 + 8 * s, 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16(BM, BN, p.a_mn != 0, p.b_mn != 0);
+      const uint32_t a_lbo = p.a_mn ? 8192u : 16u, b_lbo = p.b_mn ? 8192u : 16u;
+      const uint32_t a_kstep = p.a_mn ? 2048u : 32u, b_kstep = p.b_mn ? 2048u : 32u;  // bytes per K=16
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!(ok = mbar_wait(tempty0 + 8 * acc, acc_ph ^ 1, wc, 2))) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!(ok = mbar_wait(full0 + 8 * s, ph, wc, 3))) break;
+          tc_fence_after();
+          const uint32_t sa = base + s * kStageBytes;
+          const uint32_t sb = sa + kATile;
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j) {
+            const uint64_t da = make_smem_desc(sa + j * a_kstep, a_lbo, 1024);
+            const uint64_t db = make_smem_desc(sb + j * b_kstep, b_lbo, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(empty0 + 8 * s);  // stage reusable once these MMAs have read it
+        }
+        if (ok) umma_commit(tfull0 + 8 * acc);
+      }
+    }
+  } else if (kMode == kModeGather && warp >= 6) {
+    // ------------------------------------------------------------------ shard fetch (warps 6,7)
+    // Copy the owners' shards into the local B buffer in address order (= panel order), 16 KiB per
+    // step and CTA; each warp moves half a chunk and then counts it on the panel's flag.
+    const int fw = warp - 6;
+    const long long total_bytes = static_cast<long long>(p.N) * p.K * 2;
+    const long long shard_bytes = static_cast<long long>(p.rows_per_rank) * p.K * 2;
+    const long long panel_bytes_full = static_cast<long long>(BN) * p.K * 2;
+    const long long n_chunks = (total_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes;
+    // chunks never straddle a panel because panel_bytes_full is a multiple of the chunk size (K % 32 == 0)
+    for (long long c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+      const long long byte0 = c * kFetchChunkBytes + fw * (kFetchChunkBytes / 2);
+      uint4 r[8];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const long long b = byte0 + (static_cast<long long>(half * 8 + v) * 32 + lane) * 16;
+          if (b < total_bytes) {
+            const int owner = static_cast<int>(b / shard_bytes);
+            r[v] = ld_stream_v4(reinterpret_cast<const unsigned char*>(p.shard_ptrs[owner]) + (b - owner * shard_bytes));
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const long long b = byte0 + (static_cast<long long>(half * 8 + v) * 32 + lane) * 16;
+          if (b < total_bytes) *reinterpret_cast<uint4*>(p.b_local + b) = r[v];
+        }
+      }
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        const int panel = static_cast<int>((c * kFetchChunkBytes) / panel_bytes_full);
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.panel_flags + panel) : "memory");
+      }
+    }
+  } else if (warp >= 2 && warp < 6) {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      const int m0 = (tile % p.tiles_m) * BM;
+      const int n0 = (tile / p.tiles_m) * BN;
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      if (!(ok = mbar_wait(tfull0 + 8 * acc, acc_ph, wc, 4))) break;
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) continue;
+        float f[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(r[i]);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.N) f[i] += __bfloat162float(p.bias[col0 + i]);
+        }
+        if constexpr (kMode == kModeScatter) {
+          if (row_ok) {
+            const int owner = row / p.rows_per_rank;
+            float* dst = reinterpret_cast<float*>(p.acc_ptrs[owner]) + p.acc_offset +
+                         static_cast<long long>(row - owner * p.rows_per_rank) * p.ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              if (col0 + v * 4 < p.N)
+                red_add_v4_f32(dst + 4 * v, f[4 * v] * p.scale, f[4 * v + 1] * p.scale, f[4 * v + 2] * p.scale,
+                               f[4 * v + 3] * p.scale);
+          }
+        } else if (row_ok) {
+          if (p.c_is_f32) {
+            float* crow = static_cast<float*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              if (col0 + v * 4 < p.N) {
+                float4 o = make_float4(f[4 * v], f[4 * v + 1], f[4 * v + 2], f[4 * v + 3]);
+                if (p.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(crow + 4 * v);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(crow + 4 * v) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col0 + v * 8 < p.N) {
+                if (p.accumulate) {
+                  const uint4 old = *reinterpret_cast<const uint4*>(crow + 8 * v);
+                  const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    f[8 * v + 2 * i] += __uint_as_float(o[i] << 16);
+                    f[8 * v + 2 * i + 1] += __uint_as_float(o[i] & 0xffff0000u);
+                  }
+                }
+                uint4 o;
+                o.x = pack2(f[8 * v], f[8 * v + 1]);
+                o.y = pack2(f[8 * v + 2], f[8 * v + 3]);
+                o.z = pack2(f[8 * v + 4], f[8 * v + 5]);
+                o.w = pack2(f[8 * v + 6], f[8 * v + 7]);
+                *reinterpret_cast<uint4*>(crow + 8 * v) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
+    }
+    if constexpr (kMode == kModeScatter) __threadfence_system();  // this thread's remote reductions are out
+  }
+
+  // ---------------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if constexpr (kMode == kModeScatter) {
+    // last CTA to finish releases one arrival on every owner's counter
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const unsigned int prev = atomicAdd(p.done_slot, 1u);
+      if (prev == gridDim.x - 1) {
+        *p.done_slot = 0;
+        __threadfence_system();
+        if (!*abort_flag)
+          for (int r = 0; r < p.nranks; ++r)
+            signal_add_release_sys(reinterpret_cast<unsigned long long*>(p.ctr_ptrs[r]), 1ull);
+      }
+    }
+  }
+}
+
+
+}  // namespace gemm_impl
+}  // namespace odc

@@ -228,3 +228,47 @@ def test_linear_cross_entropy_matches_reference():
     torch.testing.assert_close(loss, lr_.detach(), rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(h.grad.float(), hr.grad, rtol=5e-2, atol=2e-4)
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=5e-2, atol=2e-4)
+
+
+# ------------------------------------------------------------------------------------ fused compute + comm
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("T,n_out,k_in", [(512, 256, 256), (1000, 768, 264), (4096, 2048, 2048)])
+def test_wgrad_scatter_emulated_ranks(ext, world, T, n_out, k_in):
+    """dW = dY^T X reduced straight into per-owner fp32 accumulators (owners emulated by local buffers)."""
+    torch.manual_seed(T + n_out)
+    rows_per = (n_out + world - 1) // world
+    off = 64  # the parameter starts 64 elements into each accumulator
+    accs = [torch.zeros(off + rows_per * k_in + 32, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    want = torch.zeros(n_out, k_in, device="cuda")
+    for producer in range(2):  # two emulated producers add into the same owners
+        dy = torch.randn(T, n_out, device="cuda").bfloat16()
+        x = torch.randn(T, k_in, device="cuda").bfloat16()
+        ext.gemm_wgrad_scatter(dy, x, _table(accs), _table(ctrs), off, rows_per, 0.5)
+        want += 0.5 * (dy.float().t() @ x.float())
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0
+    for r in range(world):
+        rows = max(0, min(rows_per, n_out - r * rows_per))
+        got = accs[r][off:off + rows * k_in].view(rows, k_in)
+        torch.testing.assert_close(got, want[r * rows_per:r * rows_per + rows], rtol=2e-2, atol=2e-2 * math.sqrt(T))
+        assert float(accs[r][:off].abs().sum()) == 0.0 and float(accs[r][off + rows_per * k_in:].abs().sum()) == 0.0
+        assert int(ctrs[r][0]) == 2
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 1376, 512), (8192, 3072, 2048)])
+def test_gemm_gather_emulated_ranks(ext, world, M, N, K):
+    """Y = X W^T with W assembled from row shards while the GEMM runs (owners emulated by local buffers)."""
+    torch.manual_seed(M + N + K)
+    rows_per = (N + world - 1) // world
+    W = torch.randn(world * rows_per, K, device="cuda").bfloat16()
+    shards = [W[r * rows_per:(r + 1) * rows_per].clone() for r in range(world)]
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    w_local = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+    y = ext.gemm_gather(x, _table(shards), w_local, bias, rows_per, 1 % world)
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
+    assert torch.equal(w_local, W[:N])
+    torch.testing.assert_close(y.float(), x.float() @ W[:N].float().t() + bias.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
