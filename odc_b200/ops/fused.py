@@ -1,0 +1,83 @@
+"""GEMMs fused with the on-demand primitives (single launches).
+
+``gather_linear``: ``y = x @ W.T`` where ``W`` is row-sharded over a group and lives in the
+symmetric heap; the kernel pulls the owners' shards into a local buffer panel by panel while the
+tensor cores already multiply the panels that have landed.  Returns the assembled weight too, so
+the backward pass (or a later microbatch) can reuse it without another transfer.
+
+``wgrad_scatter``: ``dW = dy.T @ x`` whose epilogue adds every output tile into the owning rank's
+fp32 accumulator and signals arrival, with the same bookkeeping as
+``ReductionService.scatter_accumulate`` (one dispatched contribution per owner per call).
+
+On CPU both fall back to the plain statement of the op over the host-shm heap so that the
+multi-rank logic is testable without a GPU.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..primitives import ReductionService
+from ..runtime import control
+from ..runtime.registry import SymmBufferRegistry
+
+
+def gather_linear(x: torch.Tensor, weight_shard: torch.Tensor, out_features: int,
+                  pg: Optional[dist.ProcessGroup] = None, bias: Optional[torch.Tensor] = None
+                  ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``weight_shard``: this rank's ``[rows_per_rank, K]`` rows of ``W`` (a symmetric-heap tensor)."""
+    reg = SymmBufferRegistry.get_instance()
+    ranks = control.group_ranks(pg)
+    me = control.rank()
+    rows_per, K = weight_shard.shape
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.is_cuda:
+        from .. import _ext
+        from . import _count
+        table = reg.peer_ptr_table(weight_shard, ranks)
+        w_full = torch.empty(out_features, K, dtype=weight_shard.dtype, device=x.device)
+        y = _ext.load().gemm_gather(x2, table, w_full, bias, rows_per, ranks.index(me) if me in ranks else 0)
+        _count()
+    else:
+        peers = reg.get_peer_tensors(weight_shard)
+        w_full = torch.cat([peers[r] for r in ranks], dim=0)[:out_features].clone()
+        y = torch.nn.functional.linear(x2, w_full.to(x2.dtype), bias)
+    return y.view(*x.shape[:-1], out_features), w_full
+
+
+def wgrad_scatter(dy: torch.Tensor, x: torch.Tensor, reduction: ReductionService, key, param_offset: int,
+                  rows_per_rank: int, pg: Optional[dist.ProcessGroup] = None, scale: float = 1.0) -> None:
+    """Add ``scale * dy.T @ x`` (shape ``[n_out, k_in]``, rows split ``rows_per_rank`` per owner) into ``key``."""
+    ranks = control.group_ranks(pg)
+    acc = reduction.get_accumulation(key)
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    x2 = x.reshape(-1, x.shape[-1])
+    n_out, k_in = dy2.shape[1], x2.shape[1]
+    if param_offset + rows_per_rank * k_in > acc.numel():
+        raise ValueError("parameter does not fit in the accumulator at this offset")
+    if dy2.is_cuda:
+        from .. import _ext
+        from . import _count
+        reg = reduction.registry
+        if acc.dtype != torch.float32:
+            raise ValueError("the fused weight-gradient path accumulates in fp32")
+        _ext.load().gemm_wgrad_scatter(dy2.contiguous(), x2.contiguous(), reg.peer_ptr_table(acc, ranks),
+                                       reg.peer_ptr_table(reduction.counter, ranks), param_offset, rows_per_rank, scale)
+        _count()
+        reduction.note_dispatch(ranks)
+    else:
+        dw = (dy2.float().t() @ x2.float()) * scale
+        pad = rows_per_rank * len(ranks) - n_out
+        if pad:
+            dw = torch.cat([dw, dw.new_zeros(pad, k_in)])
+        accs = reduction.registry.get_peer_tensors(acc)
+        ctrs = reduction.registry.get_peer_tensors(reduction.counter)
+        heap = reduction.registry.heap
+        for i, r in enumerate(ranks):
+            with heap.owner_lock(r):
+                accs[r][param_offset:param_offset + rows_per_rank * k_in] += \
+                    dw[i * rows_per_rank:(i + 1) * rows_per_rank].reshape(-1).to(acc.dtype)
+                ctrs[r][0] += 1
+        reduction.note_dispatch(ranks)

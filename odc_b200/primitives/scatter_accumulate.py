@@ -88,6 +88,10 @@ class ReductionService:
         my_index = ranks.index(me)
         with nvtx_range("odc::scatter_accumulate"):
             self.transport.scatter_add(input.view(n, shard), acc, self.counter, ranks, my_index, scale)
+        self.note_dispatch(ranks)
+
+    def note_dispatch(self, ranks) -> None:
+        """Record one contribution sent to each of ``ranks`` (also used by the fused weight-gradient GEMM)."""
         for r in ranks:
             self.dispatched[r] = self.dispatched.get(r, 0) + 1
         self.calls += 1

@@ -153,3 +153,44 @@ def test_fsdp2_uneven_microbatches_matches_stock_over_nvlink():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     _launch(FSDP, 2, timeout=600)
+
+
+FUSED = """
+from odc_b200 import parallel
+odc.init_nvshmem(dev, 4 << 30)
+lin = parallel.OdcLinear(1024, 3072, seed=3)
+torch.manual_seed(100 + rank)
+xs = [torch.randn(700 + 64 * rank, 1024, device=dev).bfloat16().requires_grad_() for _ in range(1 + rank)]
+parallel.start_minibatch()
+ys = []
+for x in xs:
+    y = lin(x)
+    (y.float() ** 2).sum().backward()
+    ys.append(y.detach())
+shards = [torch.empty_like(lin.weight.master) for _ in range(world)]
+dist.all_gather(shards, lin.weight.master)
+W = torch.cat(shards)[:3072].bfloat16().float()
+parallel.finish_minibatch(lr=0.0)
+dW = torch.zeros(3072, 1024, device=dev)
+for x, y in zip(xs, ys):
+    want = x.float() @ W.t()
+    torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(x.grad.float(), (2 * y.float()) @ W, rtol=3e-2, atol=0.5)
+    dW += (2 * y.float()).t() @ x.float()
+dist.all_reduce(dW)
+dW /= world
+got = lin.weight.grad()
+rows = lin.weight.rows_per_rank
+torch.testing.assert_close(got, dW[rank * rows:(rank + 1) * rows], rtol=3e-2, atol=2.0)
+from odc_b200 import _ext
+assert _ext.load().kernel_status()[0].item() == 0
+torch.cuda.synchronize(); dist.barrier()
+parallel.reset()
+odc.finalize_distributed()
+"""
+
+
+def test_fused_linear_over_nvlink():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(FUSED, min(_ngpu(), 4), timeout=600)
