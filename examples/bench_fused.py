@@ -30,7 +30,7 @@ def main():
     shapes = [(2048, 3072, 2048), (16384, 3072, 2048), (16384, 16384, 2048), (4096, 28672, 4096), (1024, 16384, 2048)]
     for (M, N, K) in shapes:
         rows_per = (N + world - 1) // world
-        shard = reg.allocate_symm_buffer(f"w{N}x{K}", (rows_per, K), torch.bfloat16)
+        shard = reg.allocate_symm_buffer(f"w{M}x{N}x{K}", (rows_per, K), torch.bfloat16)
         shard.copy_(0.02 * torch.randn(rows_per, K, device=dev))
         x = torch.randn(M, K, device=dev).bfloat16()
         torch.cuda.synchronize(); dist.barrier()
@@ -51,25 +51,29 @@ def main():
                   frac_of_roofline=roof_ms / t_f)
         # weight gradient
         dy = torch.randn(M, N, device=dev).bfloat16()
-        key = f"g{N}x{K}"
+        key = f"g{M}x{N}x{K}"
         red.register(key, rows_per * K, torch.float32)
         ref_acc = torch.zeros(rows_per * K, device=dev)
         rs_out = torch.empty(rows_per * K, device=dev)
         pad = world * rows_per - N
 
+        REP = 4  # several microbatches per synchronisation, as in training
+
         def ours_bwd():
-            fused.wgrad_scatter(dy, x, red, key, 0, rows_per)
+            for _ in range(REP):
+                fused.wgrad_scatter(dy, x, red, key, 0, rows_per)
             red.sync()
 
         def base_bwd():
-            dw = torch.matmul(dy.t(), x).float()
-            if pad:
-                dw = torch.cat([dw, dw.new_zeros(pad, K)])
-            dist.reduce_scatter_tensor(rs_out, dw.view(-1))
-            ref_acc.add_(rs_out)
+            for _ in range(REP):
+                dw = torch.matmul(dy.t(), x).float()
+                if pad:
+                    dw = torch.cat([dw, dw.new_zeros(pad, K)])
+                dist.reduce_scatter_tensor(rs_out, dw.view(-1))
+                ref_acc.add_(rs_out)
 
-        t_f2 = device_time_ms(ours_bwd, 6)
-        t_b2 = device_time_ms(base_bwd, 6)
+        t_f2 = device_time_ms(ours_bwd, 6) / REP
+        t_b2 = device_time_ms(base_bwd, 6) / REP
         outbound = rows_per * K * 4 * (world - 1)
         roof2 = max(flops / (peak_tf * 1e12), outbound / (NVLINK_GBS * 1e9)) * 1e3
         r2 = dict(op="wgrad_scatter", world=world, M=M, N=N, K=K, ms=t_f2, baseline_ms=t_b2, roofline_ms=roof2,

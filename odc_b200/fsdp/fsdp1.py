@@ -1,1 +1,282 @@
-"""placeholder, filled in below"""
+"""On-demand communication for PyTorch FSDP1 (``FullyShardedDataParallel`` with flat parameters).
+
+Public API of the reference (odc/fsdp/fsdp1.py:302-348): ``patch_fsdp1(reduce_dtype=None)`` before
+any ``FSDP(...)`` is constructed, ``pre_minibatch_start(fsdp_model)`` once after construction and
+after every optimizer step, ``pre_optimizer_step(fsdp_model)`` before ``optimizer.step()``,
+``stop()``.  Supported: FULL_SHARD / SHARD_GRAD_OP with ``use_orig_params=False``, with or without
+mixed precision; unsupported (asserted): communication hooks, HYBRID_SHARD, CPU offload.
+
+How it works here:
+
+* ``FlatParamHandle.shard`` places the rank's flat shard in the symmetric heap, so the optimizer
+  updates memory that peers can read.
+* With parameter mixed precision a second heap buffer holds the shard in the compute dtype,
+  refreshed once per minibatch; ``_all_gather_flat_param`` becomes one ``gather`` launch that pulls
+  compute-precision bytes (the reference pulls the original dtype and casts after the transfer,
+  odc/fsdp/fsdp1.py:189-223).  The per-unshard low-precision copy of stock FSDP is skipped.
+* ``_reduce_grad`` pads the unsharded gradient and ``scatter_accumulate``-s it, folding the
+  pre/post divide factors into the kernel's scale; nothing is attached to ``flat_param.grad``
+  until ``pre_optimizer_step`` has waited for all contributions.
+"""
+from __future__ import annotations
+
+import logging
+from typing import Any, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+import torch.distributed.fsdp._runtime_utils as _ru
+import torch.distributed.fsdp._traversal_utils as _tu
+from torch.distributed.fsdp._common_utils import HandleTrainingState, _FSDPState
+from torch.distributed.fsdp._flat_param import FlatParamHandle, HandleShardingStrategy
+
+from ..primitives import GatherService, ReductionService
+from ..runtime import control
+from ..runtime.registry import SymmBufferRegistry
+from ..utils.nvtx import nvtx_range
+
+logger = logging.getLogger("odc_b200")
+
+
+class _State:
+    patched = False
+    reduce_dtype: Optional[torch.dtype] = None
+    originals: Dict[str, Any] = {}
+    reduction: Optional[ReductionService] = None
+    gather: Optional[GatherService] = None
+    next_index = 0
+    in_shard: Optional[FlatParamHandle] = None
+
+
+_S = _State
+
+
+def get_reduction_service():
+    return _S.reduction
+
+
+def get_gather_service():
+    return _S.gather
+
+
+def _services():
+    if _S.reduction is None:
+        _S.reduction = ReductionService(accumulation_dtype=_S.reduce_dtype)
+        _S.gather = GatherService()
+    return _S.reduction, _S.gather
+
+
+def _check_supported(handle: FlatParamHandle) -> None:
+    if handle._sharding_strategy in (HandleShardingStrategy.HYBRID_SHARD, HandleShardingStrategy._HYBRID_SHARD_ZERO2):
+        raise AssertionError("on-demand FSDP1 does not support HYBRID_SHARD (use FSDP2 for HSDP)")
+    if handle._offload_params:
+        raise AssertionError("on-demand FSDP1 does not support CPU offload")
+    if handle._use_orig_params:
+        raise AssertionError("on-demand FSDP1 requires use_orig_params=False")
+
+
+# ------------------------------------------------------------------------------------------
+# shard -> symmetric heap
+# ------------------------------------------------------------------------------------------
+def _shard(self: FlatParamHandle):
+    if not self.uses_sharded_strategy:
+        return _S.originals["shard"](self)
+    _check_supported(self)
+    _S.in_shard = self
+    try:
+        return _S.originals["shard"](self)
+    finally:
+        _S.in_shard = None
+
+
+def _get_shard(tensor, rank, world_size):
+    shard, numel_to_pad = _S.originals["_get_shard"](tensor, rank, world_size)
+    handle = _S.in_shard
+    if handle is None or not SymmBufferRegistry.is_initialized():
+        return shard, numel_to_pad
+    reg = SymmBufferRegistry.get_instance()
+    if shard.device.type != reg.heap.device.type:
+        raise AssertionError("construct FSDP with the module already on the compute device (device_id=...)")
+    index = _S.next_index
+    _S.next_index += 1
+    key = f"fsdp1_flat_{index}"
+    buf = reg.allocate_symm_buffer(key, shard.shape, shard.dtype)  # collective: every rank wraps in the same order
+    buf.copy_(shard)
+    handle._odc_index = index
+    handle._odc_key = key
+    return buf, numel_to_pad
+
+
+def _handles(fsdp_model) -> List[FlatParamHandle]:
+    return [h for h in _tu._get_fsdp_handles(fsdp_model) if hasattr(h, "_odc_key")]
+
+
+def _replica(handle: FlatParamHandle) -> Optional[torch.Tensor]:
+    return getattr(handle, "_odc_replica", None)
+
+
+# ------------------------------------------------------------------------------------------
+# unshard = gather
+# ------------------------------------------------------------------------------------------
+def _use_low_precision_shard(self: FlatParamHandle):
+    if hasattr(self, "_odc_key"):
+        return  # the compute-precision copy lives in the heap and is refreshed once per minibatch
+    return _S.originals["_use_low_precision_shard"](self)
+
+
+def _free_low_precision_sharded_param(self: FlatParamHandle):
+    if hasattr(self, "_odc_key"):
+        return
+    return _S.originals["_free_low_precision_sharded_param"](self)
+
+
+@torch.no_grad()
+def _all_gather_flat_param(self: FlatParamHandle, padded_unsharded_flat_param: torch.Tensor) -> torch.Tensor:
+    if not hasattr(self, "_odc_key") or self._use_fake_all_gather:
+        return _S.originals["_all_gather_flat_param"](self, padded_unsharded_flat_param)
+    _, gather = _services()
+    shard = self.flat_param._local_shard if hasattr(self.flat_param, "_local_shard") else self.flat_param.data
+    src = shard
+    rep = _replica(self)
+    if rep is not None and padded_unsharded_flat_param.dtype == rep.dtype:
+        src = rep
+    if padded_unsharded_flat_param.numel() != src.numel() * self.world_size:
+        raise AssertionError(f"expected {src.numel() * self.world_size} elements, got {padded_unsharded_flat_param.numel()}")
+    gather.gather_into_tensor(padded_unsharded_flat_param, src, self.process_group)
+    return padded_unsharded_flat_param
+
+
+# ------------------------------------------------------------------------------------------
+# reduce = scatter_accumulate
+# ------------------------------------------------------------------------------------------
+@torch.no_grad()
+def _reduce_grad(state: _FSDPState, handle: FlatParamHandle) -> None:
+    if not hasattr(handle, "_odc_key"):
+        return _S.originals["_reduce_grad"](state, handle)
+    if state._comm_hook is not None:
+        raise AssertionError("on-demand FSDP1 does not support communication hooks")
+    reduction, _ = _services()
+    flat_param = handle.flat_param
+    unsharded_grad = flat_param.grad.data
+    flat_param.grad = None
+    padded, _unused = _ru._get_reduce_scatter_tensors(state, unsharded_grad)
+    factor = float(state._gradient_predivide_factor) * float(state._gradient_postdivide_factor)
+    if not reduction.has_accumulation(handle._odc_key):
+        reduction.register(handle._odc_key, padded.numel() // state.world_size, padded.dtype, state.process_group)
+    reduction.scatter_accumulate(handle._odc_key, padded, state.process_group, scale=1.0 / factor)
+    # marks "a gradient was produced" for stock bookkeeping; the real value is assigned in pre_optimizer_step
+    flat_param._saved_grad_shard = reduction.get_accumulation(handle._odc_key)
+
+
+def _prepare_gradient_for_optim(self: FlatParamHandle):
+    if not hasattr(self, "_odc_key"):
+        return _S.originals["prepare_gradient_for_optim"](self)
+    if hasattr(self.flat_param, "_saved_grad_shard"):
+        delattr(self.flat_param, "_saved_grad_shard")  # never hand the live accumulator to the optimizer
+
+
+# ------------------------------------------------------------------------------------------
+# minibatch boundary
+# ------------------------------------------------------------------------------------------
+def _device_sync():
+    if torch.cuda.is_available():
+        torch.cuda.current_stream().synchronize()
+
+
+@torch.no_grad()
+def pre_minibatch_start(fsdp_model) -> None:
+    """Zero accumulators, publish updated shards (and their compute-precision copies); collective."""
+    _require_patched()
+    reduction, _ = _services()
+    reg = SymmBufferRegistry.get_instance()
+    with nvtx_range("odc::pre_minibatch_start"):
+        for h in _handles(fsdp_model):
+            shard = h.flat_param._local_shard if hasattr(h.flat_param, "_local_shard") else h.flat_param.data
+            if not reduction.has_accumulation(h._odc_key):
+                acc_dtype = h._reduce_dtype if getattr(h, "_reduce_dtype", None) is not None else shard.dtype
+                if h._uses_param_mixed_precision and getattr(h, "_reduce_dtype", None) is None:
+                    acc_dtype = h._fwd_bwd_param_dtype
+                reduction.register(h._odc_key, shard.numel(), acc_dtype, h.process_group)
+            if h._uses_param_mixed_precision and h._fwd_bwd_param_dtype != shard.dtype:
+                if _replica(h) is None:
+                    h._odc_replica = reg.allocate_symm_buffer(f"fsdp_params_lowp_{h._odc_key}", shard.shape,
+                                                              h._fwd_bwd_param_dtype)
+                h._odc_replica.copy_(shard)
+        reduction.clear_accumulations()
+        _device_sync()
+        control.host_barrier()
+
+
+@torch.no_grad()
+def pre_optimizer_step(fsdp_model) -> None:
+    """Wait for every contribution (collective) and expose the summed gradient as ``flat_param.grad``."""
+    _require_patched()
+    if not isinstance(fsdp_model, _FSDPState):
+        raise AssertionError("pass the root FSDP module")
+    reduction, _ = _services()
+    reduction.sync()
+    for h in _handles(fsdp_model):
+        if not reduction.has_accumulation(h._odc_key):
+            continue
+        acc = reduction.get_accumulation(h._odc_key)
+        fp = h.flat_param
+        shard = fp._local_shard if hasattr(fp, "_local_shard") else fp.data
+        g = acc.to(shard.dtype) if acc.dtype != shard.dtype else acc.clone()
+        if fp.data.data_ptr() != shard.data_ptr():
+            fp.data = shard  # the optimizer must see the sharded flat parameter
+        fp.grad = g.view_as(shard)
+
+
+# ------------------------------------------------------------------------------------------
+def _require_patched():
+    if not _S.patched:
+        raise RuntimeError("call odc_b200.fsdp.fsdp1.patch_fsdp1() first")
+
+
+def patch_fsdp1(reduce_dtype: Optional[torch.dtype] = None) -> None:
+    """Route FSDP1's flat-parameter all-gather and gradient reduce-scatter through the on-demand primitives."""
+    if _S.patched:
+        return
+    _S.reduce_dtype = reduce_dtype
+    _S.originals = {
+        "shard": FlatParamHandle.shard,
+        "_get_shard": FlatParamHandle._get_shard,
+        "_all_gather_flat_param": FlatParamHandle._all_gather_flat_param,
+        "_use_low_precision_shard": FlatParamHandle._use_low_precision_shard,
+        "_free_low_precision_sharded_param": FlatParamHandle._free_low_precision_sharded_param,
+        "prepare_gradient_for_optim": FlatParamHandle.prepare_gradient_for_optim,
+        "_reduce_grad": _ru._reduce_grad,
+    }
+    FlatParamHandle.shard = _shard
+    FlatParamHandle._get_shard = staticmethod(_get_shard)
+    FlatParamHandle._all_gather_flat_param = _all_gather_flat_param
+    FlatParamHandle._use_low_precision_shard = _use_low_precision_shard
+    FlatParamHandle._free_low_precision_sharded_param = _free_low_precision_sharded_param
+    FlatParamHandle.prepare_gradient_for_optim = _prepare_gradient_for_optim
+    _ru._reduce_grad = _reduce_grad
+    _S.patched = True
+
+
+def unpatch_fsdp1() -> None:
+    if not _S.patched:
+        return
+    o = _S.originals
+    FlatParamHandle.shard = o["shard"]
+    FlatParamHandle._get_shard = staticmethod(o["_get_shard"])
+    FlatParamHandle._all_gather_flat_param = o["_all_gather_flat_param"]
+    FlatParamHandle._use_low_precision_shard = o["_use_low_precision_shard"]
+    FlatParamHandle._free_low_precision_sharded_param = o["_free_low_precision_sharded_param"]
+    FlatParamHandle.prepare_gradient_for_optim = o["prepare_gradient_for_optim"]
+    _ru._reduce_grad = o["_reduce_grad"]
+    _S.patched = False
+    _S.reduction = _S.gather = None
+    _S.next_index = 0
+
+
+def stop() -> None:
+    """End of training: stop the services and release the symmetric heap (collective)."""
+    if _S.reduction is not None:
+        _S.reduction.stop()
+    unpatch_fsdp1()
+    from .. import finalize_distributed
+    finalize_distributed()

@@ -1,0 +1,66 @@
+"""FSDP1 with on-demand communication against stock FSDP1, on CPU ranks (gloo)."""
+import pytest
+import torch
+
+from _mp import run_ranks
+
+
+def _train(rank, world, mode, uneven):
+    import functools
+
+    import torch.distributed as dist
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+    from torch.distributed.fsdp.wrap import ModuleWrapPolicy
+
+    import odc_b200 as odc
+    from odc_b200.data import LengthSpec, make_minibatch
+    from odc_b200.fsdp import fsdp1
+    from odc_b200.models import DecoderLayer, DecoderLM, get_config
+
+    if mode == "odc":
+        fsdp1.patch_fsdp1(reduce_dtype=torch.float32)
+        odc.init_nvshmem("cpu", 256 << 20)
+    torch.manual_seed(0)
+    model = DecoderLM(get_config("tiny"))
+    model.reset_parameters(seed=0)
+    model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=torch.device("cpu"),
+                 use_orig_params=False)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    if mode == "odc":
+        fsdp1.pre_minibatch_start(model)
+    losses = []
+    for step in range(3):
+        mine = (2 + rank) if uneven else 2
+        n_micro = mine if mode == "odc" else (2 + world - 1 if uneven else 2)
+        total = torch.zeros(())
+        for i in range(n_micro):
+            real = i < mine
+            mb = make_minibatch(rank, step, 1024, LengthSpec("uniform", lo=16, hi=128), mine, 128, seed=7)[i if real else 0]
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"],
+                         loss_scale=mb["loss_scale"])
+            if not real:
+                loss = loss * 0.0
+            loss.backward()
+            total += loss.detach()
+        if mode == "odc":
+            fsdp1.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+        if mode == "odc":
+            fsdp1.pre_minibatch_start(model)
+        dist.all_reduce(total)
+        losses.append(float(total))
+    with FSDP.summon_full_params(model):
+        full = {k: v.detach().clone() for k, v in model.named_parameters()}
+    if mode == "odc":
+        fsdp1.stop()
+    return losses, full
+
+
+@pytest.mark.parametrize("uneven", [False, True])
+def test_fsdp1_matches_stock(uneven):
+    a = run_ranks(_train, 2, "stock", uneven)
+    b = run_ranks(_train, 2, "odc", uneven)
+    assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)

@@ -194,3 +194,56 @@ def test_fused_linear_over_nvlink():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     _launch(FUSED, min(_ngpu(), 4), timeout=600)
+
+
+FSDP1 = """
+from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, MixedPrecision
+from torch.distributed.fsdp.wrap import ModuleWrapPolicy
+from odc_b200.fsdp import fsdp1
+from odc_b200.models import DecoderLM, DecoderLayer, get_config
+from odc_b200.data import LengthSpec, make_minibatch, to_device
+
+def run(use_odc):
+    if use_odc:
+        fsdp1.patch_fsdp1(reduce_dtype=torch.float32)
+    cfg = get_config("tiny", hidden_size=512, intermediate_size=1536, num_heads=8, num_kv_heads=2, vocab_size=4096)
+    with torch.device(dev):
+        model = DecoderLM(cfg)
+    model.reset_parameters(seed=0)
+    mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, buffer_dtype=torch.bfloat16)
+    model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=dev, use_orig_params=False, mixed_precision=mp)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    if use_odc:
+        fsdp1.pre_minibatch_start(model)
+    losses = []
+    for step in range(3):
+        tot = torch.zeros((), device=dev)
+        for i in range(2):
+            mb = to_device(make_minibatch(rank, step, cfg.vocab_size, LengthSpec("uniform", lo=32, hi=300), 2, 1024, seed=5)[i], dev)
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"], loss_scale=mb["loss_scale"])
+            loss.backward()
+            tot += loss.detach()
+        if use_odc:
+            fsdp1.pre_optimizer_step(model)
+        opt.step(); opt.zero_grad()
+        if use_odc:
+            fsdp1.pre_minibatch_start(model)
+        dist.all_reduce(tot)
+        losses.append(float(tot))
+    if use_odc:
+        fsdp1.unpatch_fsdp1()
+    return losses
+
+odc.init_nvshmem(dev, 4 << 30)
+l_odc = run(True)
+l_ref = run(False)
+for a, b in zip(l_odc, l_ref):
+    assert abs(a - b) <= 2e-2 * abs(b), (l_odc, l_ref)
+odc.finalize_distributed()
+"""
+
+
+def test_fsdp1_mixed_precision_matches_stock_over_nvlink():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(FSDP1, 2, timeout=600)
