@@ -1,0 +1,25 @@
+"""Command-line flags of the LLM trainers (counterpart of the reference's examples/llm_training/args.py)."""
+import argparse
+import os
+
+
+def get_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--dataset", default="synthetic", help="'synthetic' or a .pt file holding a list of 1-D token tensors")
+    p.add_argument("--length-dist", default="lognormal", choices=["lognormal", "longtail", "uniform"])
+    p.add_argument("--minibatch_size", type=int, default=8, help="sequences per rank per minibatch")
+    p.add_argument("--micro_batch_size", type=int, default=1)
+    p.add_argument("--max_token_len", type=int, default=65536)
+    p.add_argument("--limit_dataset_token_len", type=int, default=None)
+    p.add_argument("--model_name", default="qwen2.5-1.5b")
+    p.add_argument("--packing_method", default="DynamicDiffMicro",
+                   choices=["None", "DynamicSameMicro", "DynamicDiffMicro", "LocalSort", "DebugUneven"])
+    p.add_argument("--cost_model", default="linear", choices=["linear", "fit", "flops"])
+    p.add_argument("--run_name", default="run")
+    p.add_argument("--project_name", default="odc_b200")
+    p.add_argument("--forward_only", action="store_true", default=os.environ.get("FORWARD_ONLY", "0") == "1")
+    p.add_argument("--steps", type=int, default=10)
+    p.add_argument("--lr", type=float, default=5e-4)
+    p.add_argument("--activation-checkpointing", action="store_true")
+    p.add_argument("--num-sequences", type=int, default=4096)
+    return p.parse_args()

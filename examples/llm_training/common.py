@@ -1,0 +1,75 @@
+"""Pieces shared by the FSDP1 and FSDP2 trainers."""
+import json
+import os
+import sys
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+from odc_b200.data import BatchedDataset, LengthSpec, get_cost_fn, sample_lengths  # noqa: E402
+from odc_b200.models import get_config  # noqa: E402
+
+
+class Timer:
+    """Wall-clock timer that synchronises the device on both sides."""
+
+    def __init__(self, name, sink):
+        self.name, self.sink = name, sink
+
+    def __enter__(self):
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.t0 = time.perf_counter()
+
+    def __exit__(self, *exc):
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        self.sink[self.name] = self.sink.get(self.name, 0.0) + time.perf_counter() - self.t0
+
+
+def build_sequences(args, vocab):
+    if args.dataset != "synthetic":
+        return torch.load(args.dataset)
+    spec = {"lognormal": LengthSpec("lognormal", lo=16, median=1024.0, sigma=1.2, cap=min(16384, args.max_token_len)),
+            "longtail": LengthSpec("longtail", long=(8192, min(32768, args.max_token_len))),
+            "uniform": LengthSpec("uniform", lo=64, hi=2048)}[args.length_dist]
+    rng = np.random.default_rng(0)  # the same global dataset on every rank; packing decides who gets what
+    lens = sample_lengths(spec, args.num_sequences, rng)
+    return [torch.from_numpy(rng.integers(0, vocab, size=n)) for n in lens]
+
+
+def make_dataset(args, cfg, rank, world, odc_enabled):
+    seqs = build_sequences(args, cfg.vocab_size)
+    kw = {}
+    if args.cost_model == "flops":
+        h, f = cfg.hidden_size, cfg.intermediate_size
+        kw = dict(linear_params=cfg.num_layers * (cfg.qkv_dim * h + h * cfg.num_heads * cfg.head_dim + 3 * h * f),
+                  attn_width=cfg.num_layers * cfg.num_heads * cfg.head_dim)
+    cost = get_cost_fn(args.cost_model, **kw)
+    return BatchedDataset(seqs, args.minibatch_size, rank, world, args.packing_method, args.max_token_len,
+                          args.limit_dataset_token_len, cost, odc_enabled)
+
+
+def log_metrics(rank, step, metrics):
+    """Rank 0 prints one JSON line per minibatch (the reference logs the same fields to wandb)."""
+    if rank == 0:
+        print(json.dumps({"step": step, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in metrics.items()}}),
+              flush=True)
+
+
+def memory_metrics():
+    if not torch.cuda.is_available():
+        return {}
+    from odc_b200.runtime.registry import SymmBufferRegistry
+    symm = SymmBufferRegistry.get_instance().memory_allocated() / 2**30 if SymmBufferRegistry.is_initialized() else 0.0
+    return {"torch_mem_gib": torch.cuda.memory_allocated() / 2**30, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2**30,
+            "symm_mem_gib": symm}
+
+
+def mark_done(args):
+    os.makedirs("gpurun_out", exist_ok=True)
+    with open(os.path.join("gpurun_out", f"{args.run_name}.done"), "w") as f:
+        f.write("done\n")

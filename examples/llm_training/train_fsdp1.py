@@ -1,0 +1,82 @@
+"""LLM trainer on FSDP1 (counterpart of the reference's examples/llm_training/torch_fsdp.py).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        examples/llm_training/train_fsdp1.py --model_name qwen2.5-1.5b --activation-checkpointing
+"""
+import os
+
+import torch
+import torch.distributed as dist
+from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+from torch.distributed.fsdp import MixedPrecision
+from torch.distributed.fsdp.wrap import ModuleWrapPolicy
+
+from args import get_args
+from common import Timer, log_metrics, make_dataset, mark_done, memory_metrics
+
+import odc_b200 as odc
+from odc_b200.data import to_device
+from odc_b200.fsdp import fsdp1
+from odc_b200.models import DecoderLayer, DecoderLM, get_config
+
+ODC = os.environ.get("ODC", "1") == "1"
+if ODC:
+    fsdp1.patch_fsdp1(reduce_dtype=torch.float32)  # before any FSDP(...) is constructed
+
+
+def main():
+    args = get_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    if ODC:
+        odc.init_nvshmem(dev)
+    cfg = get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)
+    with torch.device(dev):
+        model = DecoderLM(cfg)
+    model.reset_parameters(seed=0)
+    mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, buffer_dtype=torch.bfloat16)
+    model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=dev, use_orig_params=False,
+                 mixed_precision=mp)
+    opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
+    data = make_dataset(args, cfg, rank, world, ODC)
+    if ODC:
+        fsdp1.pre_minibatch_start(model)
+    for step in range(min(args.steps, len(data))):
+        times = {}
+        microbatches = data[step]
+        with Timer("minibatch_time", times):
+            total = torch.zeros((), device=dev)
+            tokens = 0
+            for mb in microbatches:
+                mb = to_device(mb, dev)
+                tokens += mb["num_tokens"]
+                loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"],
+                             loss_scale=mb["loss_scale"])
+                if not args.forward_only:
+                    loss.backward()
+                total += loss.detach()
+            if not args.forward_only:
+                with Timer("sync_time", times):
+                    if ODC:
+                        fsdp1.pre_optimizer_step(model)
+                with Timer("optimizer_step_time", times):
+                    grad_norm = model.clip_grad_norm_(1.0)
+                    opt.step()
+                    opt.zero_grad()
+                if ODC:
+                    fsdp1.pre_minibatch_start(model)
+        dist.all_reduce(total)
+        tok = torch.tensor([tokens], device=dev)
+        dist.all_reduce(tok)
+        log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
+                                 "tokens_per_s": int(tok) / times["minibatch_time"], **times, **memory_metrics()})
+    mark_done(args)
+    if ODC:
+        fsdp1.stop()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

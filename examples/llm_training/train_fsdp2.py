@@ -1,0 +1,112 @@
+"""LLM trainer on FSDP2 (counterpart of the reference's examples/llm_training/torch_fsdp2.py).
+
+Environment switches: ``ODC`` (default 1), ``HPZ``, ``HSDP``; ``TORCH_PROFILED=1`` writes a chrome
+trace per rank; ``CUDA_PROFILED=1`` brackets the last minibatch with cudaProfilerStart/Stop.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        examples/llm_training/train_fsdp2.py --model_name llama3.2-1b --packing_method DynamicDiffMicro --max_token_len 16384
+"""
+import os
+
+import torch
+import torch.distributed as dist
+from torch.distributed.device_mesh import init_device_mesh
+from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+
+from args import get_args
+from common import Timer, log_metrics, make_dataset, mark_done, memory_metrics
+
+import odc_b200 as odc
+from odc_b200.data import to_device
+from odc_b200.fsdp import fsdp2
+from odc_b200.models import DecoderLM, get_config
+from odc_b200.utils.nvtx import nvtx_range
+
+ODC = os.environ.get("ODC", "1") == "1"
+HPZ = os.environ.get("HPZ", "0") == "1"
+HSDP = os.environ.get("HSDP", "0") == "1"
+
+
+def main():
+    args = get_args()
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    cfg = get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)
+    if ODC:
+        odc.init_nvshmem(dev)
+        fsdp2.patch_fsdp2(enable_hpz=HPZ)
+    with torch.device(dev):
+        model = DecoderLM(cfg)
+    model.reset_parameters(seed=0)
+    mesh = init_device_mesh("cuda", (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard")) if HSDP \
+        else init_device_mesh("cuda", (world,))
+    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+    raf = (world // 2 if not HSDP else max(1, world // 4)) if HPZ else True
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh, mp_policy=mp, reshard_after_forward=raf)
+    fully_shard(model, mesh=mesh, mp_policy=mp, reshard_after_forward=raf)
+    if ODC:
+        for m in list(model.layers) + [model]:
+            fsdp2.patch_lazy_init(m)
+    use_fused = ODC and os.environ.get("FUSED_OPTIMIZER", "1") == "1"
+    opt = fsdp2.FusedAdamW(model, lr=args.lr, weight_decay=0.01) if use_fused else \
+        torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
+    data = make_dataset(args, cfg, rank, world, ODC)
+    prof = None
+    if os.environ.get("TORCH_PROFILED", "0") == "1":
+        prof = torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA])
+        prof.start()
+    steps = min(args.steps, len(data))
+    for step in range(steps):
+        times = {}
+        if os.environ.get("CUDA_PROFILED", "0") == "1" and step == steps - 1:
+            torch.cuda.cudart().cudaProfilerStart()
+        microbatches = data[step]
+        with Timer("minibatch_time", times):
+            if ODC:
+                fsdp2.pre_minibatch_start(model)
+            total = torch.zeros((), device=dev)
+            tokens = 0
+            for mb in microbatches:
+                with nvtx_range("microbatch"):
+                    mb = to_device(mb, dev)
+                    tokens += mb["num_tokens"]
+                    with torch.set_grad_enabled(not args.forward_only):
+                        loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"],
+                                     labels=mb["labels"], loss_scale=mb["loss_scale"])
+                    if not args.forward_only:
+                        loss.backward()
+                    total += loss.detach()
+            if not args.forward_only:
+                with Timer("sync_time", times):
+                    if ODC:
+                        fsdp2.pre_optimizer_step(model, materialize_grads=not use_fused)
+                with Timer("optimizer_step_time", times):
+                    if use_fused:
+                        grad_norm = opt.clip_grad_norm_(1.0)
+                    else:
+                        grad_norm = torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+                    opt.step()
+                    opt.zero_grad()
+        dist.all_reduce(total)
+        tok = torch.tensor([tokens], device=dev)
+        dist.all_reduce(tok)
+        log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
+                                 "tokens_per_s": int(tok) / times["minibatch_time"],
+                                 "grad_norm": float(grad_norm) if not args.forward_only else 0.0, **times, **memory_metrics()})
+    if os.environ.get("CUDA_PROFILED", "0") == "1":
+        torch.cuda.cudart().cudaProfilerStop()
+    if prof is not None:
+        prof.stop()
+        os.makedirs("gpurun_out", exist_ok=True)
+        prof.export_chrome_trace(f"gpurun_out/trace_{args.run_name}_rank{rank}.json")
+    mark_done(args)
+    if ODC:
+        fsdp2.stop()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
