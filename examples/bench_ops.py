@@ -149,6 +149,40 @@ def bench_attention():
               f"[flash-attn {t_r:.3f} ms] | bwd {t_b:.3f} ms {2.5 * flops / t_b / 1e9:.0f} TFLOP/s [flash-attn {t_rb:.3f} ms]")
 
 
+def small_gemm():
+    """One forward-shaped GEMM, a few launches: the small case used for ncu captures (operands + output > L2)."""
+    from odc_b200 import _ext
+    ext = _ext.load()
+    layout = sys.argv[2] if len(sys.argv) > 2 else "nt"
+    M, N, K = 16384, 3072, 2048
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = torch.randn(K, N, device="cuda").bfloat16()
+    a = A.t().contiguous() if layout == "tn" else A
+    b = B.t().contiguous() if layout == "nt" else B
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    for _ in range(4):
+        ext.gemm(a, b, c, layout, None, False)
+    torch.cuda.synchronize()
+    print("small_gemm ok", layout, float(c.float().abs().mean()))
+
+
+def small_attention():
+    """One attention forward+backward on 16384 packed tokens: the small case used for ncu captures."""
+    from odc_b200 import ops
+    T, hq, hkv, d = 16384, 32, 8, 64
+    lens = [4096, 2048, 2048, 1024, 1024, 512, 512, 512, 512] + [256] * 16
+    cu = torch.tensor([0] + lens, device="cuda").cumsum(0).int()
+    q = torch.randn(T, hq, d, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(T, hkv, d, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(T, hkv, d, device="cuda").bfloat16().requires_grad_()
+    for _ in range(2):
+        o = ops.varlen_attention(q, k, v, cu, max(lens))
+        o.backward(torch.ones_like(o))
+    torch.cuda.synchronize()
+    print("small_attention ok", float(o.float().abs().mean()))
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "elementwise": bench_elementwise, "comm": bench_comm, "attention": bench_attention}[which]()
+    {"gemm": bench_gemm, "elementwise": bench_elementwise, "comm": bench_comm, "attention": bench_attention,
+     "small_gemm": small_gemm, "small_attention": small_attention}[which]()
