@@ -8,6 +8,7 @@
 
 #include "../heap/symm_heap.h"
 #include "../kernels/api.h"
+#include "../kernels/tensor_map.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -70,6 +71,7 @@ Tensor tensor_from_ptr(uintptr_t ptr, int64_t numel, at::ScalarType dtype, int d
 py::bytes get_ipc_handle(const Tensor& t) {
   TORCH_CHECK(t.is_cuda(), "get_ipc_handle expects a CUDA tensor");
   c10::cuda::CUDAGuard g(t.device());
+  odc::bind_device(t.get_device());
   return py::bytes(odc::ipc_export(t.data_ptr()));
 }
 
@@ -85,6 +87,7 @@ Tensor reconstruct_tensor(const std::string& blob, std::vector<int64_t> shape, a
 void gather(Tensor out2d, Tensor table, int64_t n, at::ScalarType src_dtype, int my_index, bool checkb,
             Tensor status) {
   c10::cuda::CUDAGuard g(out2d.device());
+  odc::bind_device(out2d.get_device());
   const int nranks = static_cast<int>(table.numel());
   TORCH_CHECK(out2d.is_contiguous() && out2d.numel() == n * nranks, "gather: bad output shape");
   const int ssz = static_cast<int>(c10::elementSize(src_dtype));
@@ -100,6 +103,7 @@ void gather(Tensor out2d, Tensor table, int64_t n, at::ScalarType src_dtype, int
 void scatter_accumulate(Tensor inp2d, Tensor acc_table, Tensor ctr_table, int64_t n, at::ScalarType acc_dtype,
                         int my_index, double scale, bool checkb, Tensor status) {
   c10::cuda::CUDAGuard g(inp2d.device());
+  odc::bind_device(inp2d.get_device());
   const int nranks = static_cast<int>(acc_table.numel());
   TORCH_CHECK(inp2d.is_contiguous() && inp2d.numel() == n * nranks, "scatter_accumulate: bad input shape");
   (void)checkb;
@@ -115,6 +119,7 @@ void scatter_accumulate(Tensor inp2d, Tensor acc_table, Tensor ctr_table, int64_
 
 void wait_counter(Tensor counter, int64_t expected, int64_t timeout_ms, Tensor status) {
   c10::cuda::CUDAGuard g(counter.device());
+  odc::bind_device(counter.get_device());
   check(odc::launch_wait_counter(counter.data_ptr(), static_cast<unsigned long long>(expected),
                                  static_cast<unsigned long long>(timeout_ms) * 1000000ull, status.data_ptr<int>(),
                                  cur_stream()),
@@ -124,6 +129,7 @@ void wait_counter(Tensor counter, int64_t expected, int64_t timeout_ms, Tensor s
 // ---------------------------------------------------------------------------------------- ops
 std::tuple<Tensor, Tensor> rmsnorm_fwd(Tensor x, Tensor w, double eps) {
   c10::cuda::CUDAGuard g(x.device());
+  odc::bind_device(x.get_device());
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && x.scalar_type() == at::kBFloat16, "rmsnorm: x must be [T,H] bf16");
   TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.is_contiguous(), "rmsnorm: weight must be bf16");
   auto y = torch::empty_like(x);
@@ -137,6 +143,7 @@ std::tuple<Tensor, Tensor> rmsnorm_fwd(Tensor x, Tensor w, double eps) {
 
 std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) {
   c10::cuda::CUDAGuard g(x.device());
+  odc::bind_device(x.get_device());
   const int rows = static_cast<int>(x.size(0)), cols = static_cast<int>(x.size(1));
   auto dx = torch::empty_like(x);
   const int grid = odc::rmsnorm_bwd_grid(rows, sm_count());
@@ -150,6 +157,7 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rst
 
 Tensor rope_qkv(Tensor qkv, Tensor pos, int n_q, int n_kv, int head_dim, double theta, bool inverse) {
   c10::cuda::CUDAGuard g(qkv.device());
+  odc::bind_device(qkv.get_device());
   TORCH_CHECK(qkv.dim() == 2 && qkv.is_contiguous() && qkv.scalar_type() == at::kBFloat16, "rope: qkv [T,W] bf16");
   TORCH_CHECK(qkv.size(1) == int64_t(n_q + 2 * n_kv) * head_dim, "rope: width mismatch");
   TORCH_CHECK(pos.scalar_type() == at::kLong && pos.numel() == qkv.size(0), "rope: position_ids int64 [T]");
@@ -163,6 +171,7 @@ Tensor rope_qkv(Tensor qkv, Tensor pos, int n_q, int n_kv, int head_dim, double 
 
 Tensor swiglu_fwd(Tensor gu) {
   c10::cuda::CUDAGuard g(gu.device());
+  odc::bind_device(gu.get_device());
   TORCH_CHECK(gu.is_contiguous() && gu.scalar_type() == at::kBFloat16, "swiglu: bf16 contiguous");
   const int f = static_cast<int>(gu.size(-1) / 2);
   auto sizes = gu.sizes().vec();
@@ -175,6 +184,7 @@ Tensor swiglu_fwd(Tensor gu) {
 
 Tensor swiglu_bwd(Tensor dy, Tensor gu) {
   c10::cuda::CUDAGuard g(gu.device());
+  odc::bind_device(gu.get_device());
   const int f = static_cast<int>(gu.size(-1) / 2);
   auto out = torch::empty_like(gu);
   check(odc::launch_swiglu_bwd(dy.data_ptr(), gu.data_ptr(), out.data_ptr(), gu.numel() / (2 * f), f, sm_count(),
@@ -185,6 +195,7 @@ Tensor swiglu_bwd(Tensor dy, Tensor gu) {
 
 void ce_fwd_bwd(Tensor logits, Tensor labels, c10::optional<Tensor> loss_scale, Tensor loss, int64_t ignore_index) {
   c10::cuda::CUDAGuard g(logits.device());
+  odc::bind_device(logits.get_device());
   TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kBFloat16, "ce: logits bf16");
   TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous(), "ce: labels int64");
   const float* ls = nullptr;
@@ -201,6 +212,7 @@ void ce_fwd_bwd(Tensor logits, Tensor labels, c10::optional<Tensor> loss_scale, 
 void adamw_step(Tensor p, Tensor g, Tensor m, Tensor v, c10::optional<Tensor> p_lowp, double lr, double beta1,
                 double beta2, double eps, double wd, int64_t step, double grad_scale) {
   c10::cuda::CUDAGuard guard(p.device());
+  odc::bind_device(p.get_device());
   TORCH_CHECK(p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat,
               "adamw: fp32 master state");
   TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous");
@@ -220,6 +232,7 @@ void adamw_step(Tensor p, Tensor g, Tensor m, Tensor v, c10::optional<Tensor> p_
 
 void cast_f32_to_bf16(Tensor in, Tensor out) {
   c10::cuda::CUDAGuard g(in.device());
+  odc::bind_device(in.get_device());
   TORCH_CHECK(in.scalar_type() == at::kFloat && out.scalar_type() == at::kBFloat16 && in.numel() == out.numel() &&
                   in.is_contiguous() && out.is_contiguous(), "cast: fp32 -> bf16, same numel, contiguous");
   check(odc::launch_cast_f32_to_bf16(in.data_ptr<float>(), out.data_ptr(), static_cast<size_t>(in.numel()), sm_count(),
@@ -229,6 +242,7 @@ void cast_f32_to_bf16(Tensor in, Tensor out) {
 
 void sumsq(Tensor x, Tensor out) {
   c10::cuda::CUDAGuard g(x.device());
+  odc::bind_device(x.get_device());
   TORCH_CHECK(x.is_contiguous() && out.scalar_type() == at::kFloat, "sumsq: contiguous input, fp32 output");
   check(odc::launch_sumsq(x.data_ptr(), kind_of(x.scalar_type()), static_cast<size_t>(x.numel()), out.data_ptr<float>(),
                           sm_count(), cur_stream()),
@@ -252,6 +266,7 @@ Tensor kernel_status() {
 
 void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional<Tensor> bias, bool accumulate) {
   c10::cuda::CUDAGuard g(a.device());
+  odc::bind_device(a.get_device());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2, "gemm: 2-D operands");
   TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16, "gemm: bf16 inputs");
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && c.stride(1) == 1, "gemm: innermost stride must be 1");
@@ -274,15 +289,19 @@ void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional
     TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm: bias bf16 [N]");
     bias_ptr = bias->data_ptr();
   }
-  check(odc::gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), kind_of(c.scalar_type()), bias_ptr, M, N, K, lay,
-                       accumulate, a.stride(0), b.stride(0), c.stride(0), gemm_status(a.get_device()).data_ptr<int>(),
-                       sm_count(), cur_stream()),
-        "gemm");
+  cudaError_t e = odc::gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), kind_of(c.scalar_type()), bias_ptr, M, N, K,
+                                 lay, accumulate, a.stride(0), b.stride(0), c.stride(0),
+                                 gemm_status(a.get_device()).data_ptr<int>(), sm_count(), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "gemm(", layout, ") M=", M, " N=", N, " K=", K, " lda=", a.stride(0), " ldb=", b.stride(0),
+              " ldc=", c.stride(0), " align(a,b,c)=", reinterpret_cast<uintptr_t>(a.data_ptr()) % 16, ",",
+              reinterpret_cast<uintptr_t>(b.data_ptr()) % 16, ",", reinterpret_cast<uintptr_t>(c.data_ptr()) % 16, ": ",
+              cudaGetErrorString(e));
 }
 
 void gemm_wgrad_scatter(Tensor dy, Tensor x, Tensor acc_table, Tensor ctr_table, int64_t acc_offset,
                         int64_t rows_per_rank, double scale) {
   c10::cuda::CUDAGuard g(dy.device());
+  odc::bind_device(dy.get_device());
   TORCH_CHECK(dy.dim() == 2 && x.dim() == 2 && dy.size(0) == x.size(0), "wgrad_scatter: dy [T,N], x [T,K]");
   TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16, "wgrad_scatter: bf16 inputs");
   TORCH_CHECK(dy.stride(1) == 1 && x.stride(1) == 1, "wgrad_scatter: innermost stride must be 1");
@@ -298,6 +317,7 @@ void gemm_wgrad_scatter(Tensor dy, Tensor x, Tensor acc_table, Tensor ctr_table,
 Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<Tensor> bias, int64_t rows_per_rank,
                    int start_rank) {
   c10::cuda::CUDAGuard g(x.device());
+  odc::bind_device(x.get_device());
   TORCH_CHECK(x.dim() == 2 && w_local.dim() == 2 && x.size(1) == w_local.size(1), "gemm_gather: x [M,K], w_local [N,K]");
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w_local.scalar_type() == at::kBFloat16 && w_local.is_contiguous() &&
                   x.stride(1) == 1, "gemm_gather: bf16, contiguous weight buffer");
@@ -321,6 +341,7 @@ Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<T
 std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, bool causal,
                                     double scale) {
   c10::cuda::CUDAGuard g(q.device());
+  odc::bind_device(q.get_device());
   TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "attention: q/k/v are [T, H, D]");
   TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16,
               "attention: bf16 inputs");
@@ -342,6 +363,7 @@ std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seql
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse,
                                             Tensor cu_seqlens, int max_seqlen, bool causal, double scale) {
   c10::cuda::CUDAGuard g(q.device());
+  odc::bind_device(q.get_device());
   const int T = q.size(0), hq = q.size(1), d = q.size(2), hkv = k.size(1);
   TORCH_CHECK(dout.is_contiguous() && dout.scalar_type() == at::kBFloat16, "attention bwd: dout contiguous bf16");
   TORCH_CHECK(o.stride(2) == 1 && o.stride(1) == d, "attention bwd: o heads packed");

@@ -56,7 +56,7 @@ cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_
   p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.scale = scale; p.done_slot = done_slot;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_bf16_kernel<kModeScatter><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p);
+  gemm_bf16_kernel<kModeScatter><<<grid, Roles<kModeScatter>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, p);
   return cudaGetLastError();
 }
 
@@ -68,7 +68,7 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   if (K == 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(y)) & 15)
     return cudaErrorMisalignedAddress;
-  if ((ldx % 8) || (ldy % 8) || (N % 8) || (K % 32)) return cudaErrorInvalidValue;
+  if ((ldx % 8) || (ldy % 8) || (N % 8) || (K % 128)) return cudaErrorInvalidValue;
   if (static_cast<long long>(rows_per_rank) * nranks < N) return cudaErrorInvalidValue;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -96,7 +96,7 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   if (e != cudaSuccess) return e;
   // every CTA also fetches, so use the whole machine even when there are few tiles
   const int grid = sm_count;
-  gemm_bf16_kernel<kModeGather><<<grid, kThreads + 64, kSmemBytes, stream>>>(ta, tb, p);
+  gemm_bf16_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, p);
   return cudaGetLastError();
 }
 

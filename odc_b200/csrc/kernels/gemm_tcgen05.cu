@@ -41,13 +41,13 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
                       int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
                       int sm_count, cudaStream_t stream) {
   if (M == 0 || N == 0) return cudaSuccess;
-  if (K == 0) return cudaErrorInvalidValue;
+  if (K == 0) return cudaErrorInvalidSymbol;
   const bool a_mn = (layout == 2);
   const bool b_mn = (layout != 0);
   // 16-byte rules of TMA: base addresses, row pitches; and of the vector epilogue: N, ldc
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15)
     return cudaErrorMisalignedAddress;
-  if ((lda % 8) || (ldb % 8) || (N % 8) || (ldc % (c_kind == kF32 ? 4 : 8))) return cudaErrorInvalidValue;
+  if ((lda % 8) || (ldb % 8) || (N % 8) || (ldc % (c_kind == kF32 ? 4 : 8))) return cudaErrorInvalidDevicePointer;
 
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
@@ -59,14 +59,14 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
   CUtensorMap ta, tb;
   // A: K-major -> dims {K, M}, box {64, 128};  MN-major -> global [K rows, M cols], box {64 (M), 64 (K)}
   if (!a_mn) {
-    if (!encode_tile_map_2d(&ta, a, /*inner*/ K, /*outer*/ M, lda * 2, 64, BM)) return cudaErrorInvalidValue;
+    if (!encode_tile_map_2d(&ta, a, /*inner*/ K, /*outer*/ M, lda * 2, 64, BM)) return cudaErrorInvalidPitchValue;
   } else {
-    if (!encode_tile_map_2d(&ta, a, /*inner*/ M, /*outer*/ K, lda * 2, 64, 64)) return cudaErrorInvalidValue;
+    if (!encode_tile_map_2d(&ta, a, /*inner*/ M, /*outer*/ K, lda * 2, 64, 64)) return cudaErrorInvalidPitchValue;
   }
   if (!b_mn) {
-    if (!encode_tile_map_2d(&tb, b, K, N, ldb * 2, 64, BN)) return cudaErrorInvalidValue;
+    if (!encode_tile_map_2d(&tb, b, K, N, ldb * 2, 64, BN)) return cudaErrorInvalidTexture;
   } else {
-    if (!encode_tile_map_2d(&tb, b, N, K, ldb * 2, 64, 64)) return cudaErrorInvalidValue;
+    if (!encode_tile_map_2d(&tb, b, N, K, ldb * 2, 64, 64)) return cudaErrorInvalidTexture;
   }
   Params p{};
   p.c = c;
@@ -81,7 +81,7 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
   p.status = status;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_bf16_kernel<kModePlain><<<grid, kThreads, kSmemBytes, stream>>>(ta, tb, p);
+  gemm_bf16_kernel<kModePlain><<<grid, Roles<kModePlain>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, p);
   return cudaGetLastError();
 }
 

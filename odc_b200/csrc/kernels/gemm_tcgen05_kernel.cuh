@@ -55,7 +55,14 @@ struct Params {
 };
 
 constexpr int kModePlain = 0, kModeScatter = 1, kModeGather = 2;
-constexpr int kFetchChunkBytes = 16384;
+// warp roles: 0 = TMA, 1 = MMA, then epilogue warps, then (gather mode) shard-fetch warps
+template <int kMode> struct Roles {
+  static constexpr int kEpilogueWarps = (kMode == kModeScatter) ? 8 : 4;  // remote reductions need more issue slots
+  static constexpr int kFetchWarps = (kMode == kModeGather) ? 4 : 0;
+  static constexpr int kThreadsTotal = 32 * (2 + kEpilogueWarps + kFetchWarps);
+};
+constexpr int kFetchWarpBytes = 16384;                  // moved by one fetch warp between two flag updates
+constexpr int kFetchChunkBytes = 4 * kFetchWarpBytes;   // per CTA and step
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -63,7 +70,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 template <int kMode>
-__global__ void __launch_bounds__(kMode == kModeGather ? kThreads + 64 : kThreads, 1)
+__global__ void __launch_bounds__(Roles<kMode>::kThreadsTotal, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -90,7 +97,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8 * a, 1);
-      mbar_init(tempty0 + 8 * a, 4);  // one arrival per epilogue warp
+      mbar_init(tempty0 + 8 * a, Roles<kMode>::kEpilogueWarps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -121,7 +128,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // the 256 rows of B this tile multiplies must have landed in local memory first
           const int panel = tile / p.tiles_m;
           const long long panel_bytes = static_cast<long long>(min(BN, p.N - panel * BN)) * p.K * 2;
-          const unsigned int target = static_cast<unsigned int>((panel_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * 2u;
+          const unsigned int target = static_cast<unsigned int>((panel_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * 4u;
           const uint64_t t0 = globaltimer_ns();
           unsigned int seen;
           while (true) {
@@ -202,32 +209,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (ok) umma_commit(tfull0 + 8 * acc);
       }
     }
-  } else if (kMode == kModeGather && warp >= 6) {
-    // ------------------------------------------------------------------ shard fetch (warps 6,7)
-    // Copy the owners' shards into the local B buffer in address order (= panel order), 16 KiB per
-    // step and CTA; each warp moves half a chunk and then counts it on the panel's flag.
-    const int fw = warp - 6;
+  } else if (kMode == kModeGather && warp >= 2 + Roles<kMode>::kEpilogueWarps) {
+    // ------------------------------------------------------------------ shard fetch
+    // Copy the owners' shards into the local B buffer in address order (= panel order): 64 KiB per
+    // step and CTA, 16 KiB per warp with 16 x 16-byte loads in flight per lane; after its part a warp
+    // makes the stores visible and counts them on the panel's flag.
+    const int fw = warp - (2 + Roles<kMode>::kEpilogueWarps);
     const long long total_bytes = static_cast<long long>(p.N) * p.K * 2;
     const long long shard_bytes = static_cast<long long>(p.rows_per_rank) * p.K * 2;
-    const long long panel_bytes_full = static_cast<long long>(BN) * p.K * 2;
+    const long long panel_bytes_full = static_cast<long long>(BN) * p.K * 2;  // multiple of the chunk size (K % 128 == 0)
     const long long n_chunks = (total_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes;
-    // chunks never straddle a panel because panel_bytes_full is a multiple of the chunk size (K % 32 == 0)
     for (long long c = blockIdx.x; c < n_chunks; c += gridDim.x) {
-      const long long byte0 = c * kFetchChunkBytes + fw * (kFetchChunkBytes / 2);
-      uint4 r[8];
+      const long long byte0 = c * kFetchChunkBytes + fw * kFetchWarpBytes;
+      uint4 r[16];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const long long b = byte0 + (static_cast<long long>(half * 8 + v) * 32 + lane) * 16;
+        for (int v = 0; v < 16; ++v) {
+          const long long b = byte0 + (static_cast<long long>(half * 16 + v) * 32 + lane) * 16;
           if (b < total_bytes) {
             const int owner = static_cast<int>(b / shard_bytes);
             r[v] = ld_stream_v4(reinterpret_cast<const unsigned char*>(p.shard_ptrs[owner]) + (b - owner * shard_bytes));
           }
         }
 #pragma unroll
-        for (int v = 0; v < 8; ++v) {
-          const long long b = byte0 + (static_cast<long long>(half * 8 + v) * 32 + lane) * 16;
+        for (int v = 0; v < 16; ++v) {
+          const long long b = byte0 + (static_cast<long long>(half * 16 + v) * 32 + lane) * 16;
           if (b < total_bytes) *reinterpret_cast<uint4*>(p.b_local + b) = r[v];
         }
       }
@@ -238,9 +245,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.panel_flags + panel) : "memory");
       }
     }
-  } else if (warp >= 2 && warp < 6) {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
+  } else if (warp >= 2 && warp < 2 + Roles<kMode>::kEpilogueWarps) {
+    // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
+    constexpr int kColGroups = Roles<kMode>::kEpilogueWarps / 4;   // warps sharing a lane quadrant split the columns
+    const int col_group = (warp - 2) / 4;
     uint32_t local_tile = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
@@ -254,7 +263,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = col_group * (BN / 32 / kColGroups); c < (col_group + 1) * (BN / 32 / kColGroups); ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();

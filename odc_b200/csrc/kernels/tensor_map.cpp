@@ -1,6 +1,7 @@
 #include "tensor_map.h"
 
 #include <cuda_runtime.h>
+#include <stdio.h>
 
 namespace odc {
 
@@ -22,6 +23,13 @@ EncodeFn encoder() {
 }
 }  // namespace
 
+void bind_device(int device) {
+  static thread_local int bound = -1;
+  if (bound != device) {
+    if (cudaSetDevice(device) == cudaSuccess && cudaFree(nullptr) == cudaSuccess) bound = device;
+  }
+}
+
 bool encode_tile_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                         uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
   EncodeFn fn = encoder();
@@ -30,9 +38,14 @@ bool encode_tile_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint
   cuuint64_t strides[1] = {row_pitch_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
   cuuint32_t elem[2] = {1, 1};
-  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "odc_b200: cuTensorMapEncodeTiled failed (%d): base=%p dims={%llu,%llu} pitch=%llu box={%u,%u}\n",
+            static_cast<int>(r), base, static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+            static_cast<unsigned long long>(row_pitch_bytes), box_inner, box_outer);
+  return r == CUDA_SUCCESS;
 }
 
 bool encode_tile_map_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,

@@ -14,4 +14,9 @@ bool encode_tile_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint
 bool encode_tile_map_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                         uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0, uint32_t box1, uint32_t box2);
 
+// Make `device`'s primary context current for the calling thread in this library's CUDA runtime.
+// Threads created by PyTorch's autograd engine may not have a driver context bound yet, and
+// tensor-map encoding is a driver call that needs one.
+void bind_device(int device);
+
 }  // namespace odc

@@ -257,7 +257,7 @@ def test_wgrad_scatter_emulated_ranks(ext, world, T, n_out, k_in):
 
 
 @pytest.mark.parametrize("world", [1, 2, 8])
-@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 1376, 512), (8192, 3072, 2048)])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 1376, 512), (8192, 3072, 2048), (300, 264, 128)])
 def test_gemm_gather_emulated_ranks(ext, world, M, N, K):
     """Y = X W^T with W assembled from row shards while the GEMM runs (owners emulated by local buffers)."""
     torch.manual_seed(M + N + K)
