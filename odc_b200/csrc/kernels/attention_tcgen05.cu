@@ -82,16 +82,26 @@ __device__ __forceinline__ bool locate_block(const int* cu, int num_seqs, int bl
 
 template <int D>
 struct FwdCfg {
-  static constexpr int kStages = (D == 64) ? 3 : 2;
+  // D = 64: one score buffer, 256 TMEM columns and 112 KiB of shared memory, so two CTAs share an SM
+  // and hide each other's latency chains (most tiles of short sequences see only 1-3 key blocks).
+  // D = 128: two score buffers, one CTA per SM.
+  static constexpr int kStages = 2;
+  static constexpr int kSBufs = (D == 64) ? 1 : 2;
+  static constexpr int kTmemCols = (D == 64) ? 256 : 512;
+  static constexpr int kOCol = kSBufs * 128;
+  static constexpr int kCtasPerSm = (D == 64) ? 2 : 1;
   static constexpr int kQBytes = kBlockQ * D * 2;
   static constexpr int kKBytes = kBlockKV * D * 2;
   static constexpr int kStageBytes = 2 * kKBytes;
   static constexpr int kPBytes = kBlockQ * kBlockKV * 2;
-  static constexpr int kSmem = kQBytes + kStages * kStageBytes + kPBytes + 1024 + 256;
+  // barriers take 128 bytes; the alignment slack is trimmed for D = 64 so that two CTAs fit in one SM's
+  // 228 KiB (the dynamic window starts 1024-byte aligned in practice; the kernel checks and reports otherwise)
+  static constexpr int kAlignSlack = (D == 64) ? 768 : 1024;
+  static constexpr int kSmem = kQBytes + kStages * kStageBytes + kPBytes + 128 + kAlignSlack;
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, FwdCfg<D>::kCtasPerSm)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const FwdParams p) {
   using C = FwdCfg<D>;
@@ -106,6 +116,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
+  if (base - raw > static_cast<uint32_t>(C::kAlignSlack)) {  // cannot happen with a 1024-aligned window
+    if (threadIdx.x == 0) report(p.status, kErrBounds, 40, static_cast<int>(base - raw));
+    return;
+  }
   const uint32_t q_smem = base;
   const uint32_t kv_smem = q_smem + C::kQBytes;
   const uint32_t p_smem = kv_smem + C::kStages * C::kStageBytes;
@@ -143,14 +157,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + 256;
+  const uint32_t tmem_s0 = tmem_base, tmem_o = tmem_base + C::kOCol;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -182,31 +196,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       auto issue_s = [&](int j) {
         const int st = j % C::kStages;
         const uint32_t k_src = kv_smem + st * C::kStageBytes;
-        const uint32_t d = tmem_s0 + (j & 1) * 128;
+        const uint32_t d = tmem_s0 + (j % C::kSBufs) * 128;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
           umma_f16(d, make_smem_desc(q_smem + off, 16, 1024), make_smem_desc(k_src + off, 16, 1024), idesc_s,
                    k > 0 ? 1u : 0u);
         }
-        umma_commit(s_full0 + 8 * (j & 1));
+        umma_commit(s_full0 + 8 * (j % C::kSBufs));
+      };
+      // S(j+1) may overwrite its buffer once the softmax of block j+1-kSBufs has read it
+      auto issue_next_s = [&](int j) -> bool {
+        if (j + 1 >= n_blocks) return true;
+        const int st1 = (j + 1) % C::kStages;
+        if (!mbar_wait(kv_full0 + 8 * st1, ((j + 1) / C::kStages) & 1, wc, 14)) return false;
+        const int use = (j + 1) / C::kSBufs;
+        if (use >= 1 && !mbar_wait(s_empty0 + 8 * ((j + 1) % C::kSBufs), (use - 1) & 1, wc, 15)) return false;
+        tc_fence_after();
+        issue_s(j + 1);
+        return true;
       };
       if (ok && n_blocks > 0) {
         ok = mbar_wait(kv_full0, 0, wc, 13);
         if (ok) { tc_fence_after(); issue_s(0); }
       }
       for (int j = 0; j < n_blocks && ok; ++j) {
-        if (j + 1 < n_blocks) {
-          const int st1 = (j + 1) % C::kStages;
-          if (!(ok = mbar_wait(kv_full0 + 8 * st1, ((j + 1) / C::kStages) & 1, wc, 14))) break;
-          if (j + 1 >= 2) {  // S buffer (j+1)&1 was last read by the softmax of block j-1
-            if (!(ok = mbar_wait(s_empty0 + 8 * ((j + 1) & 1), (((j + 1) >> 1) - 1) & 1, wc, 15))) break;
-          }
-          tc_fence_after();
-          issue_s(j + 1);
+        if (C::kSBufs == 2) {  // the next score tile runs while the softmax warps work on this one
+          if (!(ok = issue_next_s(j))) break;
         }
         if (!(ok = mbar_wait(p_full, j & 1, wc, 16))) break;
         tc_fence_after();
+        if (C::kSBufs == 1) {  // single buffer: free as soon as P(j) exists; queue S(j+1) ahead of P V(j)
+          if (!(ok = issue_next_s(j))) break;
+        }
         const int st = j % C::kStages;
         const uint32_t v_src = kv_smem + st * C::kStageBytes + C::kKBytes;
 #pragma unroll
@@ -230,29 +252,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     float m_used = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_blocks && ok; ++j) {
-      if (!(ok = mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, wc, 17))) break;
+      if (!(ok = mbar_wait(s_full0 + 8 * (j % C::kSBufs), (j / C::kSBufs) & 1, wc, 17))) break;
       tc_fence_after();
-      const uint32_t t_s = tmem_s0 + (j & 1) * 128 + lane_sel;
+      const uint32_t t_s = tmem_s0 + (j % C::kSBufs) * 128 + lane_sel;
       const int kv0 = j * kBlockKV;
       const bool need_mask = (kv0 + kBlockKV > seq_len) || (p.causal && kv0 + kBlockKV > q0);
-      // pass 1: row maximum
+      // the whole score row (128 fp32) goes to registers with one wait; max, exp and packing run from there
+      uint32_t sr[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sr + c * 32);
+      tmem_ld_wait();
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kv = kv0 + c * 32 + i;
-            const bool okk = kv < seq_len && (!p.causal || kv <= q_rel);
-            mx = fmaxf(mx, okk ? __uint_as_float(r[i]) : -INFINITY);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < 128; ++i) {
+          const int kv = kv0 + i;
+          const bool okk = kv < seq_len && (!p.causal || kv <= q_rel);
+          if (!okk) sr[i] = 0xff800000u;  // -inf
+          mx = fmaxf(mx, __uint_as_float(sr[i]));
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
       }
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // lazy rescale of the running output (exact: P and l keep using m_used until it is bumped)
@@ -283,32 +304,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       float sum = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
-        float f[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]) * p.scale_log2 - m_sub;
-          if (need_mask) {
-            const int kv = kv0 + c * 32 + i;
-            const bool okk = kv < seq_len && (!p.causal || kv <= q_rel);
-            s = okk ? s : -INFINITY;
-          }
-          f[i] = exp2f(s);
+      for (int v = 0; v < 16; ++v) {
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f[i] = exp2f(fmaf(__uint_as_float(sr[8 * v + i]), p.scale_log2, -m_sub));
           sum += f[i];
         }
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 o;
-          o.x = pack2(f[8 * v], f[8 * v + 1]);
-          o.y = pack2(f[8 * v + 2], f[8 * v + 3]);
-          o.z = pack2(f[8 * v + 4], f[8 * v + 5]);
-          o.w = pack2(f[8 * v + 6], f[8 * v + 7]);
-          *reinterpret_cast<uint4*>(p_ptr + swz_chunk_offset(row, c * 4 + v)) = o;
-        }
+        uint4 o;
+        o.x = pack2(f[0], f[1]);
+        o.y = pack2(f[2], f[3]);
+        o.z = pack2(f[4], f[5]);
+        o.w = pack2(f[6], f[7]);
+        *reinterpret_cast<uint4*>(p_ptr + swz_chunk_offset(row, v)) = o;
       }
       l += sum;
       // S buffer free for block j+2; P visible to the tensor core (async proxy)
@@ -316,7 +325,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(s_empty0 + 8 * (j & 1));
+        mbar_arrive(s_empty0 + 8 * (j % C::kSBufs));
         mbar_arrive(p_full);
       }
     }
@@ -358,7 +367,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
 }
 
