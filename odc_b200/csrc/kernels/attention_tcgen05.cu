@@ -402,8 +402,10 @@ __device__ __forceinline__ void red_add_v4_gpu(float* p, float a, float b, float
                : "memory");
 }
 
+constexpr int kBwdThreads = 32 * (2 + 8);  // TMA warp, MMA warp, two compute warpgroups (each takes half of the columns)
+
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                 const BwdParams p) {
@@ -450,9 +452,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(qdo_empty0 + 8 * s, 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, 4);
+    mbar_init(dq_read, 8);
     mbar_init(dkv_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -466,7 +468,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv = tmem_base + 256, tm_dk = tmem_base + 256 + D;
-  const uint32_t tm_dq = tm_s;  // dQ_i reuses the score columns once the scores have been consumed
+  // D = 64 leaves room for a private dQ tile, so the next S/dP can be issued while dQ is read out;
+  // D = 128 fills all 512 columns and dQ_i reuses the score columns once the scores have been consumed
+  constexpr bool kPrivateDq = (D == 64);
+  const uint32_t tm_dq = kPrivateDq ? tmem_base + 384 : tm_s;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -504,7 +509,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const int st = it % C::kStages;
         const uint32_t q_src = ring + st * C::kStageBytes, do_src = q_src + C::kTile;
         if (!(ok = mbar_wait(qdo_full0 + 8 * st, (it / C::kStages) & 1, wc, 33))) break;
-        if (it > 0) {  // the score columns still hold dQ of the previous tile until it has been read out
+        if (!kPrivateDq && it > 0) {  // the score columns still hold dQ of the previous tile until it has been read out
           if (!(ok = mbar_wait(dq_read, (it - 1) & 1, wc, 34))) break;
         }
         tc_fence_after();
@@ -535,6 +540,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
                    idesc_tt, (it > 0 || k > 0) ? 1u : 0u);
         }
         // dQ_i = dS K   (reduction over the 128 keys)
+        if (kPrivateDq && it > 0) {  // the private dQ tile of the previous query tile must have been read out
+          if (!(ok = mbar_wait(dq_read, (it - 1) & 1, wc, 34))) break;
+          tc_fence_after();
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           umma_f16(tm_dq, make_smem_desc(ds_smem + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
@@ -547,6 +556,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     }
   } else {
     const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;            // which 64 of the 128 key columns this warpgroup handles
     const int row = quad * 32 + lane;
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     bool ok = true;
@@ -560,45 +570,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const float dlt = q_valid ? p.delta[static_cast<long long>(head) * p.total_tokens + tok] : 0.f;
       if (!(ok = mbar_wait(sdp_full, it & 1, wc, 36))) break;
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld_32x32(tm_s + lane_sel + c * 32, rs);
-        tmem_ld_32x32(tm_dp + lane_sel + c * 32, rd);
-        tmem_ld_wait();
-        float pf[32], df[32];
+      uint32_t rs[64], rd[64];
+      tmem_ld_32x32(tm_s + lane_sel + half * 64, rs);
+      tmem_ld_32x32(tm_s + lane_sel + half * 64 + 32, rs + 32);
+      tmem_ld_32x32(tm_dp + lane_sel + half * 64, rd);
+      tmem_ld_32x32(tm_dp + lane_sel + half * 64 + 32, rd + 32);
+      tmem_ld_wait();
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const int kv = kv0 + c * 32 + x;
+      for (int v = 0; v < 8; ++v) {
+        float pf[8], df[8];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const int col = half * 64 + v * 8 + x;
+          const int kv = kv0 + col;
           const bool okk = q_valid && kv < seq_len && (!p.causal || kv <= q_rel);
-          const float pv = okk ? exp2f(__uint_as_float(rs[x]) * p.scale_log2 - lse2) : 0.f;
+          const float pv = okk ? exp2f(fmaf(__uint_as_float(rs[v * 8 + x]), p.scale_log2, -lse2)) : 0.f;
           pf[x] = pv;
-          df[x] = pv * (__uint_as_float(rd[x]) - dlt) * p.scale;
+          df[x] = pv * (__uint_as_float(rd[v * 8 + x]) - dlt) * p.scale;
         }
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          uint4 a, b;
-          a.x = pack2(pf[8 * v], pf[8 * v + 1]); a.y = pack2(pf[8 * v + 2], pf[8 * v + 3]);
-          a.z = pack2(pf[8 * v + 4], pf[8 * v + 5]); a.w = pack2(pf[8 * v + 6], pf[8 * v + 7]);
-          b.x = pack2(df[8 * v], df[8 * v + 1]); b.y = pack2(df[8 * v + 2], df[8 * v + 3]);
-          b.z = pack2(df[8 * v + 4], df[8 * v + 5]); b.w = pack2(df[8 * v + 6], df[8 * v + 7]);
-          const uint32_t off = swz_chunk_offset(row, c * 4 + v);
-          *reinterpret_cast<uint4*>(p_ptr + off) = a;
-          *reinterpret_cast<uint4*>(ds_ptr + off) = b;
-        }
+        uint4 a, b;
+        a.x = pack2(pf[0], pf[1]); a.y = pack2(pf[2], pf[3]); a.z = pack2(pf[4], pf[5]); a.w = pack2(pf[6], pf[7]);
+        b.x = pack2(df[0], df[1]); b.y = pack2(df[2], df[3]); b.z = pack2(df[4], df[5]); b.w = pack2(df[6], df[7]);
+        const uint32_t off = swz_chunk_offset(row, half * 8 + v);
+        *reinterpret_cast<uint4*>(p_ptr + off) = a;
+        *reinterpret_cast<uint4*>(ds_ptr + off) = b;
       }
       tc_fence_before();
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      // dQ tile -> global accumulator
+      // dQ tile -> global accumulator (each warpgroup takes half of the head dimension)
       if (!(ok = mbar_wait(dq_full, it & 1, wc, 37))) break;
       tc_fence_after();
-      float* dq_row = p.dq_acc + (tok * p.n_q + head) * D;
+      float* dq_row = p.dq_acc + (tok * p.n_q + head) * D + half * (D / 2);
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(tm_dq + lane_sel + c * 32, r);
+        tmem_ld_32x32(tm_dq + lane_sel + half * (D / 2) + c * 32, r);
         tmem_ld_wait();
         if (q_valid) {
 #pragma unroll
@@ -611,37 +619,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_read);
     }
-    // dK / dV of this key tile
+    // dK / dV of this key tile: one warpgroup writes dV, the other dK
     if (ok) ok = mbar_wait(dkv_full, 0, wc, 38);
     if (ok) {
       tc_fence_after();
       const int kv_rel = kv0 + row;
       const bool kv_valid = kv_rel < seq_len;
       const long long off = (static_cast<long long>(seq_start + kv_rel) * p.n_kv + kv_head) * D;
+      __nv_bfloat16* dst = (half == 0 ? p.dv : p.dk) + off;
+      const uint32_t src = (half == 0 ? tm_dv : tm_dk) + lane_sel;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* dst = (which == 0 ? p.dv : p.dk) + off;
-        const uint32_t src = (which == 0 ? tm_dv : tm_dk) + lane_sel;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          if (total_iters > 0) {
-            tmem_ld_32x32(src + c * 32, r);
-            tmem_ld_wait();
-          } else {
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        if (total_iters > 0) {
+          tmem_ld_32x32(src + c * 32, r);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-            for (int x = 0; x < 32; ++x) r[x] = 0;
-          }
-          if (kv_valid) {
+          for (int x = 0; x < 32; ++x) r[x] = 0;
+        }
+        if (kv_valid) {
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 o;
-              o.x = pack2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
-              o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-              o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-              o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-              *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
-            }
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack2(__uint_as_float(r[8 * v]), __uint_as_float(r[8 * v + 1]));
+            o.y = pack2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+            o.z = pack2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+            o.w = pack2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+            *reinterpret_cast<uint4*>(dst + c * 32 + v * 8) = o;
           }
         }
       }
@@ -777,9 +782,9 @@ cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void*
   if (attr_err != cudaSuccess) return attr_err;
   dim3 grid((total_tokens + 127) / 128 + num_seqs, n_kv);
   if (head_dim == 64)
-    attn_bwd_kernel<64><<<grid, 192, BwdCfg<64>::kSmem, stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<64><<<grid, kBwdThreads, BwdCfg<64>::kSmem, stream>>>(tq, tk, tv, tdo, p);
   else
-    attn_bwd_kernel<128><<<grid, 192, BwdCfg<128>::kSmem, stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<128><<<grid, kBwdThreads, BwdCfg<128>::kSmem, stream>>>(tq, tk, tv, tdo, p);
   const long long n8 = static_cast<long long>(total_tokens) * n_q * head_dim / 8;
   long long g = (n8 + 255) / 256;
   if (g > sm_count * 16) g = sm_count * 16;
