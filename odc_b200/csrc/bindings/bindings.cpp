@@ -264,7 +264,8 @@ Tensor kernel_status() {
   return gemm_status(dev);
 }
 
-void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional<Tensor> bias, bool accumulate) {
+void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional<Tensor> bias, bool accumulate,
+          c10::optional<Tensor> residual) {
   c10::cuda::CUDAGuard g(a.device());
   odc::bind_device(a.get_device());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2, "gemm: 2-D operands");
@@ -289,9 +290,17 @@ void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional
     TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N && bias->is_contiguous(), "gemm: bias bf16 [N]");
     bias_ptr = bias->data_ptr();
   }
+  const void* res_ptr = nullptr;
+  long long ldr = 0;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == M &&
+                    residual->size(1) == N && residual->stride(1) == 1, "gemm: residual bf16 [M,N]");
+    res_ptr = residual->data_ptr();
+    ldr = residual->stride(0);
+  }
   cudaError_t e = odc::gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), kind_of(c.scalar_type()), bias_ptr, M, N, K,
                                  lay, accumulate, a.stride(0), b.stride(0), c.stride(0),
-                                 gemm_status(a.get_device()).data_ptr<int>(), sm_count(), cur_stream());
+                                 gemm_status(a.get_device()).data_ptr<int>(), sm_count(), cur_stream(), res_ptr, ldr);
   TORCH_CHECK(e == cudaSuccess, "gemm(", layout, ") M=", M, " N=", N, " K=", K, " lda=", a.stride(0), " ldb=", b.stride(0),
               " ldc=", c.stride(0), " align(a,b,c)=", reinterpret_cast<uintptr_t>(a.data_ptr()) % 16, ",",
               reinterpret_cast<uintptr_t>(b.data_ptr()) % 16, ",", reinterpret_cast<uintptr_t>(c.data_ptr()) % 16, ": ",
@@ -361,7 +370,7 @@ std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seql
 }
 
 std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse,
-                                            Tensor cu_seqlens, int max_seqlen, bool causal, double scale) {
+                                            Tensor cu_seqlens, int max_seqlen, bool causal, double scale, bool fused_qkv) {
   c10::cuda::CUDAGuard g(q.device());
   odc::bind_device(q.get_device());
   const int T = q.size(0), hq = q.size(1), d = q.size(2), hkv = k.size(1);
@@ -369,16 +378,25 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Ten
   TORCH_CHECK(o.stride(2) == 1 && o.stride(1) == d, "attention bwd: o heads packed");
   TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == d && k.stride(2) == 1 && k.stride(1) == d && v.stride(2) == 1 &&
                   v.stride(1) == d && k.stride(0) == v.stride(0), "attention bwd: q/k/v layout");
-  auto dq = torch::empty({T, hq, d}, q.options());
-  auto dk = torch::empty({T, hkv, d}, q.options());
-  auto dv = torch::empty({T, hkv, d}, q.options());
+  Tensor dq, dk, dv;
+  if (fused_qkv) {
+    // one [T, (hq + 2 hkv) d] gradient; dq/dk/dv are column views of it, so slicing costs nothing in autograd
+    auto dqkv = torch::empty({T, int64_t(hq + 2 * hkv) * d}, q.options());
+    dq = dqkv.narrow(1, 0, int64_t(hq) * d).view({T, hq, d});
+    dk = dqkv.narrow(1, int64_t(hq) * d, int64_t(hkv) * d).view({T, hkv, d});
+    dv = dqkv.narrow(1, int64_t(hq + hkv) * d, int64_t(hkv) * d).view({T, hkv, d});
+  } else {
+    dq = torch::empty({T, hq, d}, q.options());
+    dk = torch::empty({T, hkv, d}, q.options());
+    dv = torch::empty({T, hkv, d}, q.options());
+  }
   auto delta = torch::empty({hq, T}, q.options().dtype(at::kFloat));
   auto dq_acc = torch::empty({T, hq, d}, q.options().dtype(at::kFloat));
   check(odc::attn_bwd(dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr<float>(),
                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), delta.data_ptr<float>(), dq_acc.data_ptr<float>(),
                       cu_seqlens.data_ptr<int>(), static_cast<int>(cu_seqlens.numel() - 1), T, max_seqlen, hq, hkv, d,
-                      q.stride(0), k.stride(0), o.stride(0), static_cast<float>(scale), causal,
-                      gemm_status(q.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+                      q.stride(0), k.stride(0), o.stride(0), dq.stride(0), dk.stride(0), static_cast<float>(scale),
+                      causal, gemm_status(q.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
         "attn_bwd");
   return {dq, dk, dv};
 }
@@ -408,7 +426,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_step", &adamw_step);
   m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
   m.def("sumsq", &sumsq);
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("layout"), py::arg("bias"),
+        py::arg("accumulate"), py::arg("residual") = py::none());
   m.def("gemm_wgrad_scatter", &gemm_wgrad_scatter);
   m.def("gemm_gather", &gemm_gather);
   m.def("attn_fwd", &attn_fwd);

@@ -47,7 +47,7 @@ cudaError_t launch_sumsq(const void* x, int kind, size_t n, float* out, int sm_c
 struct GemmPlan;
 cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const void* bias, int M, int N, int K,
                       int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
-                      int sm_count, cudaStream_t stream);
+                      int sm_count, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
 
 // ---- GEMMs fused with the on-demand primitives ---------------------------------------------------
 // dW[n_out, k_in] = dY[tokens, n_out]^T X[tokens, k_in]; row r of dW is added (x scale) into
@@ -71,7 +71,7 @@ cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float
 cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
                      void* dq, void* dk, void* dv, float* delta, float* dq_acc, const int* cu_seqlens, int num_seqs,
                      int total_tokens, int max_seqlen, int n_q, int n_kv, int head_dim, long long q_stride,
-                     long long kv_stride, long long o_stride, float scale, bool causal, int* status, int sm_count,
-                     cudaStream_t stream);
+                     long long kv_stride, long long o_stride, long long dq_stride, long long dkv_stride, float scale,
+                     bool causal, int* status, int sm_count, cudaStream_t stream);
 
 }  // namespace odc

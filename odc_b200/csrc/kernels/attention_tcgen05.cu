@@ -14,8 +14,8 @@
 //
 // Backward: a pre-pass computes delta = rowsum(dO * O); the main kernel owns one (128 keys, kv
 // head) tile, keeps dK and dV in TMEM across all query tiles and query heads of the group, and
-// recomputes P from the saved log-sum-exp.  dQ tiles are reduced into an fp32 buffer with vector
-// atomics and converted to bf16 by a post-pass.
+// recomputes P from the saved log-sum-exp.  dQ tiles are staged in shared memory as fp32 and added into a
+// global fp32 buffer by the TMA unit (bulk reduce-add), then converted to bf16 by a post-pass.
 //
 // The reference calls flash-attn 2 for this op (examples/llm_training/torch_fsdp2.py:85-103).
 #include <cuda.h>
@@ -380,8 +380,9 @@ struct BwdParams {
   const float* lse;    // [n_q, total_tokens]
   const float* delta;  // [n_q, total_tokens]
   float* dq_acc;       // [total_tokens, n_q, D] fp32, zero-initialised
-  __nv_bfloat16* dk;   // [total_tokens, n_kv, D]
+  __nv_bfloat16* dk;   // rows of n_kv * D values, dkv_stride elements apart
   __nv_bfloat16* dv;
+  long long dkv_stride;
   int total_tokens;
   float scale, scale_log2;
   int causal;
@@ -408,7 +409,7 @@ template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                const BwdParams p) {
+                const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
   using C = BwdCfg<D>;
   int seq, seq_start, seq_len, kv0;
   if (!locate_block(p.cu_seqlens, p.num_seqs, blockIdx.x, 128, &seq, &seq_start, &seq_len, &kv0)) return;
@@ -439,6 +440,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t dq_full = pds_full + 8;
   const uint32_t dq_read = dq_full + 8;
   const uint32_t dkv_full = dq_read + 8;
+  const uint32_t stg_ready = dkv_full + 8;  // dQ staging tile written by all compute warps
+  const uint32_t stg_free = stg_ready + 8;  // TMA has finished reading the staging tile
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::kStages + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -456,6 +459,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     mbar_init(dq_full, 1);
     mbar_init(dq_read, 8);
     mbar_init(dkv_full, 1);
+    mbar_init(stg_ready, 8);
+    mbar_init(stg_free, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -476,6 +481,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v); prefetch_tmap(&tmap_do);
+      prefetch_tmap(&tmap_dq);
       mbar_arrive_expect_tx(kv_full, 2 * C::kTile);
 #pragma unroll
       for (int s = 0; s < D / 64; ++s) {
@@ -570,6 +576,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const float dlt = q_valid ? p.delta[static_cast<long long>(head) * p.total_tokens + tok] : 0.f;
       if (!(ok = mbar_wait(sdp_full, it & 1, wc, 36))) break;
       tc_fence_after();
+      // the P/dS buffers double as the staging tile of the previous dQ reduction: wait until TMA has read it
+      if (it > 0) {
+        if (!(ok = mbar_wait(stg_free, (it - 1) & 1, wc, 39))) break;
+      }
       uint32_t rs[64], rd[64];
       tmem_ld_32x32(tm_s + lane_sel + half * 64, rs);
       tmem_ld_32x32(tm_s + lane_sel + half * 64 + 32, rs + 32);
@@ -599,33 +609,49 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      // dQ tile -> global accumulator (each warpgroup takes half of the head dimension)
+      // dQ tile -> fp32 staging in shared memory (over the consumed P/dS buffers) -> TMA reduce-add into the
+      // global accumulator; rows past the end of the sequence are staged as zeros
       if (!(ok = mbar_wait(dq_full, it & 1, wc, 37))) break;
       tc_fence_after();
-      float* dq_row = p.dq_acc + (tok * p.n_q + head) * D + half * (D / 2);
 #pragma unroll 1
       for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(tm_dq + lane_sel + half * (D / 2) + c * 32, r);
         tmem_ld_wait();
-        if (q_valid) {
+        const int box = half * (D / 64) + c;
 #pragma unroll
-          for (int v = 0; v < 8; ++v)
-            red_add_v4_gpu(dq_row + c * 32 + 4 * v, __uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
-                           __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        for (int v = 0; v < 8; ++v) {
+          uint4 o = q_valid ? make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]) : make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(p_ptr + box * 16384 + row * 128 + ((v ^ (row & 7)) << 4)) = o;
         }
       }
       tc_fence_before();
+      fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(dq_read);
+      if (lane == 0) {
+        mbar_arrive(stg_ready);
+        mbar_arrive(dq_read);
+      }
+      if (warp == 2 && lane == 0) {  // one thread hands the staged tile to the TMA unit and frees it once read
+        if (mbar_wait(stg_ready, it & 1, wc, 40)) {
+#pragma unroll
+          for (int b2 = 0; b2 < D / 32; ++b2)
+            tma_reduce_add_2d(&tmap_dq, p_smem + b2 * 16384, head * D + 32 * b2, seq_start + i * 128);
+          bulk_commit_group();
+          bulk_wait_group_read0();
+        }
+        mbar_arrive(stg_free);
+      }
+      __syncwarp();
     }
+    if (warp == 2 && lane == 0) bulk_wait_group0();
     // dK / dV of this key tile: one warpgroup writes dV, the other dK
     if (ok) ok = mbar_wait(dkv_full, 0, wc, 38);
     if (ok) {
       tc_fence_after();
       const int kv_rel = kv0 + row;
       const bool kv_valid = kv_rel < seq_len;
-      const long long off = (static_cast<long long>(seq_start + kv_rel) * p.n_kv + kv_head) * D;
+      const long long off = static_cast<long long>(seq_start + kv_rel) * p.dkv_stride + kv_head * D;
       __nv_bfloat16* dst = (half == 0 ? p.dv : p.dk) + off;
       const uint32_t src = (half == 0 ? tm_dv : tm_dk) + lane_sel;
 #pragma unroll 1
@@ -682,13 +708,17 @@ attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* _
   if (lane == 0) delta[static_cast<long long>(h) * total_tokens + t] = s;
 }
 
+// acc is dense [tokens, width] fp32; dq rows are dq_stride elements apart
 __global__ void __launch_bounds__(256)
-cast_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long n8) {
+cast_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long long n8, int width8,
+               long long dq_stride) {
   for (long long v = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; v < n8;
        v += static_cast<long long>(gridDim.x) * blockDim.x) {
     const float4 a = *reinterpret_cast<const float4*>(acc + v * 8);
     const float4 b = *reinterpret_cast<const float4*>(acc + v * 8 + 4);
-    *reinterpret_cast<uint4*>(dq + v * 8) =
+    const long long row = v / width8;
+    const int col = static_cast<int>(v % width8) * 8;
+    *reinterpret_cast<uint4*>(dq + row * dq_stride + col) =
         make_uint4(pack2(a.x, a.y), pack2(a.z, a.w), pack2(b.x, b.y), pack2(b.z, b.w));
   }
 }
@@ -742,14 +772,15 @@ namespace odc {
 cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* o, const float* lse,
                      void* dq, void* dk, void* dv, float* delta, float* dq_acc, const int* cu_seqlens, int num_seqs,
                      int total_tokens, int max_seqlen, int n_q, int n_kv, int head_dim, long long q_stride,
-                     long long kv_stride, long long o_stride, float scale, bool causal, int* status, int sm_count,
-                     cudaStream_t stream) {
+                     long long kv_stride, long long o_stride, long long dq_stride, long long dkv_stride, float scale,
+                     bool causal, int* status, int sm_count, cudaStream_t stream) {
   (void)max_seqlen;
   if (total_tokens == 0 || num_seqs == 0) return cudaSuccess;
   if (head_dim != 64 && head_dim != 128) return cudaErrorInvalidValue;
   if (n_q % n_kv != 0) return cudaErrorInvalidValue;
-  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8)) return cudaErrorInvalidValue;
-  // dout, dq are contiguous [T, n_q, D]; dk, dv contiguous [T, n_kv, D]
+  if ((q_stride % 8) || (kv_stride % 8) || (o_stride % 8) || (dq_stride % 8) || (dkv_stride % 8))
+    return cudaErrorInvalidValue;
+  // dout is contiguous [T, n_q, D]; dq / dk / dv rows may be strided (views of one fused qkv gradient)
   const long long do_stride = static_cast<long long>(n_q) * head_dim;
   {
     const long long warps = static_cast<long long>(total_tokens) * n_q;
@@ -760,7 +791,10 @@ cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void*
   }
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, sizeof(float) * static_cast<size_t>(total_tokens) * n_q * head_dim, stream);
   if (e != cudaSuccess) return e;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
+  if (!encode_tile_map_2d_f32(&tdq, dq_acc, static_cast<uint64_t>(n_q) * head_dim, total_tokens,
+                              static_cast<uint64_t>(n_q) * head_dim * 4, 32, 128))
+    return cudaErrorInvalidValue;
   if (!encode_tile_map_2d(&tq, q, static_cast<uint64_t>(n_q) * head_dim, total_tokens, q_stride * 2, 64, 128) ||
       !encode_tile_map_2d(&tk, k, static_cast<uint64_t>(n_kv) * head_dim, total_tokens, kv_stride * 2, 64, 128) ||
       !encode_tile_map_2d(&tv, v, static_cast<uint64_t>(n_kv) * head_dim, total_tokens, kv_stride * 2, 64, 128) ||
@@ -770,7 +804,7 @@ cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void*
   p.cu_seqlens = cu_seqlens; p.num_seqs = num_seqs; p.n_q = n_q; p.n_kv = n_kv; p.lse = lse; p.delta = delta;
   p.dq_acc = dq_acc; p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   p.total_tokens = total_tokens; p.scale = scale; p.scale_log2 = scale * kLog2e; p.causal = causal ? 1 : 0;
-  p.status = status;
+  p.status = status; p.dkv_stride = dkv_stride;
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -782,13 +816,14 @@ cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void*
   if (attr_err != cudaSuccess) return attr_err;
   dim3 grid((total_tokens + 127) / 128 + num_seqs, n_kv);
   if (head_dim == 64)
-    attn_bwd_kernel<64><<<grid, kBwdThreads, BwdCfg<64>::kSmem, stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<64><<<grid, kBwdThreads, BwdCfg<64>::kSmem, stream>>>(tq, tk, tv, tdo, tdq, p);
   else
-    attn_bwd_kernel<128><<<grid, kBwdThreads, BwdCfg<128>::kSmem, stream>>>(tq, tk, tv, tdo, p);
+    attn_bwd_kernel<128><<<grid, kBwdThreads, BwdCfg<128>::kSmem, stream>>>(tq, tk, tv, tdo, tdq, p);
   const long long n8 = static_cast<long long>(total_tokens) * n_q * head_dim / 8;
   long long g = (n8 + 255) / 256;
   if (g > sm_count * 16) g = sm_count * 16;
-  cast_dq_kernel<<<static_cast<int>(g), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8);
+  cast_dq_kernel<<<static_cast<int>(g), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), n8,
+                                                          n_q * head_dim / 8, dq_stride);
   return cudaGetLastError();
 }
 

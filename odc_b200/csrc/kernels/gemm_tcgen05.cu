@@ -39,7 +39,7 @@ using namespace gemm_impl;
 // ------------------------------------------------------------------------------------------------
 cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const void* bias, int M, int N, int K,
                       int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
-                      int sm_count, cudaStream_t stream) {
+                      int sm_count, cudaStream_t stream, const void* residual, long long ldr) {
   if (M == 0 || N == 0) return cudaSuccess;
   if (K == 0) return cudaErrorInvalidSymbol;
   const bool a_mn = (layout == 2);
@@ -79,6 +79,11 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.status = status;
+  if (residual != nullptr) {
+    if (c_kind != kBF16 || (ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15)) return cudaErrorInvalidValue;
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.ldr = ldr;
+  }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
   gemm_bf16_kernel<kModePlain><<<grid, Roles<kModePlain>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, p);

@@ -39,6 +39,8 @@ struct Params {
   int a_mn, b_mn;  // operand is MN-major
   int tiles_m, tiles_n;
   int* status;
+  const __nv_bfloat16* residual;  // optional [M, N] bf16 added to a bf16 output (row pitch ldr)
+  long long ldr;
   // --- kModeScatter: the epilogue adds the tile into the owners' fp32 accumulators ---
   const long long* acc_ptrs;   // [nranks] base address of the accumulator on each owner
   const long long* ctr_ptrs;   // [nranks] arrival counters
@@ -304,9 +306,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           } else {
             __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(p.c) + static_cast<long long>(row) * p.ldc + col0;
+            const __nv_bfloat16* rrow =
+                p.residual ? p.residual + static_cast<long long>(row) * p.ldr + col0 : nullptr;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               if (col0 + v * 8 < p.N) {
+                if (rrow != nullptr) {
+                  const uint4 res = *reinterpret_cast<const uint4*>(rrow + 8 * v);
+                  const uint32_t o[4] = {res.x, res.y, res.z, res.w};
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    f[8 * v + 2 * i] += __uint_as_float(o[i] << 16);
+                    f[8 * v + 2 * i + 1] += __uint_as_float(o[i] & 0xffff0000u);
+                  }
+                }
                 if (p.accumulate) {
                   const uint4 old = *reinterpret_cast<const uint4*>(crow + 8 * v);
                   const uint32_t o[4] = {old.x, old.y, old.z, old.w};

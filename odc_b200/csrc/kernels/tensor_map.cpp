@@ -48,6 +48,19 @@ bool encode_tile_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint
   return r == CUDA_SUCCESS;
 }
 
+bool encode_tile_map_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                            uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  EncodeFn fn = encoder();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_pitch_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool encode_tile_map_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                         uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0, uint32_t box1, uint32_t box2) {
   EncodeFn fn = encoder();

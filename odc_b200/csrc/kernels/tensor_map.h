@@ -10,6 +10,10 @@ namespace odc {
 bool encode_tile_map_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
                         uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
 
+// 2-D row-major fp32 tensor, tiles of box_inner x box_outer elements (box_inner * 4 bytes == 128 for the swizzle).
+bool encode_tile_map_2d_f32(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                            uint64_t row_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+
 // 3-D bf16 tensor [d2, d1, d0] (d0 innermost, contiguous) with byte pitches for d1 and d2.
 bool encode_tile_map_3d(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
                         uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0, uint32_t box1, uint32_t box2);

@@ -98,17 +98,14 @@ class Attention(nn.Module):
         self.bqkv = nn.Parameter(torch.zeros(cfg.qkv_dim)) if cfg.qkv_bias else None
         self.wo = nn.Parameter(torch.empty(cfg.hidden_size, cfg.num_heads * cfg.head_dim))
 
-    def forward(self, x, position_ids, cu_seqlens, max_seqlen):
+    def forward(self, x, position_ids, cu_seqlens, max_seqlen, residual=None):
         c = self.cfg
         T = x.shape[0]
         qkv = ops.linear(x, self.wqkv, self.bqkv)
         qkv = ops.rope_qkv(qkv, position_ids, c.num_heads, c.num_kv_heads, c.head_dim, c.rope_theta)
-        nq, nk = c.num_heads * c.head_dim, c.num_kv_heads * c.head_dim
-        q = qkv[:, :nq].view(T, c.num_heads, c.head_dim)
-        k = qkv[:, nq:nq + nk].view(T, c.num_kv_heads, c.head_dim)
-        v = qkv[:, nq + nk:].view(T, c.num_kv_heads, c.head_dim)
-        o = ops.varlen_attention(q, k, v, cu_seqlens, max_seqlen, causal=True)
-        return ops.linear(o.reshape(T, nq), self.wo)
+        nq = c.num_heads * c.head_dim
+        o = ops.varlen_attention_qkv(qkv, c.num_heads, c.num_kv_heads, c.head_dim, cu_seqlens, max_seqlen, causal=True)
+        return ops.linear(o.reshape(T, nq), self.wo, residual=residual)
 
 
 class MLP(nn.Module):
@@ -117,8 +114,8 @@ class MLP(nn.Module):
         self.w_gate_up = nn.Parameter(torch.empty(2 * cfg.intermediate_size, cfg.hidden_size))
         self.w_down = nn.Parameter(torch.empty(cfg.hidden_size, cfg.intermediate_size))
 
-    def forward(self, x):
-        return ops.linear(ops.swiglu(ops.linear(x, self.w_gate_up)), self.w_down)
+    def forward(self, x, residual=None):
+        return ops.linear(ops.swiglu(ops.linear(x, self.w_gate_up)), self.w_down, residual=residual)
 
 
 class DecoderLayer(nn.Module):
@@ -130,8 +127,8 @@ class DecoderLayer(nn.Module):
         self.mlp = MLP(cfg)
 
     def forward(self, x, position_ids, cu_seqlens, max_seqlen):
-        x = x + self.attn(self.attn_norm(x), position_ids, cu_seqlens, max_seqlen)
-        return x + self.mlp(self.mlp_norm(x))
+        x = self.attn(self.attn_norm(x), position_ids, cu_seqlens, max_seqlen, residual=x)
+        return self.mlp(self.mlp_norm(x), residual=x)
 
 
 class DecoderLM(nn.Module):

@@ -51,7 +51,7 @@ def attn_backend() -> str:
 # ------------------------------------------------------------------------------------------
 def gemm(a: torch.Tensor, b: torch.Tensor, layout: str = "nt", out: Optional[torch.Tensor] = None,
          bias: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None,
-         accumulate: bool = False) -> torch.Tensor:
+         accumulate: bool = False, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     if layout == "nt":
         M, N = a.shape[0], b.shape[0]
     elif layout == "nn":
@@ -69,23 +69,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, layout: str = "nt", out: Optional[tor
         r = (A.float() @ B.float()) if not a.is_cuda else (A @ B)
         if bias is not None:
             r = r + bias
+        if residual is not None:
+            r = r + residual
         if accumulate:
             out += r.to(out.dtype)
         else:
             out.copy_(r)
         return out
-    _ext().gemm(a, b, out, layout, bias, accumulate)
+    _ext().gemm(a, b, out, layout, bias, accumulate, residual)
     _count()
     return out
 
 
 class _Linear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, bias):
+    def forward(ctx, x, w, bias, residual):
         ctx.save_for_backward(x, w)
         ctx.has_bias = bias is not None
         x2 = x.reshape(-1, x.shape[-1])
-        y = gemm(x2, w, "nt", bias=bias)
+        res2 = None if residual is None else residual.reshape(-1, w.shape[0])
+        y = gemm(x2, w, "nt", bias=bias, residual=res2)  # the residual is added in the GEMM epilogue
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -102,13 +105,16 @@ class _Linear(torch.autograd.Function):
             dw = gemm(dy2, x2, "tn", out_dtype=w.dtype)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.float().sum(0).to(dy.dtype)
-        return dx, dw, db
+        dres = dy if ctx.needs_input_grad[3] else None
+        return dx, dw, db, dres
 
 
-def linear(x, w, bias=None):
+def linear(x, w, bias=None, residual=None):
+    """``x @ w.T (+ bias) (+ residual)``; on CUDA bias and residual are fused into the GEMM epilogue."""
     if not x.is_cuda:
-        return ref.linear(x, w, bias)
-    return _Linear.apply(x, w, bias)
+        y = ref.linear(x, w, bias)
+        return y if residual is None else y + residual
+    return _Linear.apply(x, w, bias, residual)
 
 
 # ------------------------------------------------------------------------------------------
@@ -206,9 +212,58 @@ class _VarlenAttention(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, lse, cu_seqlens = ctx.saved_tensors
         max_seqlen, causal, scale = ctx.cfg
-        dq, dk, dv = _ext().attn_bwd(do.contiguous(), q, k, v, o, lse, cu_seqlens, max_seqlen, causal, scale)
+        dq, dk, dv = _ext().attn_bwd(do.contiguous(), q, k, v, o, lse, cu_seqlens, max_seqlen, causal, scale, False)
         _count(3)
         return dq, dk, dv, None, None, None, None
+
+
+class _VarlenAttentionQKV(torch.autograd.Function):
+    """Attention straight on a fused ``[T, (Hq+2Hkv)*D]`` projection: q/k/v are column views in forward and the
+    backward kernels write dq/dk/dv into column views of ONE gradient tensor, so autograd never materialises
+    zero-padded slices."""
+
+    @staticmethod
+    def forward(ctx, qkv, n_q, n_kv, head_dim, cu_seqlens, max_seqlen, causal, scale):
+        T = qkv.shape[0]
+        nq, nk = n_q * head_dim, n_kv * head_dim
+        q = qkv[:, :nq].view(T, n_q, head_dim)
+        k = qkv[:, nq:nq + nk].view(T, n_kv, head_dim)
+        v = qkv[:, nq + nk:].view(T, n_kv, head_dim)
+        o, lse = _ext().attn_fwd(q, k, v, cu_seqlens, max_seqlen, causal, scale)
+        _count()
+        ctx.save_for_backward(qkv, o, lse, cu_seqlens)
+        ctx.cfg = (n_q, n_kv, head_dim, max_seqlen, causal, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        qkv, o, lse, cu_seqlens = ctx.saved_tensors
+        n_q, n_kv, head_dim, max_seqlen, causal, scale = ctx.cfg
+        T = qkv.shape[0]
+        nq, nk = n_q * head_dim, n_kv * head_dim
+        q = qkv[:, :nq].view(T, n_q, head_dim)
+        k = qkv[:, nq:nq + nk].view(T, n_kv, head_dim)
+        v = qkv[:, nq + nk:].view(T, n_kv, head_dim)
+        dq, _, _ = _ext().attn_bwd(do.contiguous(), q, k, v, o, lse, cu_seqlens, max_seqlen, causal, scale, True)
+        _count(3)
+        dqkv = dq
+        while dqkv._base is not None:  # dq is a column view of the fused gradient allocated by the kernel wrapper
+            dqkv = dqkv._base
+        return dqkv, None, None, None, None, None, None, None
+
+
+def varlen_attention_qkv(qkv, n_q: int, n_kv: int, head_dim: int, cu_seqlens, max_seqlen: int, causal: bool = True,
+                         scale: Optional[float] = None):
+    """Causal attention on a fused qkv activation ``[T, (Hq+2Hkv)*D]``; returns ``[T, Hq, D]``."""
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    T = qkv.shape[0]
+    if qkv.is_cuda and attn_backend() == "native":
+        return _VarlenAttentionQKV.apply(qkv, n_q, n_kv, head_dim, cu_seqlens, max_seqlen, causal, scale)
+    nq, nk = n_q * head_dim, n_kv * head_dim
+    q = qkv[:, :nq].view(T, n_q, head_dim)
+    k = qkv[:, nq:nq + nk].view(T, n_kv, head_dim)
+    v = qkv[:, nq + nk:].view(T, n_kv, head_dim)
+    return varlen_attention(q, k, v, cu_seqlens, max_seqlen, causal, scale)
 
 
 def varlen_attention(q, k, v, cu_seqlens, max_seqlen: int, causal: bool = True, scale: Optional[float] = None):

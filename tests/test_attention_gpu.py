@@ -56,3 +56,22 @@ def test_attention_backward(lens, hq, hkv, d):
         err = (got.float() - exp).abs().max().item()
         ref_mag = exp.abs().max().item()
         assert err <= 3e-2 * max(ref_mag, 1.0), (name, err, ref_mag)
+
+
+def test_attention_on_fused_qkv_matches_reference():
+    from odc_b200 import ops
+    from odc_b200.ops import reference as ref
+    lens, hq, hkv, d = [300, 129, 700], 8, 2, 64
+    T = sum(lens)
+    cu = torch.tensor([0] + lens, device="cuda").cumsum(0).int()
+    qkv = torch.randn(T, (hq + 2 * hkv) * d, device="cuda").bfloat16().requires_grad_()
+    o = ops.varlen_attention_qkv(qkv, hq, hkv, d, cu, max(lens))
+    do = torch.randn_like(o)
+    o.backward(do)
+    x = qkv.detach().float().requires_grad_()
+    q, k, v = x.split([hq * d, hkv * d, hkv * d], dim=-1)
+    want = ref.varlen_attention(q.reshape(T, hq, d), k.reshape(T, hkv, d), v.reshape(T, hkv, d), cu.cpu(), True, d ** -0.5)
+    want.backward(do.float())
+    torch.testing.assert_close(o.float(), want, rtol=2e-2, atol=2e-2)
+    err = (qkv.grad.float() - x.grad).abs().max().item()
+    assert err <= 3e-2 * max(x.grad.abs().max().item(), 1.0), err

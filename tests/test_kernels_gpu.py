@@ -272,3 +272,16 @@ def test_gemm_gather_emulated_ranks(ext, world, M, N, K):
     assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
     assert torch.equal(w_local, W[:N])
     torch.testing.assert_close(y.float(), x.float() @ W[:N].float().t() + bias.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+
+
+def test_linear_with_fused_residual():
+    from odc_b200 import ops
+    x = torch.randn(300, 512, device="cuda").bfloat16().requires_grad_()
+    w = (0.05 * torch.randn(768, 512, device="cuda")).bfloat16().requires_grad_()
+    res = torch.randn(300, 768, device="cuda").bfloat16().requires_grad_()
+    y = ops.linear(x, w, None, residual=res)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    want = x.detach().float() @ w.detach().float().t() + res.detach().float()
+    torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=5e-2)
+    assert torch.equal(res.grad, dy)
