@@ -56,7 +56,7 @@ cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_
   p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.scale = scale; p.done_slot = done_slot;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_bf16_kernel<kModeScatter><<<grid, Roles<kModeScatter>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, p);
+  gemm_bf16_kernel<kModeScatter><<<grid, Roles<kModeScatter>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, ta, p);
   return cudaGetLastError();
 }
 
@@ -80,6 +80,8 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   CUtensorMap ta, tb;
   if (!encode_tile_map_2d(&ta, x, K, M, ldx * 2, 64, BM)) return cudaErrorInvalidValue;
   if (!encode_tile_map_2d(&tb, w_local, K, N, static_cast<uint64_t>(K) * 2, 64, BN)) return cudaErrorInvalidValue;
+  CUtensorMap tc;
+  if (!encode_tile_map_2d(&tc, y, N, M, ldy * 2, 64, BM)) return cudaErrorInvalidValue;
   Params p{};
   p.c = y;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -96,7 +98,7 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   if (e != cudaSuccess) return e;
   // every CTA also fetches, so use the whole machine even when there are few tiles
   const int grid = sm_count;
-  gemm_bf16_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, p);
+  gemm_bf16_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, p);
   return cudaGetLastError();
 }
 

@@ -68,6 +68,13 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
   } else {
     if (!encode_tile_map_2d(&tb, b, N, K, ldb * 2, 64, 64)) return cudaErrorInvalidTexture;
   }
+  CUtensorMap tc;
+  if (c_kind == kF32) {
+    if (!encode_tile_map_2d_f32(&tc, c, N, M, ldc * 4, 32, BM)) return cudaErrorInvalidValue;
+  } else {
+    if (accumulate) return cudaErrorNotSupported;  // accumulation is offered for fp32 outputs
+    if (!encode_tile_map_2d(&tc, c, N, M, ldc * 2, 64, BM)) return cudaErrorInvalidValue;
+  }
   Params p{};
   p.c = c;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -86,7 +93,7 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_bf16_kernel<kModePlain><<<grid, Roles<kModePlain>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, p);
+  gemm_bf16_kernel<kModePlain><<<grid, Roles<kModePlain>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, p);
   return cudaGetLastError();
 }
 

@@ -25,7 +25,8 @@ constexpr int kThreads = 192;
 constexpr int kATile = BM * BK * 2;           // 16 KiB
 constexpr int kBTile = BN * BK * 2;           // 32 KiB
 constexpr int kStageBytes = kATile + kBTile;  // 48 KiB
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kStagingBytes = 128 * 128;    // one output box: 128 rows x 128 bytes (64 bf16 or 32 fp32 columns)
+constexpr int kSmemBytes = kStages * kStageBytes + 2 * kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint64_t kWaitBudgetNs = 4000000000ull;
 
@@ -74,18 +75,22 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 template <int kMode>
 __global__ void __launch_bounds__(Roles<kMode>::kThreadsTotal, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const Params p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* smem = smem_raw + (base - raw);
   // barrier block lives after the stage ring
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+  uint8_t* staging = smem + kStages * kStageBytes;               // 2 output boxes for the TMA-store epilogue
+  const uint32_t staging_u32 = base + kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + 2 * kStagingBytes);
   const uint32_t full0 = smem_u32(bars);                    // [kStages]
   const uint32_t empty0 = full0 + 8 * kStages;              // [kStages]
   const uint32_t tfull0 = empty0 + 8 * kStages;             // [2]
   const uint32_t tempty0 = tfull0 + 16;                     // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  const uint32_t sready0 = tempty0 + 16;                    // [2] staging box written by all epilogue warps
+  const uint32_t sfree0 = sready0 + 16;                     // [2] staging box read by the TMA unit
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -100,6 +105,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull0 + 8 * a, 1);
       mbar_init(tempty0 + 8 * a, Roles<kMode>::kEpilogueWarps);  // one arrival per epilogue warp
+      mbar_init(sready0 + 8 * a, 4);
+      mbar_init(sfree0 + 8 * a, 1);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -253,6 +260,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     constexpr int kColGroups = Roles<kMode>::kEpilogueWarps / 4;   // warps sharing a lane quadrant split the columns
     const int col_group = (warp - 2) / 4;
     uint32_t local_tile = 0;
+    uint32_t box_ctr = 0;  // output boxes staged so far by this CTA (selects the staging buffer)
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       const int m0 = (tile % p.tiles_m) * BM;
@@ -264,6 +272,77 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int row = m0 + quad * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      if constexpr (kMode != kModeScatter) {
+        // Output through shared memory and the TMA unit: each 128-byte piece of an output row is written to a
+        // swizzled staging box, and one thread stores (or reduce-adds) the whole 128-row box.  Rows and columns
+        // outside the matrix are clipped by the tensor map.
+        const int cols_per_box = p.c_is_f32 ? 32 : 64;
+        const int n_boxes = BN / cols_per_box;
+        const int my_row = quad * 32 + lane;
+#pragma unroll 1
+        for (int bx = 0; bx < n_boxes; ++bx) {
+          uint32_t r[64];
+          tmem_ld_32x32(t_row + bx * cols_per_box, r);
+          if (!p.c_is_f32) tmem_ld_32x32(t_row + bx * cols_per_box + 32, r + 32);
+          tmem_ld_wait();
+          const int col0 = n0 + bx * cols_per_box;
+          if (col0 >= p.N) continue;
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i)
+              if (i < cols_per_box && col0 + i < p.N)
+                r[i] = __float_as_uint(__uint_as_float(r[i]) + __bfloat162float(p.bias[col0 + i]));
+          }
+          const int buf = static_cast<int>(box_ctr & 1u);
+          const uint32_t use = box_ctr >> 1;
+          if (use >= 1) {
+            if (!(ok = mbar_wait(sfree0 + 8 * buf, (use - 1) & 1, wc, 6))) break;
+          }
+          uint8_t* srow = staging + buf * kStagingBytes + my_row * 128;
+          if (p.c_is_f32) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              *reinterpret_cast<uint4*>(srow + ((v ^ (my_row & 7)) << 4)) =
+                  make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+          } else {
+            const __nv_bfloat16* rrow = (p.residual != nullptr && row_ok)
+                                            ? p.residual + static_cast<long long>(row) * p.ldr + col0 : nullptr;
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * v + i]);
+              if (rrow != nullptr && col0 + 8 * v < p.N) {
+                const uint4 res = *reinterpret_cast<const uint4*>(rrow + 8 * v);
+                const uint32_t o[4] = {res.x, res.y, res.z, res.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  f[2 * i] += __uint_as_float(o[i] << 16);
+                  f[2 * i + 1] += __uint_as_float(o[i] & 0xffff0000u);
+                }
+              }
+              *reinterpret_cast<uint4*>(srow + ((v ^ (my_row & 7)) << 4)) =
+                  make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
+            }
+          }
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(sready0 + 8 * buf);
+          if (warp == 2 && lane == 0) {
+            if (mbar_wait(sready0 + 8 * buf, use & 1, wc, 7)) {
+              if (p.accumulate) tma_reduce_add_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
+              else tma_store_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
+              bulk_commit_group();
+              if (box_ctr >= 1) {
+                bulk_wait_group_read1();             // the previous box has been read: its buffer is free again
+                mbar_arrive(sfree0 + 8 * (buf ^ 1));
+              }
+            }
+          }
+          ++box_ctr;
+        }
+        if (!ok) break;
+      } else {
 #pragma unroll 1
       for (int c = col_group * (BN / 32 / kColGroups); c < (col_group + 1) * (BN / 32 / kColGroups); ++c) {
         uint32_t r[32];
@@ -340,11 +419,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
       }
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
     }
     if constexpr (kMode == kModeScatter) __threadfence_system();  // this thread's remote reductions are out
+    if (kMode != kModeScatter && warp == 2 && lane == 0) bulk_wait_group0();  // all output boxes are in memory
   }
 
   // ---------------------------------------------------------------------- teardown
