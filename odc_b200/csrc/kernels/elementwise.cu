@@ -59,37 +59,68 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // ------------------------------------------------------------------------- RMSNorm ----------
+// A row is handled by R warps (R = 1 up to 2048 columns, 2 up to 4096, 4 up to 8192); a lane keeps up to 8
+// 16-byte pieces of the row in registers with all loads in flight at once.  With R = 1 the row statistics
+// need only warp shuffles and no block-wide barrier sits on the critical path.
 constexpr int kNormThreads = 256;
-constexpr int kNormMaxVec = 4;  // cols <= 256 * 8 * 4 = 8192 stay in registers
+constexpr int kNormWarps = kNormThreads / 32;
+constexpr int kNormVec = 8;
 
+// sum over the R warps that share a row (R > 1 only); every thread of the CTA must call it
+template <int R>
+__device__ __forceinline__ float row_sum(float v, float* red, int warp, int lane) {
+  v = warp_sum(v);
+  if constexpr (R == 1) return v;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int first = warp - warp % R;
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < R; ++i) t += red[first + i];
+  return t;
+}
+
+template <int R>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16* __restrict__ y,
                    float* __restrict__ rstd_out, int rows, int cols, float eps) {
-  __shared__ float red[32];
+  __shared__ float red[kNormWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = warp % R;                       // which part of the row this warp covers
+  constexpr int kRowsPerIter = kNormWarps / R;
   const int nvec = cols / 8;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * cols);
-    uint4 xv[kNormMaxVec];
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  const int iters = (rows + gridDim.x * kRowsPerIter - 1) / (gridDim.x * kRowsPerIter);
+  for (int it = 0; it < iters; ++it) {
+    const int row = (it * gridDim.x + blockIdx.x) * kRowsPerIter + warp / R;
+    const bool live = row < rows;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(live ? row : 0) * cols);
+    uint4 xv[kNormVec];
     float ss = 0.f;
 #pragma unroll
-    for (int k = 0; k < kNormMaxVec; ++k) {
-      const int v = threadIdx.x + k * kNormThreads;
-      if (v < nvec) {
-        xv[k] = xr[v];
+    for (int k = 0; k < kNormVec; ++k) {
+      const int v = (sub * kNormVec + k) * 32 + lane;
+      if (live && v < nvec) xv[k] = xr[v];
+    }
+#pragma unroll
+    for (int k = 0; k < kNormVec; ++k) {
+      const int v = (sub * kNormVec + k) * 32 + lane;
+      if (live && v < nvec) {
         float f[8];
         unpack8(xv[k], f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
       }
     }
-    ss = block_sum(ss, red);
+    ss = row_sum<R>(ss, red, warp, lane);
+    if (!live) continue;
     const float rstd = rsqrtf(ss / cols + eps);
-    if (threadIdx.x == 0) rstd_out[row] = rstd;
+    if (lane == 0 && sub == 0) rstd_out[row] = rstd;
     uint4* yr = reinterpret_cast<uint4*>(y + size_t(row) * cols);
-    const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
-    for (int k = 0; k < kNormMaxVec; ++k) {
-      const int v = threadIdx.x + k * kNormThreads;
+    for (int k = 0; k < kNormVec; ++k) {
+      const int v = (sub * kNormVec + k) * 32 + lane;
       if (v < nvec) {
         float f[8], g[8];
         unpack8(xv[k], f);
@@ -102,31 +133,48 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   }
 }
 
-// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x));  dw partial per CTA in registers
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)).  Each lane accumulates dw for its own columns in
+// registers over all rows it handles; the warps of a CTA then combine through shared memory and the CTA
+// writes one row of partial sums.
+template <int R>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                    const float* __restrict__ rstd_in, bf16* __restrict__ dx, float* __restrict__ partial, int rows,
                    int cols) {
-  __shared__ float red[32];
+  extern __shared__ float dw_smem[];  // [cols]
+  __shared__ float red[kNormWarps];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = warp % R;
+  constexpr int kRowsPerIter = kNormWarps / R;
   const int nvec = cols / 8;
-  float dw[kNormMaxVec][8];
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_smem[c] = 0.f;
+  float dw[kNormVec][8];
 #pragma unroll
-  for (int k = 0; k < kNormMaxVec; ++k)
+  for (int k = 0; k < kNormVec; ++k)
 #pragma unroll
     for (int i = 0; i < 8; ++i) dw[k][i] = 0.f;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * cols);
-    const uint4* gr = reinterpret_cast<const uint4*>(dy + size_t(row) * cols);
-    const float rstd = rstd_in[row];
-    uint4 xv[kNormMaxVec], gv[kNormMaxVec];
-    float dot = 0.f;
+  const int iters = (rows + gridDim.x * kRowsPerIter - 1) / (gridDim.x * kRowsPerIter);
+  for (int it = 0; it < iters; ++it) {
+    const int row = (it * gridDim.x + blockIdx.x) * kRowsPerIter + warp / R;
+    const bool live = row < rows;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(live ? row : 0) * cols);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + size_t(live ? row : 0) * cols);
+    const float rstd = live ? rstd_in[row] : 0.f;
+    uint4 xv[kNormVec], gv[kNormVec];
 #pragma unroll
-    for (int k = 0; k < kNormMaxVec; ++k) {
-      const int v = threadIdx.x + k * kNormThreads;
-      if (v < nvec) {
+    for (int k = 0; k < kNormVec; ++k) {
+      const int v = (sub * kNormVec + k) * 32 + lane;
+      if (live && v < nvec) {
         xv[k] = xr[v];
         gv[k] = gr[v];
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int k = 0; k < kNormVec; ++k) {
+      const int v = (sub * kNormVec + k) * 32 + lane;
+      if (live && v < nvec) {
         float xf[8], gf[8], wf[8];
         unpack8(xv[k], xf);
         unpack8(gv[k], gf);
@@ -138,12 +186,13 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
         }
       }
     }
-    dot = block_sum(dot, red);
+    dot = row_sum<R>(dot, red, warp, lane);
+    if (!live) continue;
     const float c = dot * rstd * rstd / cols;
     uint4* dr = reinterpret_cast<uint4*>(dx + size_t(row) * cols);
 #pragma unroll
-    for (int k = 0; k < kNormMaxVec; ++k) {
-      const int v = threadIdx.x + k * kNormThreads;
+    for (int k = 0; k < kNormVec; ++k) {
+      const int v = (sub * kNormVec + k) * 32 + lane;
       if (v < nvec) {
         float xf[8], gf[8], wf[8], o[8];
         unpack8(xv[k], xf);
@@ -155,15 +204,18 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
       }
     }
   }
-  float* prow = partial + size_t(blockIdx.x) * cols;
+  __syncthreads();
 #pragma unroll
-  for (int k = 0; k < kNormMaxVec; ++k) {
-    const int v = threadIdx.x + k * kNormThreads;
+  for (int k = 0; k < kNormVec; ++k) {
+    const int v = (sub * kNormVec + k) * 32 + lane;
     if (v < nvec) {
-      *reinterpret_cast<float4*>(prow + v * 8) = make_float4(dw[k][0], dw[k][1], dw[k][2], dw[k][3]);
-      *reinterpret_cast<float4*>(prow + v * 8 + 4) = make_float4(dw[k][4], dw[k][5], dw[k][6], dw[k][7]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[v * 8 + i], dw[k][i]);
     }
   }
+  __syncthreads();
+  float* prow = partial + size_t(blockIdx.x) * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) prow[c] = dw_smem[c];
 }
 
 __global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts, int cols) {
@@ -387,29 +439,50 @@ int cap_grid(long long work_items, int threads, int sm_count, int per_sm) {
   return static_cast<int>(g);
 }
 
+template <int R>
+cudaError_t rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps, int sm_count,
+                          cudaStream_t stream) {
+  const int want = (rows + kNormWarps / R - 1) / (kNormWarps / R);
+  const int grid = want < sm_count * 8 ? want : sm_count * 8;
+  rmsnorm_fwd_kernel<R><<<grid, kNormThreads, 0, stream>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(w),
+                                                           static_cast<bf16*>(y), rstd, rows, cols, eps);
+  return cudaGetLastError();
+}
+
+template <int R>
+cudaError_t rmsnorm_bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* partial,
+                          int rows, int cols, int grid, cudaStream_t stream) {
+  rmsnorm_bwd_kernel<R><<<grid, kNormThreads, cols * sizeof(float), stream>>>(
+      static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
+      static_cast<bf16*>(dx), partial, rows, cols);
+  return cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps,
                                int sm_count, cudaStream_t stream) {
-  if (cols % 8 != 0 || cols > kNormThreads * 8 * kNormMaxVec) return cudaErrorInvalidValue;
+  if (cols % 8 != 0 || cols > 8192) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
-  const int grid = rows < sm_count * 8 ? rows : sm_count * 8;
-  rmsnorm_fwd_kernel<<<grid, kNormThreads, 0, stream>>>(static_cast<const bf16*>(x), static_cast<const bf16*>(w),
-                                                        static_cast<bf16*>(y), rstd, rows, cols, eps);
-  return cudaGetLastError();
+  if (cols <= 2048) return rmsnorm_fwd_t<1>(x, w, y, rstd, rows, cols, eps, sm_count, stream);
+  if (cols <= 4096) return rmsnorm_fwd_t<2>(x, w, y, rstd, rows, cols, eps, sm_count, stream);
+  return rmsnorm_fwd_t<4>(x, w, y, rstd, rows, cols, eps, sm_count, stream);
 }
 
 int rmsnorm_bwd_grid(int rows, int sm_count) {
-  const int g = sm_count * 4;
-  return rows < g ? (rows < 1 ? 1 : rows) : g;
+  const int want = (rows + kNormWarps - 1) / kNormWarps;
+  const int g = sm_count * 2;
+  return want < g ? (want < 1 ? 1 : want) : g;
 }
 
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                float* partial, float* dw, int rows, int cols, int grid, cudaStream_t stream) {
-  if (cols % 8 != 0 || cols > kNormThreads * 8 * kNormMaxVec) return cudaErrorInvalidValue;
-  rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, stream>>>(static_cast<const bf16*>(dy), static_cast<const bf16*>(x),
-                                                        static_cast<const bf16*>(w), rstd, static_cast<bf16*>(dx),
-                                                        partial, rows, cols);
+  if (cols % 8 != 0 || cols > 8192) return cudaErrorInvalidValue;
+  cudaError_t e;
+  if (cols <= 2048) e = rmsnorm_bwd_t<1>(dy, x, w, rstd, dx, partial, rows, cols, grid, stream);
+  else if (cols <= 4096) e = rmsnorm_bwd_t<2>(dy, x, w, rstd, dx, partial, rows, cols, grid, stream);
+  else e = rmsnorm_bwd_t<4>(dy, x, w, rstd, dx, partial, rows, cols, grid, stream);
+  if (e != cudaSuccess) return e;
   colsum_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(partial, dw, grid, cols);
   return cudaGetLastError();
 }
