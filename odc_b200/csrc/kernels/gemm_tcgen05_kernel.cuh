@@ -230,6 +230,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const long long n_chunks = (total_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes;
     for (long long c = blockIdx.x; c < n_chunks; c += gridDim.x) {
       const long long byte0 = c * kFetchChunkBytes + fw * kFetchWarpBytes;
+      // usually the warp's 16 KiB lie inside one owner's shard: resolve the owner once
+      const long long last = min(byte0 + kFetchWarpBytes, total_bytes) - 1;
+      const int owner0 = static_cast<int>(byte0 / shard_bytes);
+      const bool one_owner = byte0 < total_bytes && owner0 == static_cast<int>(last / shard_bytes);
+      const unsigned char* src0 = one_owner
+          ? reinterpret_cast<const unsigned char*>(p.shard_ptrs[owner0]) - static_cast<long long>(owner0) * shard_bytes
+          : nullptr;
       uint4 r[16];
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -237,8 +244,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int v = 0; v < 16; ++v) {
           const long long b = byte0 + (static_cast<long long>(half * 16 + v) * 32 + lane) * 16;
           if (b < total_bytes) {
-            const int owner = static_cast<int>(b / shard_bytes);
-            r[v] = ld_stream_v4(reinterpret_cast<const unsigned char*>(p.shard_ptrs[owner]) + (b - owner * shard_bytes));
+            if (one_owner) {
+              r[v] = ld_stream_v4(src0 + b);
+            } else {
+              const int owner = static_cast<int>(b / shard_bytes);
+              r[v] = ld_stream_v4(reinterpret_cast<const unsigned char*>(p.shard_ptrs[owner]) + (b - owner * shard_bytes));
+            }
           }
         }
 #pragma unroll
