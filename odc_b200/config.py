@@ -63,11 +63,6 @@ def debug_bounds() -> bool:
     return os.environ.get("ODC_DEBUG_BOUNDS", "0") not in ("0", "", "false")
 
 
-def deterministic() -> bool:
-    """Owner-side fixed-order reduction instead of remote floating-point atomics."""
-    return os.environ.get("ODC_DETERMINISTIC", "0") not in ("0", "", "false")
-
-
 def local_world_size(default: int) -> int:
     """GPUs per node: ``RAY_LOCAL_WORLD_SIZE`` overrides ``LOCAL_WORLD_SIZE`` (utils.py:195-199)."""
     for name in ("RAY_LOCAL_WORLD_SIZE", "LOCAL_WORLD_SIZE"):

@@ -401,6 +401,42 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Ten
   return {dq, dk, dv};
 }
 
+// --- single-primitive test entry points: addresses are plain integers so peers' mappings can be passed
+void put_block(uintptr_t remote_dst, Tensor local_src) {
+  c10::cuda::CUDAGuard g(local_src.device());
+  odc::bind_device(local_src.get_device());
+  check(odc::launch_put_block(reinterpret_cast<void*>(remote_dst), local_src.data_ptr(), local_src.nbytes(), cur_stream()),
+        "put_block");
+}
+void get_block(Tensor local_dst, uintptr_t remote_src) {
+  c10::cuda::CUDAGuard g(local_dst.device());
+  odc::bind_device(local_dst.get_device());
+  check(odc::launch_get_block(local_dst.data_ptr(), reinterpret_cast<const void*>(remote_src), local_dst.nbytes(),
+                              cur_stream()), "get_block");
+}
+void scalar_put_get(uintptr_t remote_word, int value, Tensor readback) {
+  c10::cuda::CUDAGuard g(readback.device());
+  odc::bind_device(readback.get_device());
+  check(odc::launch_scalar_put_get(reinterpret_cast<int*>(remote_word), value, readback.data_ptr<int>(), cur_stream()),
+        "scalar_put_get");
+}
+void atomic_test(Tensor word, Tensor cas_seen, Tensor swap_seen, int expected_old, int cas_new, int swap_new) {
+  c10::cuda::CUDAGuard g(word.device());
+  odc::bind_device(word.get_device());
+  check(odc::launch_atomic_test(word.data_ptr<int>(), cas_seen.data_ptr<int>(), swap_seen.data_ptr<int>(),
+                                static_cast<int>(cas_seen.numel()), expected_old, cas_new, swap_new, cur_stream()),
+        "atomic_test");
+}
+void grid_barrier_test(Tensor counter, Tensor slots, Tensor out, int64_t timeout_ms, Tensor status) {
+  c10::cuda::CUDAGuard g(out.device());
+  odc::bind_device(out.get_device());
+  TORCH_CHECK(out.numel() <= sm_count(), "grid barrier needs co-resident CTAs: at most one per SM");
+  check(odc::launch_grid_barrier_test(reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), slots.data_ptr<int>(),
+                                      out.data_ptr<int>(), static_cast<int>(out.numel()),
+                                      static_cast<unsigned long long>(timeout_ms) * 1000000ull, status.data_ptr<int>(),
+                                      cur_stream()), "grid_barrier_test");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -428,6 +464,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("layout"), py::arg("bias"),
         py::arg("accumulate"), py::arg("residual") = py::none());
+  m.def("put_block", &put_block);
+  m.def("get_block", &get_block);
+  m.def("scalar_put_get", &scalar_put_get);
+  m.def("atomic_test", &atomic_test);
+  m.def("grid_barrier_test", &grid_barrier_test);
   m.def("gemm_wgrad_scatter", &gemm_wgrad_scatter);
   m.def("gemm_gather", &gemm_gather);
   m.def("attn_fwd", &attn_fwd);

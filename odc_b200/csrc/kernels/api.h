@@ -19,6 +19,15 @@ cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long l
 cudaError_t launch_wait_counter(const void* ctr, unsigned long long expected, unsigned long long budget_ns,
                                 int* status, cudaStream_t stream);
 
+// ---- single-primitive test kernels (device_prims.cu) ---------------------------------------------
+cudaError_t launch_put_block(void* remote_dst, const void* local_src, size_t bytes, cudaStream_t s);
+cudaError_t launch_get_block(void* local_dst, const void* remote_src, size_t bytes, cudaStream_t s);
+cudaError_t launch_scalar_put_get(int* remote_word, int value, int* readback, cudaStream_t s);
+cudaError_t launch_atomic_test(int* word, int* cas_seen, int* swap_seen, int ctas, int expected_old, int cas_new,
+                               int swap_new, cudaStream_t s);
+cudaError_t launch_grid_barrier_test(unsigned int* counter, int* slots, int* out, int ctas,
+                                     unsigned long long budget_ns, int* status, cudaStream_t s);
+
 // ---- elementwise / normalisation (bf16 activations, fp32 math) -----------------------------
 cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps,
                                int sm_count, cudaStream_t stream);

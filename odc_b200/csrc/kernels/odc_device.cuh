@@ -91,4 +91,32 @@ __device__ __forceinline__ bool bounded_wait_ge(const unsigned long long* p, uns
   return true;
 }
 
+// Grid-wide barrier on a monotonic counter (the caller passes the same zero-initialised word to every
+// launch that uses it only once, or tracks the running target itself).  All CTAs of the grid must be
+// co-resident.  Bounded: on timeout the status word is written and false is returned to every thread.
+__device__ __forceinline__ bool grid_barrier_bounded(unsigned int* counter, unsigned int expected,
+                                                     uint64_t budget_ns, int* status) {
+  __shared__ int ok_flag;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    atomicAdd(counter, 1u);
+    const uint64_t t0 = globaltimer_ns();
+    ok_flag = 1;
+    unsigned int v;
+    while (true) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+      if (v >= expected) break;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        report(status, kErrWaitTimeout, 1, static_cast<int>(v));
+        ok_flag = 0;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
 }  // namespace odc
