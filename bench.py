@@ -30,9 +30,13 @@ def parse():
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="odc_b200", choices=["odc_b200", "reference", "stock"])
-    ap.add_argument("--model", default="llama3.2-1b")
-    ap.add_argument("--microbatches", type=int, default=8)
-    ap.add_argument("--token-budget", type=int, default=16384)
+    ap.add_argument("--config", default="3", choices=["3", "4", "5"],
+                    help="workload: 3 = Llama-3.2-1B FSDP2 full shard (headline), 4 = Llama-3-8B HSDP 4x2 + "
+                         "reshard_after_forward=4 + activation checkpointing, 5 = Qwen2.5-14B FSDP1 + activation "
+                         "checkpointing with long-tail lengths")
+    ap.add_argument("--model", default=None)
+    ap.add_argument("--microbatches", type=int, default=None)
+    ap.add_argument("--token-budget", type=int, default=None)
     ap.add_argument("--uneven", action="store_true", help="ranks run different numbers of microbatches")
     ap.add_argument("--optimizer", default="fused", choices=["fused", "torch"])
     return ap.parse_args()
@@ -84,27 +88,76 @@ def main():
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
 
     use_odc = args.impl == "odc_b200"
-    cfg = get_config(args.model)
+    presets = {
+        "3": dict(model="llama3.2-1b", microbatches=8, token_budget=16384, engine="fsdp2", hsdp=False, hpz=0, ac=False,
+                  spec=LengthSpec("lognormal", lo=16, median=512.0, sigma=1.0, cap=8192),
+                  seq="lognormal(median 512, sigma 1.0, cap 8192), packed"),
+        "4": dict(model="llama3-8b", microbatches=16, token_budget=32768, engine="fsdp2", hsdp=True, hpz=4, ac=True,
+                  spec=LengthSpec("lognormal", lo=16, median=1024.0, sigma=1.2, cap=16384),
+                  seq="lognormal(median 1024, sigma 1.2, cap 16384), packed"),
+        "5": dict(model="qwen2.5-14b", microbatches=8, token_budget=32768, engine="fsdp1", hsdp=False, hpz=0, ac=True,
+                  spec=LengthSpec("longtail", short=(256, 2048), long=(8192, 32768), long_frac=0.25),
+                  seq="75% uniform[256,2048] + 25% uniform[8192,32768], packed"),
+    }
+    wl = presets[args.config]
+    args.model = args.model or wl["model"]
+    args.microbatches = args.microbatches or wl["microbatches"]
+    args.token_budget = args.token_budget or wl["token_budget"]
+    cfg = get_config(args.model, activation_checkpointing=wl["ac"])
     torch.manual_seed(0)
-    with torch.device(device):
-        model = DecoderLM(cfg)
-    model.reset_parameters(seed=0)
-    if use_odc:
-        odc.init_nvshmem(device)
-        fsdp2.patch_fsdp2()
-    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
-    for layer in model.layers:
-        fully_shard(layer, mp_policy=mp)
-    fully_shard(model, mp_policy=mp)
-    if use_odc:
-        for m in list(model.layers) + [model]:
-            fsdp2.patch_lazy_init(m)
-    if use_odc and args.optimizer == "fused":
-        opt = fsdp2.FusedAdamW(model, lr=1e-4, weight_decay=0.01)
-    else:
-        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
+    engine = wl["engine"]
+    if engine == "fsdp1":
+        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+        from torch.distributed.fsdp import MixedPrecision
+        from torch.distributed.fsdp.wrap import ModuleWrapPolicy
 
-    spec = LengthSpec("lognormal", lo=16, median=512.0, sigma=1.0, cap=8192)
+        from odc_b200.fsdp import fsdp1
+        from odc_b200.models import DecoderLayer
+        if use_odc:
+            fsdp1.patch_fsdp1(reduce_dtype=torch.float32)
+            odc.init_nvshmem(device)
+        with torch.device(device):
+            model = DecoderLM(cfg)
+        model.reset_parameters(seed=0)
+        model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=device, use_orig_params=False,
+                     mixed_precision=MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32,
+                                                    buffer_dtype=torch.bfloat16))
+        args.optimizer = "torch"
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
+        parallelism = f"fsdp1-dp{world}"
+    else:
+        with torch.device(device):
+            model = DecoderLM(cfg)
+        model.reset_parameters(seed=0)
+        hpz = wl["hpz"] if (use_odc and wl["hpz"] and world >= wl["hpz"]) else 0
+        if use_odc:
+            odc.init_nvshmem(device)
+            fsdp2.patch_fsdp2(enable_hpz=bool(hpz))
+        mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+        kw = {"mp_policy": mp}
+        parallelism = f"fsdp2-dp{world}"
+        if wl["hsdp"] and world >= 4 and world % 2 == 0:
+            from torch.distributed.device_mesh import init_device_mesh
+            kw["mesh"] = init_device_mesh("cuda", (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard"))
+            parallelism = f"hsdp-replicate2-shard{world // 2}"
+        if hpz:
+            kw["reshard_after_forward"] = hpz
+            parallelism += f"-hpz{hpz}"
+        if wl["ac"]:
+            parallelism += "-actckpt"
+        for layer in model.layers:
+            fully_shard(layer, **kw)
+        fully_shard(model, **kw)
+        if use_odc:
+            for m in list(model.layers) + [model]:
+                fsdp2.patch_lazy_init(m)
+        if use_odc and args.optimizer == "fused":
+            opt = fsdp2.FusedAdamW(model, lr=1e-4, weight_decay=0.01)
+        else:
+            args.optimizer = "torch"
+            opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01, fused=True)
+
+    spec = wl["spec"]
     n_micro = args.microbatches
     if args.uneven:
         n_micro = max(1, args.microbatches - (rank % 3))
@@ -113,8 +166,11 @@ def main():
     pool_dev = [[to_device(mb, device) for mb in mbs] for mbs in pool]
     tokens_per_step = [sum(mb["num_tokens"] for mb in mbs) for mbs in pool]
 
+    if use_odc and engine == "fsdp1":
+        fsdp1.pre_minibatch_start(model)
+
     def step(mbs, from_host: bool):
-        if use_odc:
+        if use_odc and engine == "fsdp2":
             fsdp2.pre_minibatch_start(model)
         total = None
         for mb in mbs:
@@ -124,10 +180,14 @@ def main():
                          labels=mb["labels"], loss_scale=mb["loss_scale"])
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
-        if use_odc:
-            fsdp2.pre_optimizer_step(model)
+        if use_odc and engine == "fsdp2":
+            fsdp2.pre_optimizer_step(model, materialize_grads=(args.optimizer != "fused"))
+        elif use_odc:
+            fsdp1.pre_optimizer_step(model)
         opt.step()
         opt.zero_grad()
+        if use_odc and engine == "fsdp1":
+            fsdp1.pre_minibatch_start(model)
         return total
 
     def timed(from_host: bool, steps: int):
@@ -153,11 +213,19 @@ def main():
 
     for i in range(args.warmup):
         step(pool_dev[i % len(pool_dev)], False)
-    launches0 = ops.kernel_launches() + (fsdp2.transport_launches() if use_odc else 0)
+    def comm_launches():
+        if not use_odc:
+            return 0
+        if engine == "fsdp2":
+            return fsdp2.transport_launches()
+        return sum(getattr(svc.transport, "launches", 0) for svc in (fsdp1.get_gather_service(), fsdp1.get_reduction_service())
+                   if svc is not None)
+
+    launches0 = ops.kernel_launches() + comm_launches()
     sampler = ClockSampler(gpu_index=local_rank).start() if rank == 0 else None
     ms, toks, _ = timed(False, args.steps)
     clocks = sampler.stop() if sampler else {}
-    launches = ops.kernel_launches() + (fsdp2.transport_launches() if use_odc else 0) - launches0
+    launches = ops.kernel_launches() + comm_launches() - launches0
     e2e_ms, e2e_toks, last_loss = timed(True, args.steps)
 
     if rank == 0:
@@ -168,7 +236,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic token ids, random-init weights", "impl": args.impl,
             "config": {"model": args.model, "global_batch": f"{world}x{n_micro} microbatches x <= {args.token_budget} tokens",
-                       "seq_len": "lognormal(median 512, sigma 1.0, cap 8192), packed", "parallelism": f"fsdp2-dp{world}",
+                       "seq_len": wl["seq"], "parallelism": parallelism, "workload": f"BASELINE.json config {args.config}",
                        "tokens_per_step": toks / args.steps, "l2": "working set (params+activations, >10 GB) exceeds the 126 MB L2",
                        "optimizer": args.optimizer, "gemm": ops.gemm_backend(), "attention": ops.attn_backend(),
                        "params": cfg.num_params()},
@@ -180,8 +248,10 @@ def main():
             "gpu_launches": launches,
         }
         print(json.dumps(line))
-    if use_odc:
+    if use_odc and engine == "fsdp2":
         fsdp2.stop()
+    elif use_odc:
+        fsdp1.stop()
     dist.destroy_process_group()
     return 0
 
