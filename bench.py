@@ -129,14 +129,16 @@ def main():
         with torch.device(device):
             model = DecoderLM(cfg)
         model.reset_parameters(seed=0)
-        hpz = wl["hpz"] if (use_odc and wl["hpz"] and world >= wl["hpz"]) else 0
+        use_hsdp = wl["hsdp"] and world >= 4 and world % 2 == 0
+        shard_size = world // 2 if use_hsdp else world
+        hpz = wl["hpz"] if (use_odc and wl["hpz"] and shard_size % wl["hpz"] == 0) else 0
         if use_odc:
             odc.init_nvshmem(device)
             fsdp2.patch_fsdp2(enable_hpz=bool(hpz))
         mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
         kw = {"mp_policy": mp}
         parallelism = f"fsdp2-dp{world}"
-        if wl["hsdp"] and world >= 4 and world % 2 == 0:
+        if use_hsdp:
             from torch.distributed.device_mesh import init_device_mesh
             kw["mesh"] = init_device_mesh("cuda", (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard"))
             parallelism = f"hsdp-replicate2-shard{world // 2}"
