@@ -101,3 +101,59 @@ def test_fsdp2_hsdp():
 def test_fsdp2_hpz():
     b = _compare(4, hpz=2)
     assert b[0][2]["hpz_buffer"] > 0
+
+
+def _train_fused(rank, world, mode):
+    """HSDP (2 x 2) + secondary partition of 2 + activation checkpointing; on-demand side uses FusedAdamW."""
+    import torch.distributed as dist
+    from torch.distributed.device_mesh import init_device_mesh
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+    from odc_b200.models import DecoderLM, get_config
+
+    model = DecoderLM(get_config("tiny", activation_checkpointing=True))
+    model.reset_parameters(seed=0)
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 256 << 20)
+        fsdp2.patch_fsdp2(enable_hpz=True)
+    mesh = init_device_mesh("cpu", (2, 2), mesh_dim_names=("rep", "shard"))
+    raf = 2 if mode == "odc" else True
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh, reshard_after_forward=raf)
+    fully_shard(model, mesh=mesh, reshard_after_forward=raf)
+    if mode == "odc":
+        for m in list(model.layers) + [model]:
+            fsdp2.patch_lazy_init(m)
+        opt = fsdp2.FusedAdamW(model, lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    else:
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+    norms = []
+    for step in range(3):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        for i in range(2):
+            mb = _make_batches(rank, step, 2)[i]
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"],
+                         labels=mb["labels"], loss_scale=mb["loss_scale"])
+            loss.backward()
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model, materialize_grads=False)
+            norms.append(float(opt.clip_grad_norm_(1e9)))
+        else:
+            norms.append(float(torch.nn.utils.clip_grad_norm_(model.parameters(), 1e9).full_tensor()))
+        opt.step()
+        opt.zero_grad()
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    if mode == "odc":
+        fsdp2.stop()
+    return norms, full
+
+
+def test_fsdp2_hsdp_hpz_checkpointing_fused_adamw():
+    a = run_ranks(_train_fused, 4, "stock")
+    b = run_ranks(_train_fused, 4, "odc")
+    assert a[0][0] == pytest.approx(b[0][0], rel=1e-3), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
