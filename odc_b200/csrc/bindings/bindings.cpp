@@ -323,6 +323,24 @@ void gemm_wgrad_scatter(Tensor dy, Tensor x, Tensor acc_table, Tensor ctr_table,
         "gemm_wgrad_scatter");
 }
 
+bool gemm_wgrad_scatter_tma(Tensor dy, Tensor x, std::vector<int64_t> acc_addrs, Tensor ctr_table, int64_t acc_offset,
+                            int64_t rows_per_rank, double scale) {
+  c10::cuda::CUDAGuard g(dy.device());
+  odc::bind_device(dy.get_device());
+  TORCH_CHECK(dy.dim() == 2 && x.dim() == 2 && dy.size(0) == x.size(0), "wgrad_scatter: dy [T,N], x [T,K]");
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && x.scalar_type() == at::kBFloat16, "wgrad_scatter: bf16 inputs");
+  TORCH_CHECK(dy.stride(1) == 1 && x.stride(1) == 1, "wgrad_scatter: innermost stride must be 1");
+  std::vector<long long> addrs(acc_addrs.begin(), acc_addrs.end());
+  cudaError_t e = odc::gemm_wgrad_scatter_tma(
+      dy.data_ptr(), x.data_ptr(), dy.size(0), dy.size(1), x.size(1), dy.stride(0), x.stride(0), addrs.data(),
+      reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()), acc_offset, static_cast<int>(rows_per_rank),
+      static_cast<int>(addrs.size()), static_cast<float>(scale), next_done_slot(dy.get_device()),
+      gemm_status(dy.get_device()).data_ptr<int>(), sm_count(), cur_stream());
+  if (e == cudaErrorNotSupported) return false;  // shape not eligible: the caller uses the red.add variant
+  check(e, "gemm_wgrad_scatter_tma");
+  return true;
+}
+
 Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<Tensor> bias, int64_t rows_per_rank,
                    int start_rank) {
   c10::cuda::CUDAGuard g(x.device());
@@ -470,6 +488,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("atomic_test", &atomic_test);
   m.def("grid_barrier_test", &grid_barrier_test);
   m.def("gemm_wgrad_scatter", &gemm_wgrad_scatter);
+  m.def("gemm_wgrad_scatter_tma", &gemm_wgrad_scatter_tma);
   m.def("gemm_gather", &gemm_gather);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

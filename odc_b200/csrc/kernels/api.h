@@ -65,6 +65,13 @@ cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_
                                long long ld_x, const long long* acc_ptrs, const long long* ctr_ptrs,
                                long long acc_offset, int rows_per_rank, int nranks, float scale,
                                unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream);
+// Same contract, but output boxes go through shared memory and TMA bulk reduce-add into the owners' accumulators.
+// acc_addrs_host: HOST array of the accumulators' addresses (tensor maps are built on the host).  Returns
+// cudaErrorNotSupported when rows_per_rank is not a multiple of 128 or there are more than 8 owners.
+cudaError_t gemm_wgrad_scatter_tma(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
+                                   long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
+                                   long long acc_offset, int rows_per_rank, int nranks, float scale,
+                                   unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream);
 // Y[M, N] = X[M, K] W[N, K]^T with rank r holding rows [r * rows_per_rank, ...) of W at shard_ptrs[r];
 // w_local [N, K] receives the gathered weight; panel_flags needs ceil(N / 256) words.
 cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_local, void* y, const void* bias,

@@ -56,7 +56,50 @@ cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_
   p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.scale = scale; p.done_slot = done_slot;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_bf16_kernel<kModeScatter><<<grid, Roles<kModeScatter>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, ta, p);
+  gemm_bf16_kernel<kModeScatter><<<grid, Roles<kModeScatter>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, ta, OwnerMaps{}, p);
+  return cudaGetLastError();
+}
+
+cudaError_t gemm_wgrad_scatter_tma(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
+                                   long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
+                                   long long acc_offset, int rows_per_rank, int nranks, float scale,
+                                   unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream) {
+  if (n_out == 0 || k_in == 0 || nranks == 0) return cudaSuccess;
+  if (tokens == 0) return cudaErrorInvalidValue;
+  if (nranks > kMaxOwners || (rows_per_rank % BM) != 0) return cudaErrorNotSupported;  // caller falls back to red.add
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x)) & 15) return cudaErrorMisalignedAddress;
+  if ((ld_dy % 8) || (ld_x % 8) || (k_in % 8) || (acc_offset % 4)) return cudaErrorInvalidValue;
+  if (static_cast<long long>(rows_per_rank) * nranks < n_out) return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<kModeScatterTma>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  CUtensorMap ta, tb;
+  if (!encode_tile_map_2d(&ta, dy, n_out, tokens, ld_dy * 2, 64, 64)) return cudaErrorInvalidValue;
+  if (!encode_tile_map_2d(&tb, x, k_in, tokens, ld_x * 2, 64, 64)) return cudaErrorInvalidValue;
+  OwnerMaps owners{};
+  for (int r = 0; r < nranks; ++r) {
+    float* base = reinterpret_cast<float*>(static_cast<uintptr_t>(acc_addrs_host[r])) + acc_offset;
+    if (!encode_tile_map_2d_f32(&owners.m[r], base, k_in, rows_per_rank, static_cast<uint64_t>(k_in) * 4, 32, BM))
+      return cudaErrorInvalidValue;
+  }
+  Params p{};
+  p.M = n_out; p.N = k_in; p.K = tokens;
+  p.ldc = k_in;
+  p.c_is_f32 = 1;
+  p.a_mn = 1; p.b_mn = 1;
+  p.tiles_m = (n_out + BM - 1) / BM;
+  p.tiles_n = (k_in + BN - 1) / BN;
+  p.status = status;
+  p.ctr_ptrs = ctr_ptrs;
+  p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.scale = scale; p.done_slot = done_slot;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  gemm_bf16_kernel<kModeScatterTma><<<grid, Roles<kModeScatterTma>::kThreadsTotal, kSmemBytes, stream>>>(
+      ta, tb, ta, owners, p);
   return cudaGetLastError();
 }
 
@@ -98,7 +141,7 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   if (e != cudaSuccess) return e;
   // every CTA also fetches, so use the whole machine even when there are few tiles
   const int grid = sm_count;
-  gemm_bf16_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, p);
+  gemm_bf16_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, OwnerMaps{}, p);
   return cudaGetLastError();
 }
 

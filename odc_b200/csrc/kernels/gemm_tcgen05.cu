@@ -93,7 +93,7 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_bf16_kernel<kModePlain><<<grid, Roles<kModePlain>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, p);
+  gemm_bf16_kernel<kModePlain><<<grid, Roles<kModePlain>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, OwnerMaps{}, p);
   return cudaGetLastError();
 }
 

@@ -3,6 +3,9 @@
 //   kModePlain   : C is written (or accumulated) locally.
 //   kModeScatter : weight-gradient GEMM whose epilogue issues 16-byte red.add.f32 straight into the
 //                  fp32 accumulator of the rank that owns each output row, then signals arrival.
+//   kModeScatterTma : same result, but output boxes are staged in shared memory and added into the owner's
+//                  accumulator by the TMA unit (bulk reduce-add through the peer mapping), which keeps the
+//                  link busy with far fewer issued instructions than per-thread reductions.
 //   kModeGather  : forward GEMM whose B operand (a row-sharded weight) is pulled from the owners'
 //                  shards into local memory by two extra warps per CTA while the tensor cores work
 //                  on panels that have already landed; TMA only ever reads this GPU's own memory.
@@ -57,7 +60,12 @@ struct Params {
   int start_rank;
 };
 
-constexpr int kModePlain = 0, kModeScatter = 1, kModeGather = 2;
+constexpr int kModePlain = 0, kModeScatter = 1, kModeGather = 2, kModeScatterTma = 3;
+constexpr int kMaxOwners = 8;
+// one fp32 tensor map per owner's accumulator region (kModeScatterTma)
+struct OwnerMaps {
+  CUtensorMap m[kMaxOwners];
+};
 // warp roles: 0 = TMA, 1 = MMA, then epilogue warps, then (gather mode) shard-fetch warps
 template <int kMode> struct Roles {
   static constexpr int kEpilogueWarps = (kMode == kModeScatter) ? 8 : 4;  // remote reductions need more issue slots
@@ -75,7 +83,7 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 template <int kMode>
 __global__ void __launch_bounds__(Roles<kMode>::kThreadsTotal, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+                 const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ OwnerMaps owners, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -298,6 +306,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tmem_ld_wait();
           const int col0 = n0 + bx * cols_per_box;
           if (col0 >= p.N) continue;
+          if constexpr (kMode == kModeScatterTma) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * p.scale);
+          }
           if (p.bias != nullptr) {
 #pragma unroll
             for (int i = 0; i < 64; ++i)
@@ -341,8 +353,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (lane == 0) mbar_arrive(sready0 + 8 * buf);
           if (warp == 2 && lane == 0) {
             if (mbar_wait(sready0 + 8 * buf, use & 1, wc, 7)) {
-              if (p.accumulate) tma_reduce_add_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
-              else tma_store_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
+              if constexpr (kMode == kModeScatterTma) {
+                // tiles never straddle owners (rows_per_rank is a multiple of the tile height)
+                const int owner = m0 / p.rows_per_rank;
+                tma_reduce_add_2d(&owners.m[owner], staging_u32 + buf * kStagingBytes, col0,
+                                  m0 - owner * p.rows_per_rank);
+              } else if (p.accumulate) {
+                tma_reduce_add_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
+              } else {
+                tma_store_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
+              }
               bulk_commit_group();
               if (box_ctr >= 1) {
                 bulk_wait_group_read1();             // the previous box has been read: its buffer is free again
@@ -436,7 +456,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (lane == 0) mbar_arrive(tempty0 + 8 * acc);
     }
     if constexpr (kMode == kModeScatter) __threadfence_system();  // this thread's remote reductions are out
-    if (kMode != kModeScatter && warp == 2 && lane == 0) bulk_wait_group0();  // all output boxes are in memory
+    if (kMode != kModeScatter && warp == 2 && lane == 0) {
+      bulk_wait_group0();  // all output boxes are in memory
+      if constexpr (kMode == kModeScatterTma) __threadfence_system();
+    }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -446,7 +469,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  if constexpr (kMode == kModeScatter) {
+  if constexpr (kMode == kModeScatter || kMode == kModeScatterTma) {
     // last CTA to finish releases one arrival on every owner's counter
     if (threadIdx.x == 0) {
       __threadfence_system();

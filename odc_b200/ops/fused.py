@@ -14,6 +14,7 @@ multi-rank logic is testable without a GPU.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -63,8 +64,17 @@ def wgrad_scatter(dy: torch.Tensor, x: torch.Tensor, reduction: ReductionService
         reg = reduction.registry
         if acc.dtype != torch.float32:
             raise ValueError("the fused weight-gradient path accumulates in fp32")
-        _ext.load().gemm_wgrad_scatter(dy2.contiguous(), x2.contiguous(), reg.peer_ptr_table(acc, ranks),
-                                       reg.peer_ptr_table(reduction.counter, ranks), param_offset, rows_per_rank, scale)
+        ext = _ext.load()
+        dy2, x2 = dy2.contiguous(), x2.contiguous()
+        done = False
+        if os.environ.get("ODC_WGRAD_SCATTER", "tma") == "tma":
+            # output boxes staged in shared memory and added into the owners by the TMA unit; needs
+            # rows_per_rank % 128 == 0 and at most 8 owners, otherwise the per-thread red.add variant runs
+            done = ext.gemm_wgrad_scatter_tma(dy2, x2, reg.peer_ptrs(acc, ranks), reg.peer_ptr_table(reduction.counter, ranks),
+                                              param_offset, rows_per_rank, scale)
+        if not done:
+            ext.gemm_wgrad_scatter(dy2, x2, reg.peer_ptr_table(acc, ranks), reg.peer_ptr_table(reduction.counter, ranks),
+                                   param_offset, rows_per_rank, scale)
         _count()
         reduction.note_dispatch(ranks)
     else:

@@ -285,3 +285,30 @@ def test_linear_with_fused_residual():
     want = x.detach().float() @ w.detach().float().t() + res.detach().float()
     torch.testing.assert_close(y.float(), want, rtol=2e-2, atol=5e-2)
     assert torch.equal(res.grad, dy)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("T,n_out,k_in", [(512, 1024, 256), (1000, 2048, 264), (4096, 2048, 2048)])
+def test_wgrad_scatter_tma_emulated_ranks(ext, world, T, n_out, k_in):
+    """Same contract as the red.add variant, output through smem staging + TMA reduce-add (owners emulated locally)."""
+    torch.manual_seed(T + n_out)
+    rows_per = (n_out + world - 1) // world
+    rows_per = (rows_per + 127) // 128 * 128
+    off = 64
+    accs = [torch.zeros(off + rows_per * k_in + 32, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    want = torch.zeros(world * rows_per, k_in, device="cuda")
+    for producer in range(2):
+        dy = torch.randn(T, n_out, device="cuda").bfloat16()
+        x = torch.randn(T, k_in, device="cuda").bfloat16()
+        assert ext.gemm_wgrad_scatter_tma(dy, x, [a.data_ptr() for a in accs], _table(ctrs), off, rows_per, 0.5)
+        want[:n_out] += 0.5 * (dy.float().t() @ x.float())
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0
+    for r in range(world):
+        got = accs[r][off:off + rows_per * k_in].view(rows_per, k_in)
+        torch.testing.assert_close(got, want[r * rows_per:(r + 1) * rows_per], rtol=2e-2, atol=2e-2 * math.sqrt(T))
+        assert float(accs[r][:off].abs().sum()) == 0.0 and float(accs[r][off + rows_per * k_in:].abs().sum()) == 0.0
+        assert int(ctrs[r][0]) == 2
+    # ineligible split (rows per owner not a multiple of 128): the entry point declines, nothing is launched
+    assert not ext.gemm_wgrad_scatter_tma(dy, x, [a.data_ptr() for a in accs], _table(ctrs), off, 100, 1.0)
