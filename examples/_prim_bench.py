@@ -44,9 +44,10 @@ def device_time_ms(fn, iters: int, warmup: int = 3) -> float:
 def sizes_from_argv(default_lo=64 << 10, default_hi=1 << 30):
     lo, hi = default_lo, default_hi
     for a in sys.argv[1:]:
-        if a.startswith("--min="):
+        # names chosen so that torch.distributed.run's own parser does not claim them by prefix
+        if a.startswith("--min=") or a.startswith("--size-min="):
             lo = int(a.split("=")[1])
-        if a.startswith("--max="):
+        if a.startswith("--size-max="):
             hi = int(a.split("=")[1])
     out, s = [], lo
     while s <= hi:

@@ -1,6 +1,6 @@
 """`gather` against NCCL `all_gather_into_tensor` (counterpart of the reference's examples/all_gather.py).
 
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 examples/all_gather.py [--min=65536 --max=1073741824]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 examples/all_gather.py [--size-min=65536 --size-max=1073741824]
 
 Every rank owns a bf16 shard of N(0,1) values in the symmetric heap and pulls all peers' shards.
 Payload per rank = shard_bytes * (W-1) crosses NVLink inbound; bandwidth = payload / device time

@@ -107,13 +107,13 @@ void scatter_accumulate(Tensor inp2d, Tensor acc_table, Tensor ctr_table, int64_
   const int nranks = static_cast<int>(acc_table.numel());
   TORCH_CHECK(inp2d.is_contiguous() && inp2d.numel() == n * nranks, "scatter_accumulate: bad input shape");
   (void)checkb;
-  (void)status;
   check(odc::launch_scatter_accumulate(inp2d.data_ptr(), kind_of(inp2d.scalar_type()),
                                        reinterpret_cast<const long long*>(acc_table.data_ptr<int64_t>()),
                                        kind_of(acc_dtype),
                                        reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()),
                                        static_cast<size_t>(n), nranks, my_index, static_cast<float>(scale),
-                                       next_done_slot(inp2d.get_device()), sm_count(), cur_stream()),
+                                       next_done_slot(inp2d.get_device()), sm_count(), cur_stream(),
+                                       status.data_ptr<int>()),
         "scatter_accumulate launch");
 }
 

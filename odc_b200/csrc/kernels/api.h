@@ -15,7 +15,8 @@ cudaError_t launch_gather(const long long* peers, void* out, size_t n, int src_e
                           int sm_count, cudaStream_t stream);
 cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long long* accs, int acc_kind,
                                       const long long* ctrs, size_t n, int nranks, int start, float scale,
-                                      unsigned int* done_slot, int sm_count, cudaStream_t stream);
+                                      unsigned int* done_slot, int sm_count, cudaStream_t stream,
+                                      int* status_for_bulk = nullptr);
 cudaError_t launch_wait_counter(const void* ctr, unsigned long long expected, unsigned long long budget_ns,
                                 int* status, cudaStream_t stream);
 

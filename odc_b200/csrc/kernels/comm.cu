@@ -9,8 +9,11 @@
 // reductions into the fp32 accumulator (no mailbox, no second pass on the owner); the last CTA
 // to finish bumps every owner's arrival counter with a system-scope release.  Replaces mailbox
 // copy + request/ack kernels + watcher add (odc/primitives/scatter_accumulate.py:649-691,369-395).
+#include <stdlib.h>
+
 #include "api.h"
 #include "odc_device.cuh"
+#include "sm100_ptx.cuh"
 
 namespace odc {
 
@@ -215,6 +218,75 @@ scatter_acc_bf16_kernel(const __nv_bfloat16* __restrict__ inp, const long long* 
   finish_and_signal(ctrs, nranks, done_slot);
 }
 
+// ---------------------------------------------------------------- scatter-accumulate, bulk (TMA) path ---------
+// fp32 rows into fp32 accumulators without touching registers: one thread per CTA streams 32 KiB pieces
+// global -> shared (bulk copy, mbarrier completion) and shared -> owner's accumulator (bulk reduce-add through
+// the peer mapping).  Four pieces per CTA are in flight, i.e. ~19 MB across the GPU, which is what keeps the
+// links busy; the SMs' load/store and atomic pipes stay idle.
+constexpr int kBulkBytes = 32768;
+constexpr int kBulkStages = 4;
+constexpr int kBulkSmem = kBulkStages * kBulkBytes + 64;
+
+__global__ void __launch_bounds__(32)
+scatter_acc_bulk_kernel(const float* __restrict__ inp, const long long* __restrict__ accs,
+                        const long long* __restrict__ ctrs, size_t n, int nranks, int start,
+                        unsigned int* done_slot, int* status) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  using namespace sm100;
+  __shared__ int abort_flag;
+  const uint32_t buf0 = smem_u32(bulk_smem);
+  const uint32_t bar0 = buf0 + kBulkStages * kBulkBytes;
+  const size_t row_bytes = n * sizeof(float);
+  const size_t tiles_per_row = (row_bytes + kBulkBytes - 1) / kBulkBytes;
+  const size_t total_tiles = tiles_per_row * nranks;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kBulkStages; ++s) mbar_init(bar0 + 8 * s, 1);
+    fence_barrier_init();
+    const WaitCtx wc{&abort_flag, status, 4000000000ull};
+    auto tile_info = [&](size_t t, const float** src, float** dst, uint32_t* bytes) {
+      const int peer = (static_cast<int>(t % nranks) + start) % nranks;
+      const size_t off = (t / nranks) * kBulkBytes;
+      const size_t len = row_bytes - off < size_t(kBulkBytes) ? row_bytes - off : size_t(kBulkBytes);
+      *src = reinterpret_cast<const float*>(reinterpret_cast<const unsigned char*>(inp + size_t(peer) * n) + off);
+      *dst = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(accs[peer]) + off);
+      *bytes = static_cast<uint32_t>(len);
+    };
+    auto issue_load = [&](size_t t, int s) {
+      const float* src; float* dst; uint32_t bytes;
+      tile_info(t, &src, &dst, &bytes);
+      mbar_arrive_expect_tx(bar0 + 8 * s, bytes);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(buf0 + s * kBulkBytes), "l"(src), "r"(bytes), "r"(bar0 + 8 * s) : "memory");
+    };
+    // my tiles: blockIdx.x, blockIdx.x + gridDim.x, ...
+    size_t next_load = blockIdx.x;
+    uint32_t loaded = 0, done = 0;
+    for (; loaded < kBulkStages && next_load < total_tiles; ++loaded, next_load += gridDim.x)
+      issue_load(next_load, loaded % kBulkStages);
+    bool ok = true;
+    for (size_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++done) {
+      const int s = done % kBulkStages;
+      if (!(ok = mbar_wait(bar0 + 8 * s, (done / kBulkStages) & 1, wc, 50))) break;
+      const float* src; float* dst; uint32_t bytes;
+      tile_info(t, &src, &dst, &bytes);
+      asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                   ::"l"(dst), "r"(buf0 + s * kBulkBytes), "r"(bytes) : "memory");
+      bulk_commit_group();
+      if (next_load < total_tiles) {
+        // the stage about to be refilled is the one just handed to the reduce: wait until it has been read
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        issue_load(next_load, s);
+        ++loaded;
+        next_load += gridDim.x;
+      }
+    }
+    bulk_wait_group0();
+    __threadfence_system();
+  }
+  finish_and_signal(ctrs, nranks, done_slot);
+}
+
 __global__ void wait_counter_kernel(const unsigned long long* ctr, unsigned long long expected,
                                     unsigned long long budget_ns, int* status) {
   if (threadIdx.x == 0 && blockIdx.x == 0) bounded_wait_ge(ctr, expected, budget_ns, status, /*detail=*/0);
@@ -249,12 +321,30 @@ cudaError_t launch_gather(const long long* peers, void* out, size_t n, int src_e
 
 cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long long* accs, int acc_kind,
                                       const long long* ctrs, size_t n, int nranks, int start, float scale,
-                                      unsigned int* done_slot, int sm_count, cudaStream_t stream) {
+                                      unsigned int* done_slot, int sm_count, cudaStream_t stream, int* status_for_bulk) {
   if (nranks == 0) return cudaSuccess;
   const size_t tiles = ((n / 4 + kTileVecs - 1) / kTileVecs + 1) * nranks;
   const int grid = grid_for(tiles, sm_count);
   const int vec_ok = ((n % 4) == 0 || nranks == 1) && (reinterpret_cast<uintptr_t>(inp) % 16) == 0;
-  if (acc_kind == kF32 && in_kind == kF32) {
+  static const bool bulk_enabled = [] {
+    // opt-in: measured at 2 GPUs it does not beat the per-thread red.add kernel (426 vs 479 GB/s on 256 MiB
+    // shards including the arrival wait), so the red.add kernel stays the default
+    const char* e = getenv("ODC_SCATTER_BULK");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (bulk_enabled && acc_kind == kF32 && in_kind == kF32 && scale == 1.0f && (n % 4) == 0 && n * sizeof(float) >= 65536 &&
+      (reinterpret_cast<uintptr_t>(inp) % 16) == 0) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      cudaError_t e = cudaFuncSetAttribute(scatter_acc_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmem);
+      if (e != cudaSuccess) return e;
+      attr_set = true;
+    }
+    const size_t bulk_tiles = ((n * sizeof(float) + kBulkBytes - 1) / kBulkBytes) * nranks;
+    const int bulk_grid = bulk_tiles < size_t(sm_count) ? static_cast<int>(bulk_tiles) : sm_count;
+    scatter_acc_bulk_kernel<<<bulk_grid, 32, kBulkSmem, stream>>>(static_cast<const float*>(inp), accs, ctrs, n, nranks,
+                                                                start, done_slot, status_for_bulk);
+  } else if (acc_kind == kF32 && in_kind == kF32) {
     scatter_acc_f32_kernel<float><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(inp), accs, ctrs, n,
                                                                  nranks, start, scale, done_slot, vec_ok);
   } else if (acc_kind == kF32 && in_kind == kBF16) {

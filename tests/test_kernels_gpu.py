@@ -312,3 +312,30 @@ def test_wgrad_scatter_tma_emulated_ranks(ext, world, T, n_out, k_in):
         assert int(ctrs[r][0]) == 2
     # ineligible split (rows per owner not a multiple of 128): the entry point declines, nothing is launched
     assert not ext.gemm_wgrad_scatter_tma(dy, x, [a.data_ptr() for a in accs], _table(ctrs), off, 100, 1.0)
+
+
+def test_scatter_accumulate_bulk_path_matches(ext):
+    """The opt-in bulk (TMA) scatter path gives the same sums; run in a child process so the switch is seen at first use."""
+    import subprocess, sys, os, textwrap
+    code = textwrap.dedent("""
+        import torch, sys
+        sys.path.insert(0, %r)
+        from odc_b200 import _ext
+        ext = _ext.load()
+        world, n = 4, 1 << 18
+        accs = [torch.zeros(n, device="cuda") for _ in range(world)]
+        ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+        tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device="cuda")
+        xs = [torch.randint(-4, 5, (world, n), device="cuda").float() for _ in range(world)]
+        st = torch.zeros(4, dtype=torch.int32, device="cuda")
+        for me in range(world):
+            ext.scatter_accumulate(xs[me], tab(accs), tab(ctrs), n, torch.float32, me, 1.0, False, st)
+        torch.cuda.synchronize()
+        want = torch.stack(xs).sum(0)
+        assert all(torch.equal(accs[p], want[p]) for p in range(world))
+        assert all(int(c[0]) == world for c in ctrs) and int(st[0]) == 0
+        print("BULK_OK")
+    """ % os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, ODC_SCATTER_BULK="1"), capture_output=True, text=True,
+                       timeout=120)
+    assert r.returncode == 0 and "BULK_OK" in r.stdout, r.stdout + r.stderr
