@@ -1,6 +1,6 @@
 """Headline benchmark: training tokens/s on imbalanced variable-length minibatches.
 
-Workload (BASELINE.json config 3): Llama-3.2-1B-shaped decoder, bf16 compute with fp32 gradient
+Default workload (--config 3): Llama-3.2-1B-shaped decoder, bf16 compute with fp32 gradient
 accumulation, FSDP2 full shard over N GPUs through this package's on-demand engine; each
 minibatch is 8 microbatches per rank, each packed up to 16384 tokens from log-normal sequence
 lengths (median 512, sigma 1.0, cap 8192) seeded independently per rank.  Synthetic token ids,
@@ -238,7 +238,7 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic token ids, random-init weights", "impl": args.impl,
             "config": {"model": args.model, "global_batch": f"{world}x{n_micro} microbatches x <= {args.token_budget} tokens",
-                       "seq_len": wl["seq"], "parallelism": parallelism, "workload": f"BASELINE.json config {args.config}",
+                       "seq_len": wl["seq"], "parallelism": parallelism, "workload": f"config {args.config}",
                        "tokens_per_step": toks / args.steps, "l2": "working set (params+activations, >10 GB) exceeds the 126 MB L2",
                        "optimizer": args.optimizer, "gemm": ops.gemm_backend(), "attention": ops.attn_backend(),
                        "params": cfg.num_params()},

@@ -59,6 +59,7 @@ def sizes_from_argv(default_lo=64 << 10, default_hi=1 << 30):
 def emit(rank, rows, name):
     if rank != 0:
         return
-    os.makedirs("gpurun_out", exist_ok=True)
-    with open(os.path.join("gpurun_out", name), "w") as f:
+    out_dir = os.environ.get("ODC_OUT_DIR", "bench_out")
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, name), "w") as f:
         json.dump(rows, f, indent=1)

@@ -70,6 +70,7 @@ def memory_metrics():
 
 
 def mark_done(args):
-    os.makedirs("gpurun_out", exist_ok=True)
-    with open(os.path.join("gpurun_out", f"{args.run_name}.done"), "w") as f:
+    out_dir = os.environ.get("ODC_OUT_DIR", "bench_out")
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, f"{args.run_name}.done"), "w") as f:
         f.write("done\n")

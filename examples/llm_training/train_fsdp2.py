@@ -100,8 +100,9 @@ def main():
         torch.cuda.cudart().cudaProfilerStop()
     if prof is not None:
         prof.stop()
-        os.makedirs("gpurun_out", exist_ok=True)
-        prof.export_chrome_trace(f"gpurun_out/trace_{args.run_name}_rank{rank}.json")
+        out_dir = os.environ.get("ODC_OUT_DIR", "bench_out")
+        os.makedirs(out_dir, exist_ok=True)
+        prof.export_chrome_trace(f"{out_dir}/trace_{args.run_name}_rank{rank}.json")
     mark_done(args)
     if ODC:
         fsdp2.stop()
