@@ -387,8 +387,9 @@ std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seql
   return {o, lse};
 }
 
-std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse,
-                                            Tensor cu_seqlens, int max_seqlen, bool causal, double scale, bool fused_qkv) {
+std::tuple<Tensor, Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse,
+                                                    Tensor cu_seqlens, int max_seqlen, bool causal, double scale,
+                                                    bool fused_qkv) {
   c10::cuda::CUDAGuard g(q.device());
   odc::bind_device(q.get_device());
   const int T = q.size(0), hq = q.size(1), d = q.size(2), hkv = k.size(1);
@@ -396,10 +397,10 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Ten
   TORCH_CHECK(o.stride(2) == 1 && o.stride(1) == d, "attention bwd: o heads packed");
   TORCH_CHECK(q.stride(2) == 1 && q.stride(1) == d && k.stride(2) == 1 && k.stride(1) == d && v.stride(2) == 1 &&
                   v.stride(1) == d && k.stride(0) == v.stride(0), "attention bwd: q/k/v layout");
-  Tensor dq, dk, dv;
+  Tensor dq, dk, dv, dqkv;
   if (fused_qkv) {
     // one [T, (hq + 2 hkv) d] gradient; dq/dk/dv are column views of it, so slicing costs nothing in autograd
-    auto dqkv = torch::empty({T, int64_t(hq + 2 * hkv) * d}, q.options());
+    dqkv = torch::empty({T, int64_t(hq + 2 * hkv) * d}, q.options());
     dq = dqkv.narrow(1, 0, int64_t(hq) * d).view({T, hq, d});
     dk = dqkv.narrow(1, int64_t(hq) * d, int64_t(hkv) * d).view({T, hkv, d});
     dv = dqkv.narrow(1, int64_t(hq + hkv) * d, int64_t(hkv) * d).view({T, hkv, d});
@@ -416,7 +417,7 @@ std::tuple<Tensor, Tensor, Tensor> attn_bwd(Tensor dout, Tensor q, Tensor k, Ten
                       q.stride(0), k.stride(0), o.stride(0), dq.stride(0), dk.stride(0), static_cast<float>(scale),
                       causal, gemm_status(q.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
         "attn_bwd");
-  return {dq, dk, dv};
+  return {dq, dk, dv, fused_qkv ? dqkv : dq};  // 4th: the fused gradient when requested
 }
 
 // --- single-primitive test entry points: addresses are plain integers so peers' mappings can be passed

@@ -212,7 +212,7 @@ class _VarlenAttention(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, lse, cu_seqlens = ctx.saved_tensors
         max_seqlen, causal, scale = ctx.cfg
-        dq, dk, dv = _ext().attn_bwd(do.contiguous(), q, k, v, o, lse, cu_seqlens, max_seqlen, causal, scale, False)
+        dq, dk, dv, _ = _ext().attn_bwd(do.contiguous(), q, k, v, o, lse, cu_seqlens, max_seqlen, causal, scale, False)
         _count(3)
         return dq, dk, dv, None, None, None, None
 
@@ -244,11 +244,8 @@ class _VarlenAttentionQKV(torch.autograd.Function):
         q = qkv[:, :nq].view(T, n_q, head_dim)
         k = qkv[:, nq:nq + nk].view(T, n_kv, head_dim)
         v = qkv[:, nq + nk:].view(T, n_kv, head_dim)
-        dq, _, _ = _ext().attn_bwd(do.contiguous(), q, k, v, o, lse, cu_seqlens, max_seqlen, causal, scale, True)
+        _, _, _, dqkv = _ext().attn_bwd(do.contiguous(), q, k, v, o, lse, cu_seqlens, max_seqlen, causal, scale, True)
         _count(3)
-        dqkv = dq
-        while dqkv._base is not None:  # dq is a column view of the fused gradient allocated by the kernel wrapper
-            dqkv = dqkv._base
         return dqkv, None, None, None, None, None, None, None
 
 
