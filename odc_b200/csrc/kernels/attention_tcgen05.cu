@@ -395,7 +395,10 @@ struct BwdCfg {
   static constexpr int kTile = 128 * D * 2;            // one [128][D] bf16 operand
   static constexpr int kStageBytes = 2 * kTile;        // Q_i and dO_i
   static constexpr int kPBytes = 128 * 128 * 2;
-  static constexpr int kSmem = 2 * kTile + kStages * kStageBytes + 2 * kPBytes + 1024 + 256;
+  // fp32 staging tile for the dQ reduction: D = 64 has room for its own 32 KiB, so the next P/dS can be written
+  // while the TMA unit still reads it; D = 128 reuses the (consumed) P and dS buffers
+  static constexpr int kDqStageBytes = (D == 64) ? 128 * 64 * 4 : 0;
+  static constexpr int kSmem = 2 * kTile + kStages * kStageBytes + 2 * kPBytes + kDqStageBytes + 1024 + 256;
 };
 
 __device__ __forceinline__ void red_add_v4_gpu(float* p, float a, float b, float c, float d) {
@@ -430,7 +433,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t ds_smem = p_smem + C::kPBytes;
   uint8_t* p_ptr = smem + 2 * C::kTile + C::kStages * C::kStageBytes;
   uint8_t* ds_ptr = p_ptr + C::kPBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + C::kPBytes);
+  constexpr bool kOwnStage = C::kDqStageBytes > 0;
+  uint8_t* stage_ptr = kOwnStage ? ds_ptr + C::kPBytes : p_ptr;
+  const uint32_t stage_smem = kOwnStage ? ds_smem + C::kPBytes : p_smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ds_ptr + C::kPBytes + C::kDqStageBytes);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t kv_full = bar0;
   const uint32_t qdo_full0 = bar0 + 8;                      // [kStages]
@@ -577,7 +583,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       if (!(ok = mbar_wait(sdp_full, it & 1, wc, 36))) break;
       tc_fence_after();
       // the P/dS buffers double as the staging tile of the previous dQ reduction: wait until TMA has read it
-      if (it > 0) {
+      if (!kOwnStage && it > 0) {
         if (!(ok = mbar_wait(stg_free, (it - 1) & 1, wc, 39))) break;
       }
       uint32_t rs[64], rd[64];
@@ -613,6 +619,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // global accumulator; rows past the end of the sequence are staged as zeros
       if (!(ok = mbar_wait(dq_full, it & 1, wc, 37))) break;
       tc_fence_after();
+      if (kOwnStage && it > 0) {  // the private staging tile of the previous query tile must have been read
+        if (!(ok = mbar_wait(stg_free, (it - 1) & 1, wc, 39))) break;
+      }
 #pragma unroll 1
       for (int c = 0; c < D / 64; ++c) {
         uint32_t r[32];
@@ -622,7 +631,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
         for (int v = 0; v < 8; ++v) {
           uint4 o = q_valid ? make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]) : make_uint4(0, 0, 0, 0);
-          *reinterpret_cast<uint4*>(p_ptr + box * 16384 + row * 128 + ((v ^ (row & 7)) << 4)) = o;
+          *reinterpret_cast<uint4*>(stage_ptr + box * 16384 + row * 128 + ((v ^ (row & 7)) << 4)) = o;
         }
       }
       tc_fence_before();
@@ -636,7 +645,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (mbar_wait(stg_ready, it & 1, wc, 40)) {
 #pragma unroll
           for (int b2 = 0; b2 < D / 32; ++b2)
-            tma_reduce_add_2d(&tmap_dq, p_smem + b2 * 16384, head * D + 32 * b2, seq_start + i * 128);
+            tma_reduce_add_2d(&tmap_dq, stage_smem + b2 * 16384, head * D + 32 * b2, seq_start + i * 128);
           bulk_commit_group();
           bulk_wait_group_read0();
         }

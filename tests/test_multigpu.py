@@ -247,3 +247,28 @@ def test_fsdp1_mixed_precision_matches_stock_over_nvlink():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     _launch(FSDP1, 2, timeout=600)
+
+
+IPC = """
+from odc_b200.primitives import get_ipc_handle, reconstruct_tensor
+from odc_b200 import _ext
+ext = _ext.load()
+# rank 0 exports a view that starts inside a cudaMalloc allocation; rank 1 maps it and reads it with a peer-load kernel
+buf = torch.arange(4096, device=dev, dtype=torch.float32) + 1000 * rank
+handles = [None] * world
+dist.all_gather_object(handles, get_ipc_handle(buf[128:]))
+torch.cuda.synchronize(); dist.barrier()
+if rank == 1:
+    remote = reconstruct_tensor(handles[0], (4096 - 128,), torch.float32)
+    out = torch.empty(4096 - 128, device=dev)
+    ext.get_block(out, remote.data_ptr())
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.arange(128, 4096, device=dev, dtype=torch.float32)), out[:4]
+torch.cuda.synchronize(); dist.barrier()
+"""
+
+
+def test_ipc_handle_across_processes():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(IPC, 2, timeout=300, env={"PYTORCH_NO_CUDA_MEMORY_CACHING": "1"})
