@@ -182,7 +182,51 @@ def small_attention():
     print("small_attention ok", float(o.float().abs().mean()))
 
 
+def small_comm():
+    """gather + scatter_accumulate with 8 emulated peers (local buffers), 16 MiB shards: small case for ncu captures."""
+    from odc_b200 import _ext
+    ext = _ext.load()
+    world, n = 8, 8 << 20
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    shards = [torch.randn(n, device="cuda").bfloat16() for _ in range(world)]
+    table = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64, device="cuda")
+    out = torch.empty(world, n, dtype=torch.bfloat16, device="cuda")
+    grads = torch.randn(world, n // 2, device="cuda")
+    accs = [torch.zeros(n // 2, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    at = torch.tensor([s.data_ptr() for s in accs], dtype=torch.int64, device="cuda")
+    ct = torch.tensor([s.data_ptr() for s in ctrs], dtype=torch.int64, device="cuda")
+    for _ in range(3):
+        ext.gather(out, table, n, torch.bfloat16, 0, False, status)
+        ext.scatter_accumulate(grads, at, ct, n // 2, torch.float32, 0, 1.0, False, status)
+    torch.cuda.synchronize()
+    print("small_comm ok", int(ctrs[0][0]))
+
+
+def small_fused():
+    """The two GEMMs fused with communication, 8 emulated owners: small case for ncu captures."""
+    from odc_b200 import _ext
+    ext = _ext.load()
+    world, M, N, K = 8, 8192, 4096, 2048
+    rows_per = N // world
+    W = torch.randn(N, K, device="cuda").bfloat16()
+    shards = [W[r * rows_per:(r + 1) * rows_per].clone() for r in range(world)]
+    table = torch.tensor([s.data_ptr() for s in shards], dtype=torch.int64, device="cuda")
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w_local = torch.empty(N, K, dtype=torch.bfloat16, device="cuda")
+    dy = torch.randn(M, N, device="cuda").bfloat16()
+    accs = [torch.zeros(rows_per * K, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    ct = torch.tensor([s.data_ptr() for s in ctrs], dtype=torch.int64, device="cuda")
+    for _ in range(3):
+        y = ext.gemm_gather(x, table, w_local, None, rows_per, 0)
+        ext.gemm_wgrad_scatter_tma(dy, x, [a.data_ptr() for a in accs], ct, 0, rows_per, 1.0)
+    torch.cuda.synchronize()
+    print("small_fused ok", float(y.float().abs().mean()), int(ctrs[0][0]))
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": bench_gemm, "elementwise": bench_elementwise, "comm": bench_comm, "attention": bench_attention,
-     "small_gemm": small_gemm, "small_attention": small_attention}[which]()
+     "small_gemm": small_gemm, "small_attention": small_attention, "small_comm": small_comm,
+     "small_fused": small_fused}[which]()
