@@ -24,10 +24,9 @@ import logging
 from typing import Any, Dict, List, Optional
 
 import torch
-import torch.distributed as dist
 import torch.distributed.fsdp._runtime_utils as _ru
 import torch.distributed.fsdp._traversal_utils as _tu
-from torch.distributed.fsdp._common_utils import HandleTrainingState, _FSDPState
+from torch.distributed.fsdp._common_utils import _FSDPState
 from torch.distributed.fsdp._flat_param import FlatParamHandle, HandleShardingStrategy
 
 from ..primitives import GatherService, ReductionService

@@ -30,7 +30,7 @@ from __future__ import annotations
 
 import logging
 from dataclasses import dataclass, field
-from typing import Any, Callable, Dict, List, Optional
+from typing import Any, Dict, List, Optional
 
 import torch
 import torch.distributed as dist
@@ -39,7 +39,6 @@ from torch.distributed.fsdp._fully_shard._fsdp_collectives import AllGatherResul
 from torch.distributed.fsdp._fully_shard._fsdp_common import (DDPMeshInfo, FSDPMeshInfo, _get_dim0_padded_size)
 from torch.distributed.fsdp._fully_shard._fsdp_param import FSDPParam, ShardedState
 from torch.distributed.fsdp._fully_shard._fsdp_param_group import FSDPParamGroup
-from torch.distributed.tensor import DTensor
 
 from ..primitives import GatherService, ReductionService
 from ..runtime import control

@@ -7,7 +7,7 @@ sequences of a microbatch concatenated, ``cu_seqlens`` giving sequence boundarie
 from __future__ import annotations
 
 import math
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 import torch.nn.functional as F

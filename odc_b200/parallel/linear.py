@@ -16,7 +16,6 @@ import math
 from typing import List, Optional
 
 import torch
-import torch.distributed as dist
 import torch.nn as nn
 
 from .. import ops

@@ -16,7 +16,7 @@ touching the FSDP integration:
 from __future__ import annotations
 
 import time
-from typing import List, Optional, Sequence
+from typing import Sequence
 
 import torch
 
