@@ -293,7 +293,13 @@ __global__ void wait_counter_kernel(const unsigned long long* ctr, unsigned long
 }
 
 int grid_for(size_t tiles, int sm_count) {
-  size_t cap = size_t(sm_count) * 2;
+  // ODC_COMM_CTAS caps the grid of the communication kernels: fewer CTAs leave more of each SM to the GEMMs
+  // they overlap with, at the price of fewer bytes in flight on the links
+  static const int env_cap = [] {
+    const char* e = getenv("ODC_COMM_CTAS");
+    return e != nullptr ? atoi(e) : 0;
+  }();
+  size_t cap = env_cap > 0 ? size_t(env_cap) : size_t(sm_count) * 2;
   size_t g = tiles < cap ? tiles : cap;
   return g < 1 ? 1 : static_cast<int>(g);
 }
