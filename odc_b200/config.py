@@ -63,6 +63,15 @@ def debug_bounds() -> bool:
     return os.environ.get("ODC_DEBUG_BOUNDS", "0") not in ("0", "", "false")
 
 
+def deterministic() -> bool:
+    """``ODC_DETERMINISTIC=1``: per-source slots on the owner, summed in rank order at ``sync`` (debugging aid).
+
+    The default path adds every producer's rows into one accumulator with remote floating-point reductions,
+    whose order across producers varies from run to run.
+    """
+    return os.environ.get("ODC_DETERMINISTIC", "0") not in ("0", "", "false")
+
+
 def local_world_size(default: int) -> int:
     """GPUs per node: ``RAY_LOCAL_WORLD_SIZE`` overrides ``LOCAL_WORLD_SIZE`` (utils.py:195-199)."""
     for name in ("RAY_LOCAL_WORLD_SIZE", "LOCAL_WORLD_SIZE"):

@@ -52,7 +52,7 @@ def wgrad_scatter(dy: torch.Tensor, x: torch.Tensor, reduction: ReductionService
                   rows_per_rank: int, pg: Optional[dist.ProcessGroup] = None, scale: float = 1.0) -> None:
     """Add ``scale * dy.T @ x`` (shape ``[n_out, k_in]``, rows split ``rows_per_rank`` per owner) into ``key``."""
     ranks = control.group_ranks(pg)
-    acc = reduction.get_accumulation(key)
+    acc = reduction.scatter_target(key)
     dy2 = dy.reshape(-1, dy.shape[-1])
     x2 = x.reshape(-1, x.shape[-1])
     n_out, k_in = dy2.shape[1], x2.shape[1]

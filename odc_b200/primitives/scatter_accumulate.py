@@ -23,6 +23,7 @@ from typing import Dict, Hashable, Optional
 import torch
 import torch.distributed as dist
 
+from .. import config
 from ..runtime import control
 from ..runtime.registry import SymmBufferRegistry
 from ..runtime.transport import Transport, make_transport
@@ -37,6 +38,10 @@ def accumulation_key(key: Hashable) -> str:
     return f"rs_accumulation_{key}"
 
 
+def slots_key(key: Hashable) -> str:
+    return f"rs_slots_{key}"
+
+
 class ReductionService:
     def __init__(self, accumulation_dtype: Optional[torch.dtype] = None, transport: Optional[Transport] = None):
         self.registry = SymmBufferRegistry.get_instance()
@@ -45,6 +50,9 @@ class ReductionService:
         self.accumulations: Dict[Hashable, torch.Tensor] = {}
         self.dispatched: Dict[int, int] = {}   # owner global rank -> contributions sent (cumulative)
         self.expected_total = 0                 # contributions this rank has been told to expect
+        # deterministic mode: one slot per producer on every owner, reduced in rank order at sync
+        self.deterministic = config.deterministic()
+        self.slots: Dict[Hashable, torch.Tensor] = {}
         self.counter = self.registry.get_or_create_symm_buffer(COUNTER_KEY, (8,), torch.int64)
         self.counter.zero_()
         self._sync_device()
@@ -64,6 +72,10 @@ class ReductionService:
         acc_dtype = self.accumulation_dtype or input_dtype
         acc = self.registry.get_or_create_symm_buffer(accumulation_key(key), (shard_numel,), acc_dtype)
         acc.zero_()
+        if self.deterministic:
+            slots = self.registry.get_or_create_symm_buffer(slots_key(key), (control.world_size(), shard_numel), acc_dtype)
+            slots.zero_()
+            self.slots[key] = slots
         self._sync_device()
         control.host_barrier()
         self.accumulations[key] = acc
@@ -86,8 +98,9 @@ class ReductionService:
             raise ValueError(f"accumulator of {key!r} holds {acc.numel()} elements, input rows have {shard}")
         me = control.rank()
         my_index = ranks.index(me)
+        target = self.scatter_target(key)
         with nvtx_range("odc::scatter_accumulate"):
-            self.transport.scatter_add(input.view(n, shard), acc, self.counter, ranks, my_index, scale)
+            self.transport.scatter_add(input.view(n, shard), target, self.counter, ranks, my_index, scale)
         self.note_dispatch(ranks)
 
     def note_dispatch(self, ranks) -> None:
@@ -99,12 +112,18 @@ class ReductionService:
     def get_accumulation(self, key: Hashable) -> torch.Tensor:
         return self.accumulations[key]
 
+    def scatter_target(self, key: Hashable) -> torch.Tensor:
+        """The buffer a producer adds into on every owner: the shared accumulator, or this rank's slot."""
+        return self.slots[key][control.rank()] if self.deterministic else self.accumulations[key]
+
     def has_accumulation(self, key: Hashable) -> bool:
         return key in self.accumulations
 
     def clear_accumulations(self) -> None:
         for acc in self.accumulations.values():
             acc.zero_()
+        for slots in self.slots.values():
+            slots.zero_()
 
     # -- once per minibatch ------------------------------------------------------------------
     def sync(self, pg: Optional[dist.ProcessGroup] = None) -> None:
@@ -114,8 +133,15 @@ class ReductionService:
             everyone = control.all_gather_object(dict(self.dispatched))
             self.expected_total = sum(d.get(me, 0) for d in everyone)
             self.transport.wait_arrivals(self.counter, self.expected_total)
+            if self.deterministic:
+                for key, slots in self.slots.items():  # fixed order: rank 0 first
+                    acc = self.accumulations[key]
+                    acc.zero_()
+                    for r in range(slots.shape[0]):
+                        acc.add_(slots[r])
 
     def stop(self) -> None:
         self._sync_device()
         control.host_barrier()
         self.accumulations.clear()
+        self.slots.clear()

@@ -69,3 +69,43 @@ def test_offset_allocator():
     a.release(x); a.release(z)
     with pytest.raises(MemoryError):
         a.alloc(2 << 20)
+
+
+def _deterministic(rank, world, trial):
+    import time
+
+    import odc_b200 as odc
+    from odc_b200.runtime import control
+    odc.init_nvshmem("cpu", 64 << 20)
+    red = odc.ReductionService(accumulation_dtype=torch.float32)
+    assert red.deterministic
+    n = 4096
+    red.register("g", n, torch.float32)
+    g = torch.Generator().manual_seed(100 + rank)
+    for k in range(2 + rank):
+        time.sleep(0.001 * ((rank * 7 + trial * 3 + k) % 5))     # shuffle arrival order between trials
+        red.scatter_accumulate("g", torch.randn(world * n, generator=g) * 1e3)
+    red.sync()
+    out = red.get_accumulation("g").clone()
+    control.host_barrier()
+    red.clear_accumulations()
+    assert float(red.get_accumulation("g").abs().sum()) == 0.0
+    red.stop()
+    odc.finalize_distributed()
+    return out
+
+
+def test_deterministic_mode_is_bitwise_reproducible():
+    runs = [run_ranks(_deterministic, 3, t, env={"ODC_DETERMINISTIC": "1"}) for t in range(2)]
+    for r in range(3):
+        assert torch.equal(runs[0][r], runs[1][r])
+    # and it is the fixed-order sum: producers in rank order, each producer's rounds in issue order
+    n = 4096
+    want = torch.zeros(n)
+    for p in range(3):
+        g = torch.Generator().manual_seed(100 + p)
+        slot = torch.zeros(n)
+        for k in range(2 + p):
+            slot += (torch.randn(3 * n, generator=g) * 1e3).view(3, n)[0]
+        want += slot
+    assert torch.equal(runs[0][0], want)
