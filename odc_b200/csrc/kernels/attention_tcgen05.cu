@@ -551,6 +551,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dk, make_smem_desc(ds_smem + k * 2048, 16384, 1024), make_smem_desc(q_src + k * 2048, 16384, 1024),
                    idesc_tt, (it > 0 || k > 0) ? 1u : 0u);
         }
+        umma_commit(qdo_empty0 + 8 * st);  // Q_i / dO_i are not read again: their stage can be refilled now
         // dQ_i = dS K   (reduction over the 128 keys)
         if (kPrivateDq && it > 0) {  // the private dQ tile of the previous query tile must have been read out
           if (!(ok = mbar_wait(dq_read, (it - 1) & 1, wc, 34))) break;
@@ -561,7 +562,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           umma_f16(tm_dq, make_smem_desc(ds_smem + (k >> 2) * 16384 + (k & 3) * 32, 16, 1024),
                    make_smem_desc(k_smem + k * 2048, 16384, 1024), idesc_dq, k > 0 ? 1u : 0u);
         }
-        umma_commit(qdo_empty0 + 8 * st);
         umma_commit(dq_full);
       }
       if (ok) umma_commit(dkv_full);

@@ -103,3 +103,24 @@ def test_fsdp2_single_gpu_training_step(single_rank_pg, monkeypatch):
         assert fsdp2.transport_launches() > 0
     finally:
         fsdp2.stop()
+
+
+def test_deterministic_reduction_mode_gpu(monkeypatch):
+    import odc_b200 as odc
+    monkeypatch.setenv("ODC_DETERMINISTIC", "1")
+    torch.cuda.set_device(0)
+    odc.init_nvshmem(torch.device("cuda", 0), 1 << 30)
+    try:
+        red = odc.ReductionService(accumulation_dtype=torch.float32)
+        assert red.deterministic
+        xs = [torch.randn(1 << 16, device="cuda") for _ in range(3)]
+        for x in xs:
+            red.scatter_accumulate("k", x)
+        red.sync()
+        want = torch.zeros(1 << 16, device="cuda")
+        for x in xs:
+            want += x
+        assert torch.equal(red.get_accumulation("k"), want)
+        red.stop()
+    finally:
+        odc.finalize_distributed()
