@@ -220,9 +220,17 @@ def small_fused():
     ct = torch.tensor([s.data_ptr() for s in ctrs], dtype=torch.int64, device="cuda")
     for _ in range(3):
         y = ext.gemm_gather(x, table, w_local, None, rows_per, 0)
+        dx = ext.gemm_gather_dgrad(dy, table, w_local, rows_per)
         ext.gemm_wgrad_scatter_tma(dy, x, [a.data_ptr() for a in accs], ct, 0, rows_per, 1.0)
     torch.cuda.synchronize()
-    print("small_fused ok", float(y.float().abs().mean()), int(ctrs[0][0]))
+    print("small_fused ok", float(y.float().abs().mean()), float(dx.float().abs().mean()), int(ctrs[0][0]))
+    # device time of the gather-fused GEMMs against a plain GEMM on an already-assembled weight
+    from odc_b200 import ops
+    t_fwd = timed(lambda: ext.gemm_gather(x, table, w_local, None, rows_per, 0))
+    t_dg = timed(lambda: ext.gemm_gather_dgrad(dy, table, w_local, rows_per))
+    t_pf = timed(lambda: ops.gemm(x, w_local, "nt"))
+    t_pd = timed(lambda: ops.gemm(dy, w_local, "nn"))
+    print(f"gather+fwd {t_fwd:.3f} ms (plain {t_pf:.3f})  gather+dgrad {t_dg:.3f} ms (plain {t_pd:.3f})")
 
 
 if __name__ == "__main__":

@@ -365,6 +365,25 @@ Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<T
   return y;
 }
 
+Tensor gemm_gather_dgrad(Tensor dy, Tensor shard_table, Tensor w_local, int64_t rows_per_rank) {
+  c10::cuda::CUDAGuard g(dy.device());
+  odc::bind_device(dy.get_device());
+  TORCH_CHECK(dy.dim() == 2 && w_local.dim() == 2 && dy.size(1) == w_local.size(0),
+              "gemm_gather_dgrad: dy [M,N], w_local [N,K]");
+  TORCH_CHECK(dy.scalar_type() == at::kBFloat16 && w_local.scalar_type() == at::kBFloat16 && w_local.is_contiguous() &&
+                  dy.stride(1) == 1, "gemm_gather_dgrad: bf16, contiguous weight buffer");
+  const int M = dy.size(0), N = dy.size(1), K = w_local.size(1);
+  auto dx = torch::empty({M, K}, dy.options());
+  auto flags = torch::empty({(N + 255) / 256}, dy.options().dtype(at::kInt));
+  check(odc::gemm_gather_nn(dy.data_ptr(), reinterpret_cast<const long long*>(shard_table.data_ptr<int64_t>()),
+                            w_local.data_ptr(), dx.data_ptr(), M, N, K, dy.stride(0), dx.stride(0),
+                            static_cast<int>(rows_per_rank), static_cast<int>(shard_table.numel()),
+                            reinterpret_cast<unsigned int*>(flags.data_ptr<int>()),
+                            gemm_status(dy.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+        "gemm_gather_dgrad");
+  return dx;
+}
+
 std::tuple<Tensor, Tensor> attn_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_seqlen, bool causal,
                                     double scale) {
   c10::cuda::CUDAGuard g(q.device());
@@ -491,6 +510,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_wgrad_scatter", &gemm_wgrad_scatter);
   m.def("gemm_wgrad_scatter_tma", &gemm_wgrad_scatter_tma);
   m.def("gemm_gather", &gemm_gather);
+  m.def("gemm_gather_dgrad", &gemm_gather_dgrad);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
   m.def("kernel_status", &kernel_status);

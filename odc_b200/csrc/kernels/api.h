@@ -79,6 +79,12 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
                            int M, int N, int K, long long ldx, long long ldy, int rows_per_rank, int nranks,
                            int start_rank, unsigned int* panel_flags, int* status, int sm_count,
                            cudaStream_t stream);
+// dX[M, k_in] = dY[M, n_out] W[n_out, k_in] with W row-sharded as above: the gathered rows are the reduction
+// dimension, so the k-loop of every output tile follows the arrival of the 256-row groups (first tile of a CTA)
+// and later tiles find the whole weight in w_local.  group_flags needs ceil(n_out / 256) words.
+cudaError_t gemm_gather_nn(const void* dy, const long long* shard_ptrs, void* w_local, void* dx, int M, int n_out,
+                           int k_in, long long lddy, long long lddx, int rows_per_rank, int nranks,
+                           unsigned int* group_flags, int* status, int sm_count, cudaStream_t stream);
 
 // ---- varlen attention ------------------------------------------------------------------------
 cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,

@@ -137,9 +137,52 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   p.b_local = static_cast<unsigned char*>(w_local);
   p.panel_flags = panel_flags;
   p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.start_rank = start_rank;
+  p.w_rows = N; p.w_cols = K;
   cudaError_t e = cudaMemsetAsync(panel_flags, 0, sizeof(unsigned int) * p.tiles_n, stream);
   if (e != cudaSuccess) return e;
   // every CTA also fetches, so use the whole machine even when there are few tiles
+  const int grid = sm_count;
+  gemm_bf16_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, OwnerMaps{}, p);
+  return cudaGetLastError();
+}
+
+cudaError_t gemm_gather_nn(const void* dy, const long long* shard_ptrs, void* w_local, void* dx, int M, int n_out,
+                           int k_in, long long lddy, long long lddx, int rows_per_rank, int nranks,
+                           unsigned int* group_flags, int* status, int sm_count, cudaStream_t stream) {
+  // dx[M, k_in] = dy[M, n_out] * W[n_out, k_in]; W's rows (the reduction dimension) are gathered
+  if (M == 0 || k_in == 0 || nranks == 0) return cudaSuccess;
+  if (n_out == 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(dx)) & 15)
+    return cudaErrorMisalignedAddress;
+  if ((lddy % 8) || (lddx % 8) || (n_out % 8) || (k_in % 128)) return cudaErrorInvalidValue;
+  if (static_cast<long long>(rows_per_rank) * nranks < n_out) return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_bf16_kernel<kModeGather>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  CUtensorMap ta, tb, tc;
+  if (!encode_tile_map_2d(&ta, dy, n_out, M, lddy * 2, 64, BM)) return cudaErrorInvalidValue;
+  // B is MN-major: rows = reduction index, box {64 output columns, 64 reduction rows}
+  if (!encode_tile_map_2d(&tb, w_local, k_in, n_out, static_cast<uint64_t>(k_in) * 2, 64, 64)) return cudaErrorInvalidValue;
+  if (!encode_tile_map_2d(&tc, dx, k_in, M, lddx * 2, 64, BM)) return cudaErrorInvalidValue;
+  Params p{};
+  p.c = dx;
+  p.M = M; p.N = k_in; p.K = n_out;
+  p.ldc = lddx;
+  p.b_mn = 1;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (k_in + BN - 1) / BN;
+  p.status = status;
+  p.shard_ptrs = shard_ptrs;
+  p.b_local = static_cast<unsigned char*>(w_local);
+  p.panel_flags = group_flags;
+  p.rows_per_rank = rows_per_rank; p.nranks = nranks;
+  p.w_rows = n_out; p.w_cols = k_in;
+  cudaError_t e = cudaMemsetAsync(group_flags, 0, sizeof(unsigned int) * ((n_out + BN - 1) / BN), stream);
+  if (e != cudaSuccess) return e;
   const int grid = sm_count;
   gemm_bf16_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, OwnerMaps{}, p);
   return cudaGetLastError();

@@ -54,9 +54,10 @@ struct Params {
   float scale;
   unsigned int* done_slot;     // self-resetting CTA completion counter (scratch)
   // --- kModeGather: operand B is assembled from the owners' shards while the GEMM runs ---
-  const long long* shard_ptrs; // [nranks] base address of each owner's [rows_per_rank, K] bf16 shard
-  unsigned char* b_local;      // local [N, K] bf16 buffer the shards are gathered into (tensor map B covers it)
-  unsigned int* panel_flags;   // [tiles_n] chunks landed per 256-row panel (zeroed before launch)
+  const long long* shard_ptrs; // [nranks] base address of each owner's [rows_per_rank, w_cols] bf16 shard
+  unsigned char* b_local;      // local [w_rows, w_cols] bf16 buffer the shards are gathered into (tensor map B covers it)
+  unsigned int* panel_flags;   // [ceil(w_rows / 256)] chunks landed per 256-row group (zeroed before launch)
+  int w_rows, w_cols;          // gathered matrix: [N, K] when B is K-major (y = x W^T), [K, N] when MN-major (dx = dy W)
   int start_rank;
 };
 
@@ -136,36 +137,46 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       prefetch_tmap(&tmap_a);
       prefetch_tmap(&tmap_b);
+      // gather mode: wait (bounded) until every chunk of 256-row group `g` of the gathered matrix is in local memory
+      int groups_ready = 0;  // groups [0, groups_ready) are known to be complete
+      auto wait_group = [&](int g) -> bool {
+        if (g < groups_ready) return true;
+        const long long group_bytes = static_cast<long long>(min(BN, p.w_rows - g * BN)) * p.w_cols * 2;
+        const unsigned int target = static_cast<unsigned int>((group_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * 4u;
+        const uint64_t t0 = globaltimer_ns();
+        unsigned int seen;
+        while (true) {
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.panel_flags + g) : "memory");
+          if (seen >= target) break;
+          if (*abort_flag) return false;
+          if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            *abort_flag = 1;
+            report(p.status, kErrPipelineTimeout, 5, g);
+            return false;
+          }
+          __nanosleep(64);
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> visible to TMA reads
+        // the reduction dimension is walked in order, so in the MN-major case all earlier groups are complete too
+        if (p.b_mn) groups_ready = g + 1;
+        return true;
+      };
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * BM;
         const int n0 = (tile / p.tiles_m) * BN;
         if constexpr (kMode == kModeGather) {
-          // the 256 rows of B this tile multiplies must have landed in local memory first
-          const int panel = tile / p.tiles_m;
-          const long long panel_bytes = static_cast<long long>(min(BN, p.N - panel * BN)) * p.K * 2;
-          const unsigned int target = static_cast<unsigned int>((panel_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * 4u;
-          const uint64_t t0 = globaltimer_ns();
-          unsigned int seen;
-          while (true) {
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.panel_flags + panel) : "memory");
-            if (seen >= target) break;
-            if (*abort_flag) { ok = false; break; }
-            if (globaltimer_ns() - t0 > kWaitBudgetNs) {
-              *abort_flag = 1;
-              report(p.status, kErrPipelineTimeout, 5, panel);
-              ok = false;
-              break;
-            }
-            __nanosleep(64);
-          }
-          if (!ok) break;
-          asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> visible to TMA reads
+          // B K-major (forward): the 256 weight rows this tile multiplies must have landed in local memory first
+          if (!p.b_mn && !(ok = wait_group(tile / p.tiles_m))) break;
         }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
+          if constexpr (kMode == kModeGather) {
+            // B MN-major (input gradient): the gathered rows are the reduction dimension, 4 k-blocks per group
+            if (p.b_mn && !(ok = wait_group((kb * BK) / BN))) break;
+          }
           if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, wc, 1))) break;
           const uint32_t sa = base + s * kStageBytes;
           const uint32_t sb = sa + kATile;
@@ -232,9 +243,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // step and CTA, 16 KiB per warp with 16 x 16-byte loads in flight per lane; after its part a warp
     // makes the stores visible and counts them on the panel's flag.
     const int fw = warp - (2 + Roles<kMode>::kEpilogueWarps);
-    const long long total_bytes = static_cast<long long>(p.N) * p.K * 2;
-    const long long shard_bytes = static_cast<long long>(p.rows_per_rank) * p.K * 2;
-    const long long panel_bytes_full = static_cast<long long>(BN) * p.K * 2;  // multiple of the chunk size (K % 128 == 0)
+    const long long total_bytes = static_cast<long long>(p.w_rows) * p.w_cols * 2;
+    const long long shard_bytes = static_cast<long long>(p.rows_per_rank) * p.w_cols * 2;
+    const long long panel_bytes_full = static_cast<long long>(BN) * p.w_cols * 2;  // multiple of the chunk size (w_cols % 128 == 0)
     const long long n_chunks = (total_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes;
     for (long long c = blockIdx.x; c < n_chunks; c += gridDim.x) {
       const long long byte0 = c * kFetchChunkBytes + fw * kFetchWarpBytes;

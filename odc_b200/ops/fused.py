@@ -5,6 +5,9 @@ symmetric heap; the kernel pulls the owners' shards into a local buffer panel by
 tensor cores already multiply the panels that have landed.  Returns the assembled weight too, so
 the backward pass (or a later microbatch) can reuse it without another transfer.
 
+``gather_dgrad``: ``dx = dy @ W`` with the same sharded ``W``; the shards are pulled again instead of
+keeping the assembled weight alive between forward and backward.
+
 ``wgrad_scatter``: ``dW = dy.T @ x`` whose epilogue adds every output tile into the owning rank's
 fp32 accumulator and signals arrival, with the same bookkeeping as
 ``ReductionService.scatter_accumulate`` (one dispatched contribution per owner per call).
@@ -46,6 +49,33 @@ def gather_linear(x: torch.Tensor, weight_shard: torch.Tensor, out_features: int
         w_full = torch.cat([peers[r] for r in ranks], dim=0)[:out_features].clone()
         y = torch.nn.functional.linear(x2, w_full.to(x2.dtype), bias)
     return y.view(*x.shape[:-1], out_features), w_full
+
+
+def gather_dgrad(dy: torch.Tensor, weight_shard: torch.Tensor, out_features: int,
+                 pg: Optional[dist.ProcessGroup] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``dx = dy @ W`` with ``W [out_features, K]`` row-sharded as in :func:`gather_linear`.
+
+    The gathered rows are the reduction dimension here: the k-loop of each CTA's first tile walks the
+    256-row groups as they land, later tiles read the assembled weight.  Returns ``(dx, w_full)``.
+    """
+    reg = SymmBufferRegistry.get_instance()
+    ranks = control.group_ranks(pg)
+    rows_per, K = weight_shard.shape
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    if dy2.is_cuda:
+        from .. import _ext
+        from . import _count
+        table = reg.peer_ptr_table(weight_shard, ranks)
+        w_full = torch.empty(out_features, K, dtype=weight_shard.dtype, device=dy.device)
+        if dy2.stride(1) != 1:
+            dy2 = dy2.contiguous()
+        dx = _ext.load().gemm_gather_dgrad(dy2, table, w_full, rows_per)
+        _count()
+    else:
+        peers = reg.get_peer_tensors(weight_shard)
+        w_full = torch.cat([peers[r] for r in ranks], dim=0)[:out_features].clone()
+        dx = dy2 @ w_full.to(dy2.dtype)
+    return dx.view(*dy.shape[:-1], K), w_full
 
 
 def wgrad_scatter(dy: torch.Tensor, x: torch.Tensor, reduction: ReductionService, key, param_offset: int,

@@ -4,8 +4,9 @@ Rows of ``W [out, in]`` are split evenly over the group; each rank keeps its fp3
 bf16 copy in the symmetric heap (what peers pull) and an fp32 gradient accumulator in the heap
 (what peers push into).  Forward is ONE kernel (``gather_linear``: shards stream in while the
 GEMM runs), the weight-gradient is ONE kernel (``wgrad_scatter``: tiles are reduced into their
-owners from the GEMM epilogue), and the input gradient is a plain GEMM on the already-assembled
-weight.  No rank waits for another between ``start_minibatch`` and ``finish_minibatch``.
+owners from the GEMM epilogue), and the input gradient is ONE kernel too (``gather_dgrad``: the
+shards are pulled again while the k-loop follows their arrival) unless ``keep_weight=True`` keeps
+the assembled weight from the forward pass.  No rank waits for another between ``start_minibatch`` and ``finish_minibatch``.
 
 This is the on-demand design applied at layer level instead of through FSDP's hooks; it covers the
 same two hot paths the reference patches into FSDP (odc/fsdp/fsdp2.py:218-313 and 607-742).
@@ -71,32 +72,42 @@ class _OdcLinearFn(torch.autograd.Function):
         p = layer.weight
         y, w_full = fused.gather_linear(x, p.lowp, p.out_features, p.pg, layer.bias)
         ctx.layer = layer
-        ctx.save_for_backward(x, w_full)
+        if layer.keep_weight:
+            ctx.save_for_backward(x, w_full)
+        else:
+            ctx.save_for_backward(x)  # the assembled weight is dropped; backward pulls the shards again
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, w_full = ctx.saved_tensors
         layer = ctx.layer
         p = layer.weight
+        x = ctx.saved_tensors[0]
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
         x2 = x.reshape(-1, x.shape[-1])
         dx = None
         if ctx.needs_input_grad[0]:
-            dx = ops.gemm(dy2, w_full, "nn").view(x.shape) if dy2.is_cuda else (dy2 @ w_full.to(dy2.dtype)).view(x.shape)
+            if not layer.keep_weight:
+                dx = fused.gather_dgrad(dy2, p.lowp, p.out_features, p.pg)[0].view(x.shape)
+            else:
+                w_full = ctx.saved_tensors[1]
+                dx = ops.gemm(dy2, w_full, "nn").view(x.shape) if dy2.is_cuda else (dy2 @ w_full.to(dy2.dtype)).view(x.shape)
         fused.wgrad_scatter(dy2, x2, _service(), p.key, 0, p.rows_per_rank, p.pg, layer.grad_scale)
         return dx, None
 
 
 class OdcLinear(nn.Module):
     def __init__(self, in_features: int, out_features: int, pg=None, name: Optional[str] = None, seed: int = 0,
-                 init_std: float = 0.02):
+                 init_std: float = 0.02, keep_weight: bool = False):
         super().__init__()
         global _next_id
         name = name or f"l{_next_id}"
         _next_id += 1
         self.weight = ShardedParameter(name, (out_features, in_features), pg, init_std=init_std, seed=seed)
         self.bias = None
+        # False: only the shard outlives the forward kernel (memory of a sharded model); the input
+        # gradient is then the gather-fused GEMM.  True trades out*in*2 bytes per layer for one transfer.
+        self.keep_weight = keep_weight
         self.grad_scale = 1.0 / self.weight.world
         _layers.append(self)
 

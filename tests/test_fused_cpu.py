@@ -1,14 +1,15 @@
 """OdcLinear (fused gather-GEMM / wgrad-scatter layer) on CPU ranks: same result as a dense layer."""
+import pytest
 import torch
 
 from _mp import run_ranks
 
 
-def _run(rank, world):
+def _run(rank, world, keep_weight):
     import odc_b200 as odc
     from odc_b200 import parallel
     odc.init_nvshmem("cpu", 64 << 20)
-    lin = parallel.OdcLinear(32, 50, seed=3)
+    lin = parallel.OdcLinear(32, 50, seed=3, keep_weight=keep_weight)
     torch.manual_seed(100 + rank)
     xs = [torch.randn(7 + rank, 32, requires_grad=True) for _ in range(1 + rank)]  # uneven microbatch counts
     parallel.start_minibatch()
@@ -29,9 +30,10 @@ def _run(rank, world):
     return out
 
 
-def test_odc_linear_matches_dense():
+@pytest.mark.parametrize("keep_weight", [False, True])
+def test_odc_linear_matches_dense(keep_weight):
     world = 2
-    res = run_ranks(_run, world)
+    res = run_ranks(_run, world, keep_weight)
     W = torch.cat([r["shard"] for r in res])[:50]
     Wb = W.bfloat16().float()  # peers pull the bf16 copy
     dW = torch.zeros(50, 32)

@@ -274,6 +274,23 @@ def test_gemm_gather_emulated_ranks(ext, world, M, N, K):
     torch.testing.assert_close(y.float(), x.float() @ W[:N].float().t() + bias.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
 
 
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (1000, 1376, 512), (8192, 3072, 2048), (300, 264, 128)])
+def test_gemm_gather_dgrad_emulated_ranks(ext, world, M, N, K):
+    """dX = dY W with W's rows (the reduction dimension) assembled from shards while the GEMM runs."""
+    torch.manual_seed(M + N + K + 1)
+    rows_per = (N + world - 1) // world
+    W = (0.1 * torch.randn(world * rows_per, K, device="cuda")).bfloat16()
+    shards = [W[r * rows_per:(r + 1) * rows_per].clone() for r in range(world)]
+    dy = torch.randn(M, N, device="cuda").bfloat16()
+    w_local = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
+    dx = ext.gemm_gather_dgrad(dy, _table(shards), w_local, rows_per)
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
+    assert torch.equal(w_local, W[:N])
+    torch.testing.assert_close(dx.float(), dy.float() @ W[:N].float(), rtol=2e-2, atol=2e-2 * math.sqrt(N) * 0.1)
+
+
 def test_linear_with_fused_residual():
     from odc_b200 import ops
     x = torch.randn(300, 512, device="cuda").bfloat16().requires_grad_()
