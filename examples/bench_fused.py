@@ -4,6 +4,7 @@
 
 (1) gather -> GEMM: Y = X W^T, W row-sharded.  Ours: one kernel.  Baseline: NCCL all_gather_into_tensor
     then torch.matmul (cuBLAS).  Roofline time = max(FLOPs / measured bf16 peak, inbound bytes / link).
+(1b) gather -> input gradient: dX = dY W with the same sharded W (the gathered rows are the reduction dimension).
 (2) wgrad -> scatter-accumulate: dW = dY^T X reduced into the owners' fp32 shards.  Ours: one kernel
     (+ arrival wait).  Baseline: torch.matmul, NCCL reduce_scatter_tensor (fp32), add_.
 Device-timed with CUDA events, max over ranks, median of the timed iterations.
@@ -49,8 +50,19 @@ def main():
         roof_ms = max(flops / (peak_tf * 1e12), inbound / (NVLINK_GBS * 1e9)) * 1e3
         r1 = dict(op="gather_gemm", world=world, M=M, N=N, K=K, ms=t_f, baseline_ms=t_b, roofline_ms=roof_ms,
                   frac_of_roofline=roof_ms / t_f)
-        # weight gradient
         dy = torch.randn(M, N, device=dev).bfloat16()
+        # input gradient: dX = dY W with W pulled again (same bytes and FLOPs as the forward product)
+
+        def base_dgrad():
+            dist.all_gather_into_tensor(w_full, shard)
+            return torch.matmul(dy, w_full[:N])
+
+        t_d = device_time_ms(lambda: fused.gather_dgrad(dy, shard, N), 10)
+        t_db = device_time_ms(base_dgrad, 10)
+        torch.testing.assert_close(fused.gather_dgrad(dy, shard, N)[0].float(), base_dgrad().float(), rtol=2e-2, atol=2e-1)
+        r3 = dict(op="gather_dgrad", world=world, M=M, N=N, K=K, ms=t_d, baseline_ms=t_db, roofline_ms=roof_ms,
+                  frac_of_roofline=roof_ms / t_d)
+        # weight gradient
         key = f"g{M}x{N}x{K}"
         red.register(key, rows_per * K, torch.float32)
         ref_acc = torch.zeros(rows_per * K, device=dev)
@@ -78,9 +90,10 @@ def main():
         roof2 = max(flops / (peak_tf * 1e12), outbound / (NVLINK_GBS * 1e9)) * 1e3
         r2 = dict(op="wgrad_scatter", world=world, M=M, N=N, K=K, ms=t_f2, baseline_ms=t_b2, roofline_ms=roof2,
                   frac_of_roofline=roof2 / t_f2)
-        rows += [r1, r2]
+        rows += [r1, r3, r2]
         if rank == 0:
             print(f"W={world} M={M} N={N} K={K}: gather+GEMM {t_f:.3f} ms (NCCL AG + cuBLAS {t_b:.3f} ms; roofline {roof_ms:.3f} ms -> {roof_ms / t_f:.2f} of {kind}) | "
+                  f"gather+dgrad {t_d:.3f} ms (NCCL AG + cuBLAS {t_db:.3f} ms -> {roof_ms / t_d:.2f}) | "
                   f"wgrad+scatter {t_f2:.3f} ms (cuBLAS + NCCL RS + add {t_b2:.3f} ms; roofline {roof2:.3f} ms -> {roof2 / t_f2:.2f})", flush=True)
         del x, dy, w_full, ref_acc, rs_out
     emit(rank, rows, f"fused_w{world}.json")
