@@ -28,6 +28,26 @@ from ..runtime import control
 from ..runtime.registry import SymmBufferRegistry
 
 
+_transports = {}
+
+
+def _spans_nodes(reg: SymmBufferRegistry, ranks) -> bool:
+    return any(not reg.heap.is_local(r) for r in ranks)
+
+
+def _gather_weight(reg: SymmBufferRegistry, weight_shard: torch.Tensor, ranks, out_features: int) -> torch.Tensor:
+    """Unfused assembly of ``W`` for groups that reach other nodes (their shards are not mapped here)."""
+    from ..runtime.transport import make_transport
+    tr = _transports.get(id(reg))
+    if tr is None or tr.registry is not reg:
+        tr = _transports[id(reg)] = make_transport(reg)
+    rows_per, K = weight_shard.shape
+    w = torch.empty(len(ranks) * rows_per, K, dtype=weight_shard.dtype, device=weight_shard.device)
+    me = control.rank()
+    tr.gather(w.view(len(ranks), -1), weight_shard, ranks, ranks.index(me) if me in ranks else 0)
+    return w[:out_features]
+
+
 def gather_linear(x: torch.Tensor, weight_shard: torch.Tensor, out_features: int,
                   pg: Optional[dist.ProcessGroup] = None, bias: Optional[torch.Tensor] = None
                   ) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -37,7 +57,11 @@ def gather_linear(x: torch.Tensor, weight_shard: torch.Tensor, out_features: int
     me = control.rank()
     rows_per, K = weight_shard.shape
     x2 = x.reshape(-1, x.shape[-1])
-    if x2.is_cuda:
+    if _spans_nodes(reg, ranks):
+        from . import gemm
+        w_full = _gather_weight(reg, weight_shard, ranks, out_features)
+        y = gemm(x2, w_full, "nt", bias=bias) if x2.is_cuda else torch.nn.functional.linear(x2, w_full.to(x2.dtype), bias)
+    elif x2.is_cuda:
         from .. import _ext
         from . import _count
         table = reg.peer_ptr_table(weight_shard, ranks)
@@ -62,7 +86,11 @@ def gather_dgrad(dy: torch.Tensor, weight_shard: torch.Tensor, out_features: int
     ranks = control.group_ranks(pg)
     rows_per, K = weight_shard.shape
     dy2 = dy.reshape(-1, dy.shape[-1])
-    if dy2.is_cuda:
+    if _spans_nodes(reg, ranks):
+        from . import gemm
+        w_full = _gather_weight(reg, weight_shard, ranks, out_features)
+        dx = gemm(dy2.contiguous(), w_full, "nn") if dy2.is_cuda else dy2 @ w_full.to(dy2.dtype)
+    elif dy2.is_cuda:
         from .. import _ext
         from . import _count
         table = reg.peer_ptr_table(weight_shard, ranks)
@@ -88,7 +116,23 @@ def wgrad_scatter(dy: torch.Tensor, x: torch.Tensor, reduction: ReductionService
     n_out, k_in = dy2.shape[1], x2.shape[1]
     if param_offset + rows_per_rank * k_in > acc.numel():
         raise ValueError("parameter does not fit in the accumulator at this offset")
-    if dy2.is_cuda:
+    if _spans_nodes(reduction.registry, ranks):
+        # unfused: form the gradient locally, then hand the rows to the transport (same-node owners over the
+        # mapped heap, the rest through the inter-node path)
+        if dy2.is_cuda:
+            from . import gemm
+            dw = gemm(dy2.contiguous(), x2.contiguous(), "tn", out_dtype=torch.float32)
+        else:
+            dw = dy2.float().t() @ x2.float()
+        pad = rows_per_rank * len(ranks) - n_out
+        if pad:
+            dw = torch.cat([dw, dw.new_zeros(pad, k_in)])
+        me = control.rank()
+        target = acc[param_offset:param_offset + rows_per_rank * k_in]
+        reduction.transport.scatter_add(dw.view(len(ranks), -1), target, reduction.counter, ranks,
+                                        ranks.index(me) if me in ranks else 0, scale)
+        reduction.note_dispatch(ranks)
+    elif dy2.is_cuda:
         from .. import _ext
         from . import _count
         reg = reduction.registry

@@ -87,7 +87,24 @@ def group_ranks(pg: Optional[dist.ProcessGroup]) -> List[int]:
 
 
 def get_local_world_size() -> int:
-    return config.local_world_size(world_size())
+    return min(config.local_world_size(world_size()), world_size())
+
+
+def node_ranks(r: Optional[int] = None) -> List[int]:
+    """Global ranks that share a node (one NVLink domain, one ``/dev/shm``) with rank ``r`` (default: this rank).
+
+    Ranks of a node are contiguous: ``[r - r % L, r - r % L + L)`` with ``L`` the local world size.
+    """
+    ws, lws = world_size(), get_local_world_size()
+    if lws <= 0 or ws % lws != 0:
+        raise ValueError(f"world size {ws} is not a multiple of the local world size {lws}")
+    r = rank() if r is None else r
+    base = r - r % lws
+    return list(range(base, base + lws))
+
+
+def num_nodes() -> int:
+    return world_size() // max(1, min(get_local_world_size(), world_size()))
 
 
 def get_local_world_pg():

@@ -108,6 +108,18 @@ class SymmetricHeap:
     def close(self) -> None:
         raise NotImplementedError
 
+    # Only the ranks of this node are mapped; the regions of other nodes are reached through the
+    # inter-node transport by heap offset (offsets are the same on every rank).
+    node: List[int]
+
+    def is_local(self, r: int) -> bool:
+        return self.node[0] <= r <= self.node[-1]
+
+    def _check_local(self, r: int) -> None:
+        if not self.is_local(r):
+            raise ValueError(f"rank {r} is on another node: its heap region is not mapped on rank {self.rank} "
+                             f"(node ranks {self.node[0]}..{self.node[-1]})")
+
 
 class HostShmHeap(SymmetricHeap):
     """CPU symmetric heap over ``/dev/shm`` files, one per rank."""
@@ -115,17 +127,18 @@ class HostShmHeap(SymmetricHeap):
     def __init__(self, nbytes: Optional[int] = None):
         self.device = torch.device("cpu")
         self.rank, self.world = control.rank(), control.world_size()
+        self.node = control.node_ranks()
         self.nbytes = _round_up(nbytes or config.symmetric_size("cpu"), 4096)
         token = control.job_token()
-        self._paths = [f"/dev/shm/odc_b200_{token}_{r}" for r in range(self.world)]
-        # create mine (sparse), then map everyone's after a barrier
+        self._paths = {r: f"/dev/shm/odc_b200_{token}_{r}" for r in self.node}
+        # create mine (sparse), then map the node's after a barrier
         with open(self._paths[self.rank], "wb") as f:
             f.truncate(self.nbytes)
         control.host_barrier()
-        self._maps = [
-            torch.from_file(p, shared=True, size=self.nbytes, dtype=torch.uint8) for p in self._paths
-        ]
-        self._lock_fds = [os.open(p, os.O_RDWR) for p in self._paths]
+        self._maps = {
+            r: torch.from_file(p, shared=True, size=self.nbytes, dtype=torch.uint8) for r, p in self._paths.items()
+        }
+        self._lock_fds = {r: os.open(p, os.O_RDWR) for r, p in self._paths.items()}
         self._alloc = OffsetAllocator(self.nbytes)
         self._base = self._maps[self.rank].data_ptr()
         control.host_barrier()
@@ -140,6 +153,7 @@ class HostShmHeap(SymmetricHeap):
         nb = numel * torch.empty((), dtype=dtype).element_size()
         if offset < 0 or offset + nb > self.nbytes:
             raise IndexError(f"heap view [{offset}, {offset + nb}) outside region of {self.nbytes} bytes")
+        self._check_local(r)
         return self._maps[r][offset : offset + nb].view(dtype)
 
     def local(self, offset, numel, dtype):
@@ -149,6 +163,7 @@ class HostShmHeap(SymmetricHeap):
         return self._view(r, offset, numel, dtype)
 
     def peer_ptr(self, r, offset):
+        self._check_local(r)
         return self._maps[r].data_ptr() + offset
 
     def offset_of(self, tensor):
@@ -173,10 +188,10 @@ class HostShmHeap(SymmetricHeap):
 
     def close(self) -> None:
         control.host_barrier()
-        for fd in self._lock_fds:
+        for fd in self._lock_fds.values():
             os.close(fd)
-        self._lock_fds = []
-        self._maps = []
+        self._lock_fds = {}
+        self._maps = {}
         try:
             os.unlink(self._paths[self.rank])
         except FileNotFoundError:
@@ -193,19 +208,22 @@ class CudaHeap(SymmetricHeap):
         self._ext = ext
         self.device = torch.device(device)
         self.rank, self.world = control.rank(), control.world_size()
+        self.node = control.node_ranks()
+        # the native heap spans one node: it knows ranks by their index within the node
+        li, lw = self.rank - self.node[0], len(self.node)
         self.nbytes = _round_up(nbytes or config.symmetric_size("cuda"), 2 << 20)
         self.mode = config.heap_mode()
-        token = control.job_token()
+        token = f"{control.job_token()}_n{self.node[0]}"
         dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         try:
-            self._h = ext.heap_create(self.rank, self.world, dev_index, self.nbytes, self.mode, token)
+            self._h = ext.heap_create(li, lw, dev_index, self.nbytes, self.mode, token)
         except RuntimeError as e:
             if self.mode != "vmm":
                 raise
             logger.warning("virtual-memory heap unavailable (%s); falling back to CUDA-IPC slab", e)
             self.mode = "ipc"
             self.nbytes = min(self.nbytes, config.parse_size(os.environ.get("ODC_IPC_SLAB_SIZE", "8G")))
-            self._h = ext.heap_create(self.rank, self.world, dev_index, self.nbytes, self.mode, token)
+            self._h = ext.heap_create(li, lw, dev_index, self.nbytes, self.mode, token)
         # every rank must agree on the mode (a fallback on one rank only would desynchronise offsets)
         modes = control.all_gather_object(self.mode)
         if len(set(modes)) != 1:
@@ -213,12 +231,12 @@ class CudaHeap(SymmetricHeap):
         if self.mode == "ipc":
             handles = control.all_gather_object(ext.heap_ipc_handle(self._h))
             for r, hb in enumerate(handles):
-                if r != self.rank:
-                    ext.heap_ipc_open(self._h, r, hb)
+                if r != self.rank and self.is_local(r):
+                    ext.heap_ipc_open(self._h, r - self.node[0], hb)
         control.host_barrier()  # all sockets bound / all slabs opened
         self._alloc = OffsetAllocator(self.nbytes)
         self._mapped = self.nbytes if self.mode == "ipc" else 0
-        self._bases = [ext.heap_base(self._h, r) for r in range(self.world)]
+        self._bases = {r: ext.heap_base(self._h, r - self.node[0]) for r in self.node}
 
     def alloc(self, nbytes: int) -> int:
         off = self._alloc.alloc(nbytes)
@@ -241,9 +259,11 @@ class CudaHeap(SymmetricHeap):
         nb = numel * torch.empty((), dtype=dtype).element_size()
         if offset < 0 or offset + nb > self._mapped:
             raise IndexError(f"heap view [{offset}, {offset + nb}) outside mapped {self._mapped} bytes")
+        self._check_local(r)
         return self._ext.tensor_from_ptr(self._bases[r] + offset, numel, dtype, self.device.index or 0)
 
     def peer_ptr(self, r, offset):
+        self._check_local(r)
         return self._bases[r] + offset
 
     def offset_of(self, tensor):

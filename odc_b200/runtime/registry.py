@@ -41,6 +41,11 @@ class SymmBufferRegistry:
         self._by_offset: Dict[int, Hashable] = {}
         self._updated: Dict[Hashable, bool] = {}
         self._ptr_tables: Dict[tuple, torch.Tensor] = {}
+        # server + client of the data path to other nodes; None while the job fits in one node
+        self.internode = None
+        if control.num_nodes() > 1:
+            from .internode import InterNodeEndpoint
+            self.internode = InterNodeEndpoint(heap)
 
     # -- singleton -------------------------------------------------------------------------
     @classmethod
@@ -137,10 +142,11 @@ class SymmBufferRegistry:
         return off
 
     def get_peer_tensors(self, local_tensor: torch.Tensor) -> List[torch.Tensor]:
-        """The same buffer on every rank of the heap, indexed by global rank."""
+        """The same buffer on every rank, indexed by global rank (``None`` for ranks of other nodes)."""
         off = self.offset_of(local_tensor)
         n, dt = local_tensor.numel(), local_tensor.dtype
-        return [self.heap.peer(r, off, n, dt).view(local_tensor.shape) for r in range(self.heap.world)]
+        return [self.heap.peer(r, off, n, dt).view(local_tensor.shape) if self.heap.is_local(r) else None
+                for r in range(self.heap.world)]
 
     def peer_ptrs(self, local_tensor: torch.Tensor, ranks: Sequence[int]) -> List[int]:
         off = self.offset_of(local_tensor)
@@ -169,5 +175,11 @@ class SymmBufferRegistry:
         self._by_offset.clear()
         self._updated.clear()
         self._ptr_tables.clear()
+        if self.internode is not None:
+            if self.heap.device.type == "cuda":
+                torch.cuda.synchronize(self.heap.device)
+            control.host_barrier()  # nobody is in the middle of a remote request any more
+            self.internode.close()
+            self.internode = None
         self.heap.close()
         SymmBufferRegistry._instance = None

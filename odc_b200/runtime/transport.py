@@ -9,9 +9,11 @@ touching the FSDP integration:
   system-scope release.
 * :class:`HostShmTransport` — CPU ranks over the ``/dev/shm`` heap; the functional model used
   by the CPU/gloo tests.
-* :class:`InterNodeTransport` — placeholder for a NIC transport (the reference's NVSHMEM
-  get/put kernels, odc/primitives/gather.py:22-64 and scatter_accumulate.py:42-174); it only
-  states the interface and refuses to run.
+* :class:`InterNodeTransport` — ranks of other nodes (the reference's NVSHMEM get/put kernels,
+  odc/primitives/gather.py:22-64 and scatter_accumulate.py:42-174): one-sided get / add by heap
+  offset, served by a small TCP server on every rank and staged through host memory.
+* :class:`HybridTransport` — splits a group into same-node and other-node members and uses the two
+  above; what the services get when the job spans more than one node.
 """
 from __future__ import annotations
 
@@ -121,24 +123,78 @@ class NvlinkP2PTransport(Transport):
 
 
 class InterNodeTransport(Transport):
-    """Interface placeholder for peers that are not on this node's NVLink domain."""
+    """Ranks of other nodes: one-sided get / add by heap offset through :mod:`odc_b200.runtime.internode`.
 
-    def _no(self):
-        raise NotImplementedError(
-            "inter-node transport is not built: this build moves data only between GPUs of one "
-            "NVLink/NVSwitch domain")
+    Takes the place of the reference's NVSHMEM get/put kernels (odc/primitives/gather.py:22-64,
+    odc/primitives/scatter_accumulate.py:42-174).  Bytes are staged through host memory (pinned on GPU
+    jobs) and travel over TCP; the owner's trainer takes no part.
+    """
 
-    def gather(self, *a, **k):
-        self._no()
+    def __init__(self, registry: SymmBufferRegistry):
+        if registry.internode is None:
+            raise RuntimeError("the inter-node endpoint was not started (single-node job?)")
+        self.registry = registry
+        self.endpoint = registry.internode
+        self.launches = 0
 
-    def scatter_add(self, *a, **k):
-        self._no()
+    def gather(self, out2d, src_local, ranks, my_index):
+        off = self.registry.offset_of(src_local)
+        got = self.endpoint.get_many(ranks, off, src_local.numel(), src_local.dtype)
+        for i, t in enumerate(got):
+            out2d[i].copy_(t.view(-1), non_blocking=True)  # converts dtype when the output's differs
+        if out2d.is_cuda:
+            torch.cuda.current_stream().synchronize()  # the pinned buffers are released on return
 
-    def wait_arrivals(self, *a, **k):
-        self._no()
+    def scatter_add(self, inp2d, acc_local, counter_local, ranks, my_index, scale=1.0):
+        rows = inp2d.detach().to("cpu") if inp2d.is_cuda else inp2d.detach()  # waits for the producing stream
+        self.endpoint.add_many(ranks, [rows[i] for i in range(len(ranks))], self.registry.offset_of(acc_local),
+                               acc_local.dtype, self.registry.offset_of(counter_local), scale)
+
+    def wait_arrivals(self, counter_local, expected):
+        raise RuntimeError("arrivals are counted on the local counter: wait through the same-node transport")
+
+
+class HybridTransport(Transport):
+    """Same-node ranks over the mapped heap, other nodes through :class:`InterNodeTransport`."""
+
+    def __init__(self, registry: SymmBufferRegistry, intra: Transport, inter: Transport):
+        self.registry, self.intra, self.inter = registry, intra, inter
+        self.heap = registry.heap
+
+    @property
+    def launches(self) -> int:
+        return getattr(self.intra, "launches", 0)
+
+    def _runs(self, ranks):
+        """Maximal runs ``(start, stop, local?)`` of consecutive group indices on / off this node."""
+        runs, a = [], 0
+        for i in range(1, len(ranks) + 1):
+            if i == len(ranks) or self.heap.is_local(ranks[i]) != self.heap.is_local(ranks[a]):
+                runs.append((a, i, self.heap.is_local(ranks[a])))
+                a = i
+        return runs
+
+    def gather(self, out2d, src_local, ranks, my_index):
+        for a, b, local in self._runs(ranks):
+            idx = my_index - a if a <= my_index < b else 0
+            (self.intra if local else self.inter).gather(out2d[a:b], src_local, ranks[a:b], idx)
+
+    def scatter_add(self, inp2d, acc_local, counter_local, ranks, my_index, scale=1.0):
+        for a, b, local in self._runs(ranks):
+            idx = my_index - a if a <= my_index < b else 0
+            (self.intra if local else self.inter).scatter_add(inp2d[a:b], acc_local, counter_local, ranks[a:b], idx,
+                                                              scale)
+
+    def wait_arrivals(self, counter_local, expected):
+        self.intra.wait_arrivals(counter_local, expected)
+
+    def check(self) -> None:
+        if hasattr(self.intra, "check"):
+            self.intra.check()
 
 
 def make_transport(registry: SymmBufferRegistry) -> Transport:
-    if registry.heap.device.type == "cuda":
-        return NvlinkP2PTransport(registry)
-    return HostShmTransport(registry)
+    intra = NvlinkP2PTransport(registry) if registry.heap.device.type == "cuda" else HostShmTransport(registry)
+    if registry.internode is not None:
+        return HybridTransport(registry, intra, InterNodeTransport(registry))
+    return intra
