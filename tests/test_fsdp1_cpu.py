@@ -64,3 +64,12 @@ def test_fsdp1_matches_stock(uneven):
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
+
+
+def test_fsdp1_two_emulated_nodes():
+    # one rank per "node": flat-parameter gathers and gradient contributions to the peer use the inter-node path
+    a = run_ranks(_train, 2, "stock", True)
+    b = run_ranks(_train, 2, "odc", True, env={"LOCAL_WORLD_SIZE": "1"})
+    assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)

@@ -84,8 +84,13 @@ def test_clock_sampler_parses_nvidia_smi_output(tmp_path, monkeypatch):
     assert out["reasons"] == ["sw_power_cap"]
 
 
-def test_inter_node_transport_refuses_to_run():
+def test_inter_node_transport_needs_a_multi_node_job():
+    import odc_b200 as odc
     from odc_b200.runtime import InterNodeTransport
-    t = InterNodeTransport()
-    with pytest.raises(NotImplementedError):
-        t.gather(None, None, [0], 0)
+    reg = odc.init_nvshmem("cpu", 1 << 20)  # single process: one node, no endpoint is started
+    try:
+        assert reg.internode is None
+        with pytest.raises(RuntimeError):
+            InterNodeTransport(reg)
+    finally:
+        odc.finalize_distributed()
