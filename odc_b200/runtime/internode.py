@@ -123,6 +123,7 @@ class InterNodeEndpoint:
             self._ext = _ext.load()
             self._stream = torch.cuda.Stream(device=heap.device)
             self._status = torch.zeros(4, dtype=torch.int32, device=heap.device)
+            self._status_hosts: Dict[int, torch.Tensor] = {}
         self._acceptor = threading.Thread(target=self._accept_loop, name="odc-internode-accept", daemon=True)
         self._acceptor.start()
         control.host_barrier()  # every listener is up before anyone connects
@@ -218,20 +219,33 @@ class InterNodeEndpoint:
                 # the accumulator, then a release-ordered arrival on the counter
                 self._ext.scatter_accumulate(dev.view(1, numel), self._table(offset), self._table(ctr_off), numel,
                                              dst_dt, 0, float(scale), config.debug_bounds(), self._status)
+                # the status word is read on this stream too: a copy on the default stream would queue behind
+                # whatever the trainer has running there
+                host_status = self._status_host(threading.get_ident())
+                host_status.copy_(self._status, non_blocking=True)
             self._stream.synchronize()
-            code = int(self._status[0])
+            code = int(host_status[0])
             if code != 0:
-                self._status.zero_()
+                with torch.cuda.stream(self._stream):
+                    self._status.zero_()
+                self._stream.synchronize()
                 raise RuntimeError(f"accumulation kernel reported error {code}")
         else:
             with self.heap.owner_lock(self.rank):
                 acc.add_(payload.to(dst_dt), alpha=scale) if scale != 1.0 else acc.add_(payload.to(dst_dt))
                 ctr[0] += 1
 
+    def _status_host(self, tid: int) -> torch.Tensor:
+        t = self._status_hosts.get(tid)
+        if t is None:
+            t = self._status_hosts[tid] = torch.zeros(4, dtype=torch.int32).pin_memory()
+        return t
+
     def _table(self, offset: int) -> torch.Tensor:
         t = self._tables.get(offset)
         if t is None:
-            t = torch.tensor([self.heap.peer_ptr(self.rank, offset)], dtype=torch.int64, device=self.heap.device)
+            t = torch.tensor([self.heap.peer_ptr(self.rank, offset)], dtype=torch.int64).pin_memory().to(
+                self.heap.device, non_blocking=True)  # issued on the caller's (server) stream
             self._tables[offset] = t
         return t
 

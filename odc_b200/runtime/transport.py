@@ -160,6 +160,8 @@ class HybridTransport(Transport):
     def __init__(self, registry: SymmBufferRegistry, intra: Transport, inter: Transport):
         self.registry, self.intra, self.inter = registry, intra, inter
         self.heap = registry.heap
+        self._poll_stream = None
+        self._poll_host = None
 
     @property
     def launches(self) -> int:
@@ -186,7 +188,28 @@ class HybridTransport(Transport):
                                                               scale)
 
     def wait_arrivals(self, counter_local, expected):
-        self.intra.wait_arrivals(counter_local, expected)
+        if not counter_local.is_cuda:
+            self.intra.wait_arrivals(counter_local, expected)
+            return
+        # Contributions from other nodes are added by kernels that this process's own server threads launch.
+        # A spinning wait kernel and those kernels would be launches of one GPU that depend on each other, which
+        # nothing guarantees to run side by side, so the counter is polled from the host until it is reached.
+        if self._poll_stream is None:
+            self._poll_stream = torch.cuda.Stream(device=counter_local.device)
+            self._poll_host = torch.zeros(1, dtype=torch.int64).pin_memory()
+        deadline = time.monotonic() + config.wait_timeout_ms() / 1e3
+        while True:
+            with torch.cuda.stream(self._poll_stream):
+                self._poll_host.copy_(counter_local[:1], non_blocking=True)
+            self._poll_stream.synchronize()
+            seen = int(self._poll_host[0])
+            if seen >= expected:
+                break
+            if time.monotonic() > deadline:
+                raise OdcTimeoutError(f"rank {self.heap.rank}: {seen} of {expected} gradient contributions arrived "
+                                      f"within {config.wait_timeout_ms()} ms")
+            time.sleep(0.0002)
+        self.check()
 
     def check(self) -> None:
         if hasattr(self.intra, "check"):

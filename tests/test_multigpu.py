@@ -93,6 +93,15 @@ def test_primitives_over_nvlink(mode):
     _launch(PRIMS, min(_ngpu(), 4), env={"ODC_HEAP_MODE": mode, "ODC_IPC_SLAB_SIZE": "2G"})
 
 
+def test_primitives_across_emulated_nodes():
+    """One GPU per "node": the peer's heap is not mapped; gathers and contributions go through the host-staged path."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    body = PRIMS.replace("red.stop()", "print('INTERNODE', reg.internode is not None, reg.internode.served)\nred.stop()")
+    outs = _launch(body, 2, env={"LOCAL_WORLD_SIZE": "1"})
+    assert all("INTERNODE True" in o for o in outs)
+
+
 FSDP = """
 from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 from odc_b200.fsdp import fsdp2
