@@ -11,7 +11,6 @@ Device-timed with CUDA events, max over ranks, median of the timed iterations.
 """
 import json
 import os
-import sys
 
 import torch
 import torch.distributed as dist

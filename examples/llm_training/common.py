@@ -6,11 +6,9 @@ import time
 
 import numpy as np
 import torch
-import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 from odc_b200.data import BatchedDataset, LengthSpec, get_cost_fn, sample_lengths  # noqa: E402
-from odc_b200.models import get_config  # noqa: E402
 
 
 class Timer:
