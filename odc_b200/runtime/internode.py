@@ -8,7 +8,10 @@ small server that every rank runs next to its trainer:
 * ``ADD  offset, numel, src dtype, dst dtype, scale, counter offset`` + payload  ->  the server adds
   ``scale * payload`` into its region (atomically with respect to same-node producers: the GPU path
   uses the same ``red.add`` kernel as NVLink peers, the CPU path takes the owner's file lock) and
-  then counts one arrival on the counter, exactly what a same-node producer does.
+  then counts one arrival on the counter, exactly what a same-node producer does.  A contribution
+  larger than the staging cap travels as several ``ADD`` messages on one connection; all but the
+  last carry counter offset -1 and count nothing, and the server handles a connection's messages
+  in order, so the arrival still means "the whole contribution has been added".
 
 The trainer of the serving rank never takes part (the server threads do), so the on-demand
 property holds across nodes: a rank can pull parameters from, and push gradients to, a rank that is
@@ -124,6 +127,11 @@ class InterNodeEndpoint:
             self._stream = torch.cuda.Stream(device=heap.device)
             self._status = torch.zeros(4, dtype=torch.int32, device=heap.device)
             self._status_hosts: Dict[int, torch.Tensor] = {}
+            # arrivals of all but the last piece of a split contribution are counted here and ignored
+            self._scratch_counter = torch.zeros(8, dtype=torch.int64, device=heap.device)
+            self._scratch_counter_table = torch.tensor([self._scratch_counter.data_ptr()], dtype=torch.int64,
+                                                       device=heap.device)
+            torch.cuda.current_stream().synchronize()
         self._acceptor = threading.Thread(target=self._accept_loop, name="odc-internode-accept", daemon=True)
         self._acceptor.start()
         control.host_barrier()  # every listener is up before anyone connects
@@ -210,14 +218,15 @@ class InterNodeEndpoint:
     def _add_region(self, offset: int, numel: int, src_dt: torch.dtype, dst_dt: torch.dtype, scale: float,
                     ctr_off: int, staging: torch.Tensor) -> None:
         acc = self.heap.local(offset, numel, dst_dt)
-        ctr = self.heap.local(ctr_off, 1, torch.int64)
+        ctr = self.heap.local(ctr_off, 1, torch.int64) if ctr_off >= 0 else None
         payload = staging[: numel * _itemsize(src_dt)].view(src_dt)
         if self.cuda:
             with torch.cuda.stream(self._stream):
                 dev = payload.to(self.heap.device, non_blocking=True)
                 # same kernel as a same-node producer, with this rank as the only owner: vector red.add into
                 # the accumulator, then a release-ordered arrival on the counter
-                self._ext.scatter_accumulate(dev.view(1, numel), self._table(offset), self._table(ctr_off), numel,
+                ctr_table = self._table(ctr_off) if ctr_off >= 0 else self._scratch_counter_table
+                self._ext.scatter_accumulate(dev.view(1, numel), self._table(offset), ctr_table, numel,
                                              dst_dt, 0, float(scale), config.debug_bounds(), self._status)
                 # the status word is read on this stream too: a copy on the default stream would queue behind
                 # whatever the trainer has running there
@@ -233,7 +242,8 @@ class InterNodeEndpoint:
         else:
             with self.heap.owner_lock(self.rank):
                 acc.add_(payload.to(dst_dt), alpha=scale) if scale != 1.0 else acc.add_(payload.to(dst_dt))
-                ctr[0] += 1
+                if ctr is not None:
+                    ctr[0] += 1
 
     def _status_host(self, tid: int) -> torch.Tensor:
         t = self._status_hosts.get(tid)
@@ -305,7 +315,10 @@ class InterNodeEndpoint:
 
     def add_many(self, ranks: Sequence[int], rows: Sequence[torch.Tensor], offset: int, dst_dt: torch.dtype,
                  ctr_offset: int, scale: float) -> None:
-        """``region[offset:] of ranks[i] += scale * rows[i]`` (host tensors), then one arrival on each counter."""
+        """``region[offset:] of ranks[i] += scale * rows[i]`` (host tensors), then one arrival on each counter.
+
+        ``ctr_offset = -1``: no arrival is counted (a piece of a contribution that is not its last).
+        """
         ranks = list(ranks)
         order = sorted(range(len(ranks)), key=lambda i: ranks[i])
         for i in order:
@@ -336,7 +349,9 @@ class InterNodeEndpoint:
                 c.close()
 
     def close(self) -> None:
-        """Call after a barrier: no request may be in flight."""
+        """Call after a barrier: no request may be in flight.  Safe to call twice."""
+        if self._closing:
+            return
         self._closing = True
         for r, c in list(self._conns.items()):
             try:

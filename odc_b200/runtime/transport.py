@@ -137,18 +137,33 @@ class InterNodeTransport(Transport):
         self.endpoint = registry.internode
         self.launches = 0
 
+    def _pieces(self, numel: int, n_peers: int):
+        """``(start, length)`` pieces so that one round of requests stages at most ``ODC_MAX_BUFFER_SIZE`` elements."""
+        cap = config.max_buffer_elems()
+        step = numel if cap <= 0 else max(64, cap // max(1, n_peers) // 64 * 64)
+        return [(s0, min(step, numel - s0)) for s0 in range(0, numel, step)] or [(0, 0)]
+
     def gather(self, out2d, src_local, ranks, my_index):
         off = self.registry.offset_of(src_local)
-        got = self.endpoint.get_many(ranks, off, src_local.numel(), src_local.dtype)
-        for i, t in enumerate(got):
-            out2d[i].copy_(t.view(-1), non_blocking=True)  # converts dtype when the output's differs
-        if out2d.is_cuda:
-            torch.cuda.current_stream().synchronize()  # the pinned buffers are released on return
+        esz = src_local.element_size()
+        for start, length in self._pieces(src_local.numel(), len(ranks)):
+            got = self.endpoint.get_many(ranks, off + start * esz, length, src_local.dtype)
+            for i, t in enumerate(got):
+                out2d[i, start:start + length].copy_(t.view(-1), non_blocking=True)  # converts dtype if they differ
+            if out2d.is_cuda:
+                torch.cuda.current_stream().synchronize()  # the pinned buffers are released on return
 
     def scatter_add(self, inp2d, acc_local, counter_local, ranks, my_index, scale=1.0):
-        rows = inp2d.detach().to("cpu") if inp2d.is_cuda else inp2d.detach()  # waits for the producing stream
-        self.endpoint.add_many(ranks, [rows[i] for i in range(len(ranks))], self.registry.offset_of(acc_local),
-                               acc_local.dtype, self.registry.offset_of(counter_local), scale)
+        acc_off = self.registry.offset_of(acc_local)
+        ctr_off = self.registry.offset_of(counter_local)
+        esz = acc_local.element_size()
+        pieces = self._pieces(inp2d.shape[1], len(ranks))
+        for k, (start, length) in enumerate(pieces):
+            part = inp2d[:, start:start + length].detach()
+            rows = part.to("cpu") if part.is_cuda else part  # waits for the producing stream
+            last = k == len(pieces) - 1
+            self.endpoint.add_many(ranks, [rows[i] for i in range(len(ranks))], acc_off + start * esz,
+                                   acc_local.dtype, ctr_off if last else -1, scale)
 
     def wait_arrivals(self, counter_local, expected):
         raise RuntimeError("arrivals are counted on the local counter: wait through the same-node transport")

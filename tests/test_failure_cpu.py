@@ -128,3 +128,47 @@ def test_arrival_protocol_model():
     assert all(_simulate(4, 5, signal_first=False, seed=s) for s in range(200))
     # negative control: signalling before the data is out is caught by some interleaving
     assert not all(_simulate(4, 5, signal_first=True, seed=s) for s in range(200))
+
+
+def _far_peer_gone(rank, world):
+    """Inter-node path: an owner whose server is gone, or that never answers, gives an error within the wait budget."""
+    import socket
+    import time
+
+    import odc_b200 as odc
+    from odc_b200.runtime import control
+    from odc_b200.runtime.status import OdcTimeoutError
+
+    reg = odc.init_nvshmem("cpu", 1 << 20)
+    ep = reg.internode
+    out = {}
+    if rank == 1:
+        ep.close()           # this rank "left" between steps: nobody listens on its port any more
+    control.host_barrier()
+    if rank == 0:
+        t0 = time.monotonic()
+        try:
+            ep.get_many([1], 0, 4, torch.int32)
+            out["refused"] = False
+        except OSError:
+            out["refused"] = True
+        # an owner that accepts the connection but never speaks: the challenge does not arrive in time
+        silent = socket.socket()
+        silent.bind(("127.0.0.1", 0))
+        silent.listen(1)
+        ep.addresses[1] = silent.getsockname()
+        try:
+            ep.get_many([1], 0, 4, torch.int32)
+            out["timed_out"] = False
+        except OdcTimeoutError:
+            out["timed_out"] = True
+        silent.close()
+        out["seconds"] = time.monotonic() - t0
+    control.host_barrier()
+    odc.finalize_distributed()
+    return out
+
+
+def test_inter_node_owner_that_left_or_stalls_is_reported():
+    res = run_ranks(_far_peer_gone, 2, env={"LOCAL_WORLD_SIZE": "1", "ODC_WAIT_TIMEOUT_MS": "500"})
+    assert res[0]["refused"] and res[0]["timed_out"] and res[0]["seconds"] < 10

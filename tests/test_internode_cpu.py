@@ -63,6 +63,15 @@ def test_gather_and_scatter_accumulate_across_emulated_nodes():
     assert sum(s["add"] for s, _ in res) == sum(2 * (r + 1) for r in range(world))
 
 
+def test_staging_cap_splits_transfers_but_counts_one_arrival_per_contribution():
+    world, lws, n = 4, 2, 3000
+    # 2048 elements per round over two far peers -> pieces of 1024 elements: 3 pieces per shard
+    res = run_ranks(_prim, world, n, env={"LOCAL_WORLD_SIZE": str(lws), "ODC_MAX_BUFFER_SIZE": "2048"})
+    for rank, (served, sent) in enumerate(res):
+        assert sent["get"] == 3 * (2 + 2)
+        assert sent["add"] == 3 * 2 * (rank + 1)
+
+
 def _bad_request(rank, world):
     import socket
 
