@@ -281,7 +281,16 @@ def _odc_foreach_reduce(fsdp_params, unsharded_grads, reduce_scatter_group, redu
     for i, (p, g) in enumerate(zip(fsdp_params, unsharded_grads)):
         if (dim := p.fsdp_placement.dim) != 0:
             unsharded_grads[i] = torch.cat(torch.chunk(g, world, dim=dim), dim=0)
-    rs_input = reduce_scatter_comm.allocate((info.acc_numel * world,), dtype=reduce_dtype, device=device)
+    # Stock FSDP2 widens the gradients to the reduce dtype while flattening them.  The accumulators already have
+    # the reduce dtype and the transport widens each element as it adds it, which gives the same sums, so the
+    # flattened staging copy keeps the (narrower) gradient dtype: half the bytes written here and read again by
+    # the scatter kernel.
+    grad_dtype = unsharded_grads[0].dtype
+    acc_dtype = _S.reduction.get_accumulation(info.acc_key).dtype
+    stage_dtype = reduce_dtype
+    if acc_dtype == reduce_dtype == torch.float32 and grad_dtype == torch.bfloat16:
+        stage_dtype = grad_dtype
+    rs_input = reduce_scatter_comm.allocate((info.acc_numel * world,), dtype=stage_dtype, device=device)
     rs2d = rs_input.view(world, info.acc_numel)
     all_present = len(fsdp_params) == len(info.trainable)
     if all_present:
