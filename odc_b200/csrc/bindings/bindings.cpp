@@ -117,6 +117,37 @@ void scatter_accumulate(Tensor inp2d, Tensor acc_table, Tensor ctr_table, int64_
         "scatter_accumulate launch");
 }
 
+bool scatter_accumulate_segments(std::vector<Tensor> grads, std::vector<int64_t> chunk_numels,
+                                 std::vector<int64_t> dst_offsets, Tensor acc_table, Tensor ctr_table,
+                                 at::ScalarType acc_dtype, int my_index, double scale) {
+  // Returns false (nothing launched) when the list does not fit this path; the caller then flattens the gradients.
+  if (grads.empty() || grads.size() > static_cast<size_t>(odc::kMaxScatterSegments) || acc_dtype != at::kFloat) return false;
+  TORCH_CHECK(grads.size() == chunk_numels.size() && grads.size() == dst_offsets.size(),
+              "scatter_accumulate_segments: one chunk size and one offset per gradient");
+  const auto dt = grads[0].scalar_type();
+  if (dt != at::kFloat && dt != at::kBFloat16) return false;
+  odc::ScatterSegments segs{};
+  segs.count = static_cast<int>(grads.size());
+  for (size_t i = 0; i < grads.size(); ++i) {
+    const Tensor& g = grads[i];
+    if (!g.is_cuda() || !g.is_contiguous() || g.scalar_type() != dt || g.device() != grads[0].device()) return false;
+    segs.src[i] = g.data_ptr();
+    segs.chunk[i] = chunk_numels[i];
+    segs.total[i] = g.numel();
+    segs.dst[i] = dst_offsets[i];
+  }
+  c10::cuda::CUDAGuard guard(grads[0].device());
+  odc::bind_device(grads[0].get_device());
+  const int nranks = static_cast<int>(acc_table.numel());
+  check(odc::launch_scatter_accumulate_segments(segs, kind_of(dt),
+                                                reinterpret_cast<const long long*>(acc_table.data_ptr<int64_t>()),
+                                                reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()), nranks,
+                                                my_index, static_cast<float>(scale),
+                                                next_done_slot(grads[0].get_device()), sm_count(), cur_stream()),
+        "scatter_accumulate_segments launch");
+  return true;
+}
+
 void wait_counter(Tensor counter, int64_t expected, int64_t timeout_ms, Tensor status) {
   c10::cuda::CUDAGuard g(counter.device());
   odc::bind_device(counter.get_device());
@@ -490,6 +521,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("reconstruct_tensor", &reconstruct_tensor);
   m.def("gather", &gather);
   m.def("scatter_accumulate", &scatter_accumulate);
+  m.def("scatter_accumulate_segments", &scatter_accumulate_segments);
   m.def("wait_counter", &wait_counter);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);

@@ -17,6 +17,21 @@ cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long l
                                       const long long* ctrs, size_t n, int nranks, int start, float scale,
                                       unsigned int* done_slot, int sm_count, cudaStream_t stream,
                                       int* status_for_bulk = nullptr);
+// scatter_accumulate taken straight from up to kMaxScatterSegments contiguous gradient tensors (fp32 accumulators
+// only).  The caller fills count/src/chunk/total/dst; the launcher derives tile_prefix and vec.
+constexpr int kMaxScatterSegments = 32;
+struct ScatterSegments {
+  int count;
+  const void* src[kMaxScatterSegments];       // contiguous gradient tensor
+  long long chunk[kMaxScatterSegments];       // elements per owner (dim-0 chunk of the padded tensor)
+  long long total[kMaxScatterSegments];       // elements that exist (owners past the end get fewer or none)
+  long long dst[kMaxScatterSegments];         // element offset inside every owner's accumulator
+  long long tile_prefix[kMaxScatterSegments + 1];
+  int vec[kMaxScatterSegments];
+};
+cudaError_t launch_scatter_accumulate_segments(ScatterSegments segs, int in_kind, const long long* accs,
+                                               const long long* ctrs, int nranks, int start, float scale,
+                                               unsigned int* done_slot, int sm_count, cudaStream_t stream);
 cudaError_t launch_wait_counter(const void* ctr, unsigned long long expected, unsigned long long budget_ns,
                                 int* status, cudaStream_t stream);
 

@@ -191,6 +191,62 @@ scatter_acc_f32_kernel(const InT* __restrict__ inp, const long long* __restrict_
   finish_and_signal(ctrs, nranks, done_slot);
 }
 
+// ---------------------------------------------------------------- scatter-accumulate, segmented
+// The same reduction taken straight from a list of gradient tensors, with no flattened [owners, shard] staging
+// copy in between.  Segment s is a contiguous tensor of `total` elements whose dim-0 chunk for owner r is
+// [r * chunk, min((r + 1) * chunk, total)) (later owners may get fewer or no elements: padding); it is added at
+// element `dst` of every owner's accumulator.  A tile is 4 * kTileVecs elements of one (segment, owner) pair.
+template <typename InT>
+__global__ void __launch_bounds__(kThreads)
+scatter_acc_segments_kernel(const __grid_constant__ ScatterSegments segs, const long long* __restrict__ accs,
+                            const long long* __restrict__ ctrs, int nranks, int start, float scale,
+                            unsigned int* done_slot) {
+  constexpr long long kTileElems = static_cast<long long>(kTileVecs) * 4;
+  const long long tiles_per_owner = segs.tile_prefix[segs.count];
+  const long long total_tiles = tiles_per_owner * nranks;
+  for (long long t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const int owner = (static_cast<int>(t % nranks) + start) % nranks;
+    const long long q = t / nranks;
+    int si = 0;
+    while (si + 1 < segs.count && q >= segs.tile_prefix[si + 1]) ++si;
+    const long long chunk = segs.chunk[si];
+    const long long len = max(0ll, min(chunk, segs.total[si] - static_cast<long long>(owner) * chunk));
+    const long long e0 = (q - segs.tile_prefix[si]) * kTileElems;
+    if (e0 >= len) continue;
+    const InT* src = static_cast<const InT*>(segs.src[si]) + static_cast<long long>(owner) * chunk;
+    float* acc = reinterpret_cast<float*>(accs[owner]) + segs.dst[si];
+    if (segs.vec[si]) {
+      float4 r[kVecPerThread];
+#pragma unroll
+      for (int k = 0; k < kVecPerThread; ++k) {
+        const long long e = e0 + (threadIdx.x + static_cast<long long>(k) * kThreads) * 4;
+        if (e + 4 <= len) {
+          if constexpr (sizeof(InT) == 4) {
+            r[k] = *reinterpret_cast<const float4*>(src + e);
+          } else {
+            const uint2 u = *reinterpret_cast<const uint2*>(src + e);
+            r[k] = make_float4(bf16_lo(u.x), bf16_hi(u.x), bf16_lo(u.y), bf16_hi(u.y));
+          }
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kVecPerThread; ++k) {
+        const long long e = e0 + (threadIdx.x + static_cast<long long>(k) * kThreads) * 4;
+        if (e + 4 <= len) {
+          red_add_v4_f32(acc + e, r[k].x * scale, r[k].y * scale, r[k].z * scale, r[k].w * scale);
+        } else if (e < len) {  // ragged end of the last owner's chunk
+          for (long long j = e; j < len; ++j) red_add_f32(acc + j, float(src[j]) * scale);
+        }
+      }
+    } else {
+      // a chunk or destination that is not 16-byte aligned: one element per reduction
+      const long long e1 = min(len, e0 + kTileElems);
+      for (long long j = e0 + threadIdx.x; j < e1; j += kThreads) red_add_f32(acc + j, float(src[j]) * scale);
+    }
+  }
+  finish_and_signal(ctrs, nranks, done_slot);
+}
+
 // bf16 gradients into bf16 accumulators (accumulation_dtype left at the input dtype)
 __global__ void __launch_bounds__(kThreads)
 scatter_acc_bf16_kernel(const __nv_bfloat16* __restrict__ inp, const long long* __restrict__ accs,
@@ -359,6 +415,36 @@ cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long l
   } else if (acc_kind == kBF16 && in_kind == kBF16) {
     scatter_acc_bf16_kernel<<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(inp), accs, ctrs, n,
                                                           nranks, start, scale, done_slot);
+  } else {
+    return cudaErrorInvalidValue;
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scatter_accumulate_segments(ScatterSegments segs, int in_kind, const long long* accs,
+                                               const long long* ctrs, int nranks, int start, float scale,
+                                               unsigned int* done_slot, int sm_count, cudaStream_t stream) {
+  if (nranks == 0) return cudaSuccess;
+  if (segs.count < 0 || segs.count > kMaxScatterSegments) return cudaErrorInvalidValue;
+  constexpr long long kTileElems = static_cast<long long>(kTileVecs) * 4;
+  const int in_size = in_kind == kF32 ? 4 : 2;
+  long long tiles = 0;
+  for (int s = 0; s < segs.count; ++s) {
+    if (segs.chunk[s] < 0 || segs.total[s] < 0 || segs.dst[s] < 0) return cudaErrorInvalidValue;
+    segs.tile_prefix[s] = tiles;
+    tiles += (segs.chunk[s] + kTileElems - 1) / kTileElems;
+    // vector path: every owner's chunk starts on a 16-byte (fp32) / 8-byte (bf16) boundary of the source and on a
+    // 16-byte boundary of the accumulator
+    const bool src_ok = (reinterpret_cast<uintptr_t>(segs.src[s]) % (4 * in_size)) == 0 && (segs.chunk[s] % 4) == 0;
+    segs.vec[s] = (src_ok && (segs.dst[s] % 4) == 0) ? 1 : 0;
+  }
+  segs.tile_prefix[segs.count] = tiles;
+  const int grid = grid_for(static_cast<size_t>(tiles) * nranks + 1, sm_count);
+  if (in_kind == kF32) {
+    scatter_acc_segments_kernel<float><<<grid, kThreads, 0, stream>>>(segs, accs, ctrs, nranks, start, scale, done_slot);
+  } else if (in_kind == kBF16) {
+    scatter_acc_segments_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(segs, accs, ctrs, nranks, start, scale,
+                                                                            done_slot);
   } else {
     return cudaErrorInvalidValue;
   }

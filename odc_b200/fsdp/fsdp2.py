@@ -281,31 +281,49 @@ def _odc_foreach_reduce(fsdp_params, unsharded_grads, reduce_scatter_group, redu
     for i, (p, g) in enumerate(zip(fsdp_params, unsharded_grads)):
         if (dim := p.fsdp_placement.dim) != 0:
             unsharded_grads[i] = torch.cat(torch.chunk(g, world, dim=dim), dim=0)
-    # Stock FSDP2 widens the gradients to the reduce dtype while flattening them.  The accumulators already have
-    # the reduce dtype and the transport widens each element as it adds it, which gives the same sums, so the
-    # flattened staging copy keeps the (narrower) gradient dtype: half the bytes written here and read again by
-    # the scatter kernel.
     grad_dtype = unsharded_grads[0].dtype
     acc_dtype = _S.reduction.get_accumulation(info.acc_key).dtype
-    stage_dtype = reduce_dtype
-    if acc_dtype == reduce_dtype == torch.float32 and grad_dtype == torch.bfloat16:
-        stage_dtype = grad_dtype
-    rs_input = reduce_scatter_comm.allocate((info.acc_numel * world,), dtype=stage_dtype, device=device)
-    rs2d = rs_input.view(world, info.acc_numel)
-    all_present = len(fsdp_params) == len(info.trainable)
-    if all_present:
-        torch.ops.fsdp.chunk_cat(unsharded_grads, dim=0, num_chunks=world, out=rs2d)
-    else:  # some parameters received no gradient in this backward: their columns contribute zero
-        rs2d.zero_()
-        for p, g in zip(fsdp_params, unsharded_grads):
-            o = info.acc_offsets[id(p)]
-            n = _get_dim0_padded_size(g.size(), world).numel() // world
-            torch.ops.fsdp.chunk_cat([g], dim=0, num_chunks=world, out=rs2d[:, o:o + n])
-    unsharded_grads.clear()
+    # First choice: reduce straight from the per-parameter gradients.  A dim-0 chunk of a contiguous tensor is
+    # contiguous, so no rank-major staging copy is needed; the kernel widens each element as it adds it.
     reduce_scatter_stream.wait_stream(current)
-    with handle.stream(reduce_scatter_stream):
-        _S.reduction.scatter_accumulate(info.acc_key, rs_input, reduce_scatter_group)
-        event = reduce_scatter_stream.record_event()
+    done = False
+    if all(g.is_contiguous() for g in unsharded_grads):
+        chunks = [_get_dim0_padded_size(g.size(), world).numel() // world for g in unsharded_grads]
+        offsets = [info.acc_offsets[id(p)] for p in fsdp_params]
+        with handle.stream(reduce_scatter_stream):
+            done = _S.reduction.scatter_accumulate_segments(info.acc_key, unsharded_grads, chunks, offsets,
+                                                            reduce_scatter_group)
+            if done:
+                event = reduce_scatter_stream.record_event()
+        if done:
+            # FSDP keeps the returned tensor until it has waited for the event; it carries the gradients along so
+            # that their memory is not reused while the kernel may still read it
+            rs_input = torch.empty(0, dtype=grad_dtype, device=device)
+            rs_input._odc_keepalive = list(unsharded_grads)
+            unsharded_grads.clear()
+    if not done:
+        # Flattened path.  Stock FSDP2 widens the gradients to the reduce dtype while flattening them; the
+        # accumulators already have the reduce dtype and the transport widens while adding, which gives the same
+        # sums, so the staging copy keeps the (narrower) gradient dtype.
+        stage_dtype = reduce_dtype
+        if acc_dtype == reduce_dtype == torch.float32 and grad_dtype == torch.bfloat16:
+            stage_dtype = grad_dtype
+        rs_input = reduce_scatter_comm.allocate((info.acc_numel * world,), dtype=stage_dtype, device=device)
+        rs2d = rs_input.view(world, info.acc_numel)
+        all_present = len(fsdp_params) == len(info.trainable)
+        if all_present:
+            torch.ops.fsdp.chunk_cat(unsharded_grads, dim=0, num_chunks=world, out=rs2d)
+        else:  # some parameters received no gradient in this backward: their columns contribute zero
+            rs2d.zero_()
+            for p, g in zip(fsdp_params, unsharded_grads):
+                o = info.acc_offsets[id(p)]
+                n = _get_dim0_padded_size(g.size(), world).numel() // world
+                torch.ops.fsdp.chunk_cat([g], dim=0, num_chunks=world, out=rs2d[:, o:o + n])
+        unsharded_grads.clear()
+        reduce_scatter_stream.wait_stream(current)
+        with handle.stream(reduce_scatter_stream):
+            _S.reduction.scatter_accumulate(info.acc_key, rs_input, reduce_scatter_group)
+            event = reduce_scatter_stream.record_event()
     info.reduce_calls += 1
     info.divide = dict(factor=gradient_divide_factor, all_reduce_group=all_reduce_group,
                        all_reduce_hook=all_reduce_hook, orig_dtype=orig_dtype)

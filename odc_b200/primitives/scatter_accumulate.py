@@ -103,6 +103,25 @@ class ReductionService:
             self.transport.scatter_add(input.view(n, shard), target, self.counter, ranks, my_index, scale)
         self.note_dispatch(ranks)
 
+    def scatter_accumulate_segments(self, key: Hashable, grads, chunk_numels, dst_offsets,
+                                    pg: Optional[dist.ProcessGroup] = None, scale: float = 1.0) -> bool:
+        """One contribution to ``key`` taken straight from a list of contiguous tensors.
+
+        Tensor i is split along dim 0 into ``|pg|`` chunks of ``chunk_numels[i]`` elements (the last owners get
+        fewer or none when the tensor is shorter than ``|pg|`` chunks) and chunk r is added at element
+        ``dst_offsets[i]`` of rank r's accumulator.  The accumulator must be registered.  Returns False without
+        doing anything when the transport cannot do this in place; the caller then builds the rank-major
+        input and calls :meth:`scatter_accumulate`.
+        """
+        ranks = control.group_ranks(pg)
+        target = self.scatter_target(key)
+        with nvtx_range("odc::scatter_accumulate"):
+            done = self.transport.scatter_add_segments(grads, chunk_numels, dst_offsets, target, self.counter, ranks,
+                                                       ranks.index(control.rank()), scale)
+        if done:
+            self.note_dispatch(ranks)
+        return done
+
     def note_dispatch(self, ranks) -> None:
         """Record one contribution sent to each of ``ranks`` (also used by the fused weight-gradient GEMM)."""
         for r in ranks:

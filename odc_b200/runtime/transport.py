@@ -42,6 +42,17 @@ class Transport:
         """Return once the local arrival counter has reached ``expected`` (bounded)."""
         raise NotImplementedError
 
+    def scatter_add_segments(self, grads, chunk_numels, dst_offsets, acc_local: torch.Tensor,
+                             counter_local: torch.Tensor, ranks: Sequence[int], my_index: int,
+                             scale: float = 1.0) -> bool:
+        """``scatter_add`` taken straight from a list of contiguous tensors (no flattened staging copy).
+
+        Tensor i is split along dim 0 into chunks of ``chunk_numels[i]`` elements, chunk r is added at element
+        ``dst_offsets[i]`` of the accumulator on ``ranks[r]``; one arrival per owner.  Returns False, having done
+        nothing, when this transport has no such path: the caller then flattens and calls ``scatter_add``.
+        """
+        return False
+
 
 class HostShmTransport(Transport):
     def __init__(self, registry: SymmBufferRegistry):
@@ -70,6 +81,24 @@ class HostShmTransport(Transport):
                 else:
                     accs[r].view(-1).add_(src)
                 ctrs[r][0] += 1
+
+    def scatter_add_segments(self, grads, chunk_numels, dst_offsets, acc_local, counter_local, ranks, my_index,
+                             scale=1.0):
+        accs = self.registry.get_peer_tensors(acc_local)
+        ctrs = self.registry.get_peer_tensors(counter_local)
+        n = len(ranks)
+        for k in range(n):
+            i = (my_index + k) % n
+            r = ranks[i]
+            with self.heap.owner_lock(r):
+                acc = accs[r].view(-1)
+                for g, chunk, off in zip(grads, chunk_numels, dst_offsets):
+                    flat = g.reshape(-1)
+                    piece = flat[i * chunk:min((i + 1) * chunk, flat.numel())]  # short or empty past the end
+                    if piece.numel():
+                        acc[off:off + piece.numel()].add_(piece.to(acc.dtype), alpha=scale)
+                ctrs[r][0] += 1
+        return True
 
     def wait_arrivals(self, counter_local, expected):
         deadline = time.monotonic() + config.wait_timeout_ms() / 1e3
@@ -105,6 +134,17 @@ class NvlinkP2PTransport(Transport):
         self.ext.scatter_accumulate(inp2d, acc_table, ctr_table, acc_local.numel(), acc_local.dtype,
                                     my_index, float(scale), config.debug_bounds(), self.status)
         self.launches += 1
+
+    def scatter_add_segments(self, grads, chunk_numels, dst_offsets, acc_local, counter_local, ranks, my_index,
+                             scale=1.0):
+        acc_table = self.registry.peer_ptr_table(acc_local, ranks)
+        ctr_table = self.registry.peer_ptr_table(counter_local, ranks)
+        done = self.ext.scatter_accumulate_segments(list(grads), [int(c) for c in chunk_numels],
+                                                    [int(o) for o in dst_offsets], acc_table, ctr_table,
+                                                    acc_local.dtype, my_index, float(scale))
+        if done:
+            self.launches += 1
+        return bool(done)
 
     def wait_arrivals(self, counter_local, expected):
         self.ext.wait_counter(counter_local, int(expected), config.wait_timeout_ms(), self.status)
@@ -201,6 +241,13 @@ class HybridTransport(Transport):
             idx = my_index - a if a <= my_index < b else 0
             (self.intra if local else self.inter).scatter_add(inp2d[a:b], acc_local, counter_local, ranks[a:b], idx,
                                                               scale)
+
+    def scatter_add_segments(self, grads, chunk_numels, dst_offsets, acc_local, counter_local, ranks, my_index,
+                             scale=1.0):
+        if any(not self.heap.is_local(r) for r in ranks):
+            return False
+        return self.intra.scatter_add_segments(grads, chunk_numels, dst_offsets, acc_local, counter_local, ranks,
+                                               my_index, scale)
 
     def wait_arrivals(self, counter_local, expected):
         if not counter_local.is_cuda:

@@ -356,3 +356,35 @@ def test_scatter_accumulate_bulk_path_matches(ext):
     r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, ODC_SCATTER_BULK="1"), capture_output=True, text=True,
                        timeout=120)
     assert r.returncode == 0 and "BULK_OK" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_scatter_accumulate_segments_emulated_ranks(ext, world, dtype):
+    """Reduction straight from a list of gradient tensors: same result as flattening them rank-major first."""
+    torch.manual_seed(world)
+    shapes = [(1024, 512), (512,), (300, 96), (7, 5), (world * 3 + 1, 64), (2048, 2048)]
+    grads = [torch.randn(*s, device="cuda").to(dtype) for s in shapes]
+    chunks, offsets, o = [], [], 0
+    for g in grads:
+        rows = -(-g.shape[0] // world)
+        c = rows * (g.numel() // g.shape[0])
+        chunks.append(c)
+        offsets.append(o)
+        o += c
+    accs = [torch.zeros(o + 16, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    for _ in range(2):
+        assert ext.scatter_accumulate_segments(grads, chunks, offsets, _table(accs), _table(ctrs), torch.float32, 1 % world, 0.5)
+    torch.cuda.synchronize()
+    for r in range(world):
+        want = torch.zeros(o + 16, device="cuda")
+        for g, c, off in zip(grads, chunks, offsets):
+            piece = g.reshape(-1)[r * c:(r + 1) * c].float()
+            want[off:off + piece.numel()] += 2 * 0.5 * piece
+        torch.testing.assert_close(accs[r], want, rtol=1e-6, atol=1e-6)
+        assert int(ctrs[r][0]) == 2
+    # lists this path does not take are refused without a launch
+    assert not ext.scatter_accumulate_segments([grads[0]] * 33, [chunks[0]] * 33, [0] * 33, _table(accs), _table(ctrs),
+                                               torch.float32, 0, 1.0)
+    assert not ext.scatter_accumulate_segments(grads, chunks, offsets, _table(accs), _table(ctrs), torch.bfloat16, 0, 1.0)
