@@ -109,3 +109,36 @@ def test_deterministic_mode_is_bitwise_reproducible():
             slot += (torch.randn(3 * n, generator=g) * 1e3).view(3, n)[0]
         want += slot
     assert torch.equal(runs[0][0], want)
+
+
+def _segments(rank, world):
+    import odc_b200 as odc
+    from odc_b200.runtime import control
+    odc.init_nvshmem("cpu", 64 << 20)
+    red = odc.ReductionService(accumulation_dtype=torch.float32)
+    shapes = [(7, 5), (world * 4, 6), (3,), (world * 2 + 1, 2, 3)]  # ragged, even, shorter than the group, 3-D
+    chunks, offsets, o = [], [], 0
+    for s in shapes:
+        rows = -(-s[0] // world)
+        c = rows * int(torch.Size(s).numel() // s[0])
+        chunks.append(c); offsets.append(o); o += c
+    red.register("g", o, torch.bfloat16)
+    gen = torch.Generator().manual_seed(7)
+    all_grads = [[torch.randint(-8, 8, s, generator=gen).to(torch.bfloat16) for s in shapes] for _ in range(world)]
+    for _ in range(rank + 1):  # rank r contributes r + 1 times
+        assert red.scatter_accumulate_segments("g", all_grads[rank], chunks, offsets, scale=0.5)
+    red.sync()
+    want = torch.zeros(o)
+    for r in range(world):
+        for g, c, off in zip(all_grads[r], chunks, offsets):
+            piece = g.reshape(-1)[rank * c:(rank + 1) * c].float()
+            want[off:off + piece.numel()] += 0.5 * (r + 1) * piece
+    ok = torch.equal(red.get_accumulation("g"), want)
+    control.host_barrier()
+    red.stop()
+    odc.finalize_distributed()
+    return ok
+
+
+def test_scatter_accumulate_segments_matches_flattened_reduction():
+    assert all(run_ranks(_segments, 3))
