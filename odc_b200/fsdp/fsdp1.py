@@ -167,6 +167,21 @@ def _reduce_grad(state: _FSDPState, handle: FlatParamHandle) -> None:
     flat_param._saved_grad_shard = reduction.get_accumulation(handle._odc_key)
 
 
+def _low_precision_hook_enabled(state: _FSDPState) -> bool:
+    """Tell stock FSDP not to widen the unsharded gradient before ``_reduce_grad``.
+
+    Stock FSDP1 casts the whole unsharded gradient to the reduce dtype first (a full-size extra pass).  The
+    accumulators here already have the reduce dtype and the reduction widens each element as it adds it, which
+    gives the same sums, so for bf16 gradients reduced in fp32 that cast is skipped.
+    """
+    h = getattr(state, "_handle", None)
+    if (h is not None and hasattr(h, "_odc_key") and state._comm_hook is None
+            and getattr(h, "_fwd_bwd_param_dtype", None) == torch.bfloat16
+            and getattr(h, "_reduce_dtype", None) == torch.float32):
+        return True
+    return _S.originals["_low_precision_hook_enabled"](state)
+
+
 def _prepare_gradient_for_optim(self: FlatParamHandle):
     if not hasattr(self, "_odc_key"):
         return _S.originals["prepare_gradient_for_optim"](self)
@@ -245,6 +260,7 @@ def patch_fsdp1(reduce_dtype: Optional[torch.dtype] = None) -> None:
         "_free_low_precision_sharded_param": FlatParamHandle._free_low_precision_sharded_param,
         "prepare_gradient_for_optim": FlatParamHandle.prepare_gradient_for_optim,
         "_reduce_grad": _ru._reduce_grad,
+        "_low_precision_hook_enabled": _ru._low_precision_hook_enabled,
     }
     FlatParamHandle.shard = _shard
     FlatParamHandle._get_shard = staticmethod(_get_shard)
@@ -253,6 +269,7 @@ def patch_fsdp1(reduce_dtype: Optional[torch.dtype] = None) -> None:
     FlatParamHandle._free_low_precision_sharded_param = _free_low_precision_sharded_param
     FlatParamHandle.prepare_gradient_for_optim = _prepare_gradient_for_optim
     _ru._reduce_grad = _reduce_grad
+    _ru._low_precision_hook_enabled = _low_precision_hook_enabled
     _S.patched = True
 
 
@@ -267,6 +284,7 @@ def unpatch_fsdp1() -> None:
     FlatParamHandle._free_low_precision_sharded_param = o["_free_low_precision_sharded_param"]
     FlatParamHandle.prepare_gradient_for_optim = o["prepare_gradient_for_optim"]
     _ru._reduce_grad = o["_reduce_grad"]
+    _ru._low_precision_hook_enabled = o["_low_precision_hook_enabled"]
     _S.patched = False
     _S.reduction = _S.gather = None
     _S.next_index = 0

@@ -5,7 +5,7 @@ import torch
 from _mp import run_ranks
 
 
-def _train(rank, world, mode, uneven):
+def _train(rank, world, mode, uneven, mp=False):
     import functools
 
     import torch.distributed as dist
@@ -17,14 +17,24 @@ def _train(rank, world, mode, uneven):
     from odc_b200.fsdp import fsdp1
     from odc_b200.models import DecoderLayer, DecoderLM, get_config
 
+    seen_dtypes = set()
     if mode == "odc":
         fsdp1.patch_fsdp1(reduce_dtype=torch.float32)
         odc.init_nvshmem("cpu", 256 << 20)
+        stock_scatter = odc.ReductionService.scatter_accumulate
+
+        def recording_scatter(self, key, input, *a, **k):
+            seen_dtypes.add((input.dtype, self.get_accumulation(key).dtype))
+            return stock_scatter(self, key, input, *a, **k)
+
+        odc.ReductionService.scatter_accumulate = recording_scatter
     torch.manual_seed(0)
     model = DecoderLM(get_config("tiny"))
     model.reset_parameters(seed=0)
+    from torch.distributed.fsdp import MixedPrecision
+    policy = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32) if mp else None
     model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=torch.device("cpu"),
-                 use_orig_params=False)
+                 use_orig_params=False, mixed_precision=policy)
     opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
     if mode == "odc":
         fsdp1.pre_minibatch_start(model)
@@ -54,7 +64,7 @@ def _train(rank, world, mode, uneven):
         full = {k: v.detach().clone() for k, v in model.named_parameters()}
     if mode == "odc":
         fsdp1.stop()
-    return losses, full
+    return losses, full, seen_dtypes
 
 
 @pytest.mark.parametrize("uneven", [False, True])
@@ -73,3 +83,13 @@ def test_fsdp1_two_emulated_nodes():
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
+
+
+def test_fsdp1_mixed_precision_reduces_bf16_gradients_into_fp32_accumulators():
+    a = run_ranks(_train, 2, "stock", True, True)
+    b = run_ranks(_train, 2, "odc", True, True)
+    # the unsharded gradients reach the reduction in bf16 (stock's widening pass is skipped) and land in fp32
+    assert b[0][2] == {(torch.bfloat16, torch.float32)}
+    assert a[0][0] == pytest.approx(b[0][0], rel=2e-2), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        torch.testing.assert_close(a[0][1][k].float(), b[0][1][k].float(), rtol=2e-2, atol=3e-3)
