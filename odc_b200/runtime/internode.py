@@ -146,7 +146,7 @@ class InterNodeEndpoint:
             conn.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)
             t = threading.Thread(target=self._serve, args=(conn,), name="odc-internode-serve", daemon=True)
             t.start()
-            self._handlers.append(t)
+            self._handlers = [h for h in self._handlers if h.is_alive()] + [t]
 
     def _authenticate(self, conn: socket.socket) -> bool:
         nonce = os.urandom(16)
@@ -178,6 +178,9 @@ class InterNodeEndpoint:
                 magic, op, src_c, dst_c, offset, numel, ctr_off, scale = _HDR.unpack(hdr)
                 if magic != _MAGIC or op == OP_BYE:
                     return
+                if (numel < 0 or offset < 0 or src_c >= len(_DTYPES) or dst_c >= len(_DTYPES)
+                        or numel * 8 > getattr(self.heap, "nbytes", 1 << 62) * 8):
+                    return  # malformed header: the byte stream cannot be trusted any further
                 try:
                     if op == OP_GET:
                         dt = _DTYPES[src_c]
@@ -303,8 +306,8 @@ class InterNodeEndpoint:
                 self._conn(ranks[i]).sendall(_HDR.pack(_MAGIC, OP_GET, _CODE[dt], _CODE[dt], offset, numel, 0, 1.0))
             for i in order:
                 self._read_reply(ranks[i], memoryview(bufs[i].numpy())[:nb])
-        except (OSError, ConnectionError, OdcTimeoutError):
-            self._drop(ranks)
+        except (OSError, ConnectionError, OdcTimeoutError, RuntimeError):
+            self._drop(ranks)  # answers of the other owners may still be queued on their connections
             raise
         finally:
             for i in order:
@@ -333,8 +336,8 @@ class InterNodeEndpoint:
                 self.sent["bytes"] += row.numel() * row.element_size()
             for i in order:
                 self._read_reply(ranks[i])
-        except (OSError, ConnectionError, OdcTimeoutError):
-            self._drop(ranks)
+        except (OSError, ConnectionError, OdcTimeoutError, RuntimeError):
+            self._drop(ranks)  # answers of the other owners may still be queued on their connections
             raise
         finally:
             for i in order:

@@ -52,6 +52,7 @@ def _heartbeat(rank, world):
     hb.beat(0)
     dist.barrier()
     assert hb.dead_peers(max_age_s=30.0) == []
+    dist.barrier()  # everyone has looked before anyone leaves
     if rank == 1:
         hb.mark_leaving()  # leaves between steps, nothing in flight
         dist.barrier()
