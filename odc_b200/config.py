@@ -72,6 +72,14 @@ def deterministic() -> bool:
     return os.environ.get("ODC_DETERMINISTIC", "0") not in ("0", "", "false")
 
 
+def reduce_from_segments() -> bool:
+    """``ODC_REDUCE_SEGMENTS=0``: FSDP2 flattens the gradients rank-major before the reduction (for A/B runs).
+
+    By default the reduction reads the per-parameter gradient tensors directly.
+    """
+    return os.environ.get("ODC_REDUCE_SEGMENTS", "1") not in ("0", "false")
+
+
 def local_world_size(default: int) -> int:
     """GPUs per node: ``RAY_LOCAL_WORLD_SIZE`` overrides ``LOCAL_WORLD_SIZE`` (utils.py:195-199)."""
     for name in ("RAY_LOCAL_WORLD_SIZE", "LOCAL_WORLD_SIZE"):

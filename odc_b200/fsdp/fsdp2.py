@@ -40,6 +40,7 @@ from torch.distributed.fsdp._fully_shard._fsdp_common import (DDPMeshInfo, FSDPM
 from torch.distributed.fsdp._fully_shard._fsdp_param import FSDPParam, ShardedState
 from torch.distributed.fsdp._fully_shard._fsdp_param_group import FSDPParamGroup
 
+from .. import config
 from ..primitives import GatherService, ReductionService
 from ..runtime import control
 from ..runtime.registry import SymmBufferRegistry
@@ -287,7 +288,7 @@ def _odc_foreach_reduce(fsdp_params, unsharded_grads, reduce_scatter_group, redu
     # contiguous, so no rank-major staging copy is needed; the kernel widens each element as it adds it.
     reduce_scatter_stream.wait_stream(current)
     done = False
-    if all(g.is_contiguous() for g in unsharded_grads):
+    if config.reduce_from_segments() and all(g.is_contiguous() for g in unsharded_grads):
         chunks = [_get_dim0_padded_size(g.size(), world).numel() // world for g in unsharded_grads]
         offsets = [info.acc_offsets[id(p)] for p in fsdp_params]
         with handle.stream(reduce_scatter_stream):

@@ -180,3 +180,84 @@ def test_fsdp2_hsdp_hpz_checkpointing_fused_adamw():
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-3), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
+
+
+def _train_partial(rank, world, mode):
+    """Frozen parameters, a branch that some microbatches skip, and a unit that one rank does not run at all.
+
+    Lock-step FSDP needs every rank to produce the same set of gradients in every backward, so the stock run
+    executes the skipped parts with weight zero; the on-demand run really skips them.  The mathematics is the same.
+    """
+    import torch.distributed as dist
+    import torch.nn as nn
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+
+    skip_for_real = mode == "odc"
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(24, 24)
+            self.b = nn.Linear(24, 24)               # skipped by some microbatches: no gradient in that backward
+            self.c = nn.Linear(24, 24, bias=False)   # frozen
+            self.side = nn.Sequential(nn.Linear(24, 24), nn.Tanh())  # its own unit; rank 1 skips it in step 1
+            self.head = nn.Linear(24, 5)
+
+        def forward(self, x, use_b, use_side):
+            h = torch.tanh(self.a(x))
+            if use_b or not skip_for_real:
+                h = h + self.b(h) * (1.0 if use_b else 0.0)
+            h = self.c(h)
+            if use_side or not skip_for_real:
+                h = h + self.side(h) * (1.0 if use_side else 0.0)
+            return self.head(h)
+
+    torch.manual_seed(0)
+    model = Net()
+    model.c.weight.requires_grad_(False)
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 64 << 20)
+        fsdp2.patch_fsdp2()
+    fully_shard(model.side)
+    fully_shard(model)
+    if mode == "odc":
+        for m in (model.side, model):
+            fsdp2.patch_lazy_init(m)
+    opt = torch.optim.SGD([p for p in model.parameters() if p.requires_grad], lr=0.05)
+    losses = []
+    for step in range(3):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        total = torch.zeros(())
+        for i in range(3):
+            g = torch.Generator().manual_seed(1000 * step + 10 * i + rank)
+            x = torch.randn(6, 24, generator=g)
+            y = torch.randint(0, 5, (6,), generator=g)
+            use_b = (i + rank) % 2 == 0                 # differs between the ranks within one microbatch
+            use_side = not (step == 1 and rank == 1)
+            loss = nn.functional.cross_entropy(model(x, use_b, use_side), y)
+            loss.backward()
+            total += loss.detach()
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+        dist.all_reduce(total)
+        losses.append(float(total))
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    if mode == "odc":
+        fsdp2.stop()
+    return losses, full
+
+
+@pytest.mark.parametrize("segments", ["1", "0"])
+def test_fsdp2_frozen_parameters_and_skipped_branches(segments):
+    a = run_ranks(_train_partial, 2, "stock")
+    b = run_ranks(_train_partial, 2, "odc", env={"ODC_REDUCE_SEGMENTS": segments})
+    assert a[0][0] == pytest.approx(b[0][0], rel=1e-5), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(a[0][1]["c.weight"], b[0][1]["c.weight"], rtol=0, atol=0)  # frozen stays frozen
