@@ -261,3 +261,53 @@ def test_fsdp2_frozen_parameters_and_skipped_branches(segments):
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=1e-5, atol=1e-6)
     torch.testing.assert_close(a[0][1]["c.weight"], b[0][1]["c.weight"], rtol=0, atol=0)  # frozen stays frozen
+
+
+def _train_zero(rank, world, mode):
+    """Rank 1 runs no microbatch at all in minibatches 0 and 2 (the first one included)."""
+    import torch.distributed as dist
+    import torch.nn as nn
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(20, 32), nn.Tanh(), nn.Linear(32, 32), nn.Tanh(), nn.Linear(32, 3))
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 64 << 20)
+        fsdp2.patch_fsdp2()
+    fully_shard(model[2])
+    fully_shard(model)
+    if mode == "odc":
+        for m in (model[2], model):
+            fsdp2.patch_lazy_init(m)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    for step in range(3):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        idle = rank == 1 and step in (0, 2)
+        for i in range(2):
+            if idle and mode == "odc":
+                continue  # nothing to do: no forward, no backward, no collective
+            g = torch.Generator().manual_seed(100 * step + 10 * i + rank)
+            x = torch.randn(5, 20, generator=g)
+            y = torch.randint(0, 3, (5,), generator=g)
+            loss = nn.functional.cross_entropy(model(x), y)
+            (loss * (0.0 if idle else 1.0)).backward()  # lock-step FSDP has to go through the motions
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    if mode == "odc":
+        fsdp2.stop()
+    return full
+
+
+def test_fsdp2_rank_with_zero_microbatches():
+    a = run_ranks(_train_zero, 2, "stock")
+    b = run_ranks(_train_zero, 2, "odc")
+    for k in a[0]:
+        torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
+        torch.testing.assert_close(b[0][k], b[1][k], rtol=0, atol=0)
