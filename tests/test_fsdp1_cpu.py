@@ -93,3 +93,50 @@ def test_fsdp1_mixed_precision_reduces_bf16_gradients_into_fp32_accumulators():
     assert a[0][0] == pytest.approx(b[0][0], rel=2e-2), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k].float(), b[0][1][k].float(), rtol=2e-2, atol=3e-3)
+
+
+def _train_zero(rank, world, mode):
+    """Rank 1 runs no microbatch in minibatch 1 (FSDP1)."""
+    import torch.nn as nn
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp1
+
+    if mode == "odc":
+        fsdp1.patch_fsdp1(reduce_dtype=None)
+        odc.init_nvshmem("cpu", 64 << 20)
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Linear(20, 32), nn.Tanh(), nn.Linear(32, 3))
+    model = FSDP(net, device_id=torch.device("cpu"), use_orig_params=False)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    if mode == "odc":
+        fsdp1.pre_minibatch_start(model)
+    for step in range(3):
+        idle = rank == 1 and step == 1
+        for i in range(2):
+            if idle and mode == "odc":
+                continue
+            g = torch.Generator().manual_seed(100 * step + 10 * i + rank)
+            x = torch.randn(5, 20, generator=g)
+            y = torch.randint(0, 3, (5,), generator=g)
+            loss = nn.functional.cross_entropy(model(x), y)
+            (loss * (0.0 if idle else 1.0)).backward()
+        if mode == "odc":
+            fsdp1.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+        if mode == "odc":
+            fsdp1.pre_minibatch_start(model)
+    with FSDP.summon_full_params(model):
+        full = {k: v.detach().clone() for k, v in model.named_parameters()}
+    if mode == "odc":
+        fsdp1.stop()
+    return full
+
+
+def test_fsdp1_rank_with_zero_microbatches():
+    a = run_ranks(_train_zero, 2, "stock")
+    b = run_ranks(_train_zero, 2, "odc")
+    for k in a[0]:
+        torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
