@@ -311,3 +311,48 @@ def test_fsdp2_rank_with_zero_microbatches():
     for k in a[0]:
         torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
         torch.testing.assert_close(b[0][k], b[1][k], rtol=0, atol=0)
+
+
+def _train_no_sync(rank, world, mode):
+    """User code written for lock-step FSDP2: gradient sync switched off for all but the last microbatch."""
+    import torch.nn as nn
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(20, 32), nn.Tanh(), nn.Linear(32, 32), nn.Tanh(), nn.Linear(32, 3))
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 64 << 20)
+        fsdp2.patch_fsdp2()
+    fully_shard(model[2])
+    fully_shard(model)
+    if mode == "odc":
+        for m in (model[2], model):
+            fsdp2.patch_lazy_init(m)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    for step in range(2):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        for i in range(3):
+            model.set_requires_gradient_sync(i == 2)
+            g = torch.Generator().manual_seed(100 * step + 10 * i + rank)
+            x = torch.randn(5, 20, generator=g)
+            y = torch.randint(0, 3, (5,), generator=g)
+            nn.functional.cross_entropy(model(x), y).backward()
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    if mode == "odc":
+        fsdp2.stop()
+    return full
+
+
+def test_fsdp2_gradient_sync_toggle_written_for_lockstep_fsdp_still_works():
+    a = run_ranks(_train_no_sync, 2, "stock")
+    b = run_ranks(_train_no_sync, 2, "odc")
+    for k in a[0]:
+        torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
