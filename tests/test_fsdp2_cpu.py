@@ -356,3 +356,59 @@ def test_fsdp2_gradient_sync_toggle_written_for_lockstep_fsdp_still_works():
     b = run_ranks(_train_no_sync, 2, "odc")
     for k in a[0]:
         torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
+
+
+def _train_variants(rank, world, mode, variant):
+    """Other stock FSDP2 knobs user code may carry over: no reshard after forward, explicit unshard, prefetch lists."""
+    import torch.nn as nn
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+
+    torch.manual_seed(0)
+    blocks = [nn.Sequential(nn.Linear(24, 24), nn.Tanh()) for _ in range(3)]
+    model = nn.Sequential(*blocks, nn.Linear(24, 3))
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 64 << 20)
+        fsdp2.patch_fsdp2()
+    raf = variant != "keep_unsharded"
+    for b in blocks:
+        fully_shard(b, reshard_after_forward=raf)
+    fully_shard(model, reshard_after_forward=raf)
+    if variant == "prefetch":
+        for i, b in enumerate(blocks):
+            if i + 1 < len(blocks):
+                b.set_modules_to_forward_prefetch([blocks[i + 1]])
+            if i > 0:
+                b.set_modules_to_backward_prefetch([blocks[i - 1]])
+    if mode == "odc":
+        for m in blocks + [model]:
+            fsdp2.patch_lazy_init(m)
+    opt = torch.optim.SGD(model.parameters(), lr=0.05)
+    for step in range(2):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        for i in range(2):
+            g = torch.Generator().manual_seed(100 * step + 10 * i + rank)
+            x = torch.randn(5, 24, generator=g)
+            y = torch.randint(0, 3, (5,), generator=g)
+            if variant == "explicit_unshard":
+                model.unshard()
+            nn.functional.cross_entropy(model(x), y).backward()
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    if mode == "odc":
+        fsdp2.stop()
+    return full
+
+
+@pytest.mark.parametrize("variant", ["keep_unsharded", "explicit_unshard", "prefetch"])
+def test_fsdp2_stock_knobs_keep_working(variant):
+    a = run_ranks(_train_variants, 2, "stock", variant)
+    b = run_ranks(_train_variants, 2, "odc", variant)
+    for k in a[0]:
+        torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
