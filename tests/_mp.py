@@ -57,3 +57,19 @@ def run_ranks(fn, world, *args, env=None, timeout=240):
         if errs:
             raise RuntimeError("\n".join(errs))
         return [torch.load(os.path.join(outdir, f"out_{r}.pt"), weights_only=False) for r in range(world)]
+
+
+def _pair_entry(rank, world, fn, stock_args, odc_args):
+    return fn(rank, world, "stock", *stock_args), fn(rank, world, "odc", *odc_args)
+
+
+def run_pair(fn, world, stock_args=(), odc_args=None, env=None, timeout=300):
+    """``fn(rank, world, "stock", ...)`` and then ``fn(rank, world, "odc", ...)`` in the same rank processes.
+
+    Returns the two per-rank result lists.  One set of child processes instead of two: starting them (and
+    importing torch in each) costs more than the small training runs the comparison tests do.
+    """
+    stock_args = tuple(stock_args)
+    res = run_ranks(_pair_entry, world, fn, stock_args, stock_args if odc_args is None else tuple(odc_args),
+                    env=env, timeout=timeout)
+    return [r[0] for r in res], [r[1] for r in res]

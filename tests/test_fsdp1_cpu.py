@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from _mp import run_ranks
+from _mp import run_pair
 
 
 def _train(rank, world, mode, uneven, mp=False):
@@ -69,8 +69,7 @@ def _train(rank, world, mode, uneven, mp=False):
 
 @pytest.mark.parametrize("uneven", [False, True])
 def test_fsdp1_matches_stock(uneven):
-    a = run_ranks(_train, 2, "stock", uneven)
-    b = run_ranks(_train, 2, "odc", uneven)
+    a, b = run_pair(_train, 2, (uneven,))
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
@@ -78,16 +77,14 @@ def test_fsdp1_matches_stock(uneven):
 
 def test_fsdp1_two_emulated_nodes():
     # one rank per "node": flat-parameter gathers and gradient contributions to the peer use the inter-node path
-    a = run_ranks(_train, 2, "stock", True)
-    b = run_ranks(_train, 2, "odc", True, env={"LOCAL_WORLD_SIZE": "1"})
+    a, b = run_pair(_train, 2, (True,), env={"LOCAL_WORLD_SIZE": "1"})
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
 
 
 def test_fsdp1_mixed_precision_reduces_bf16_gradients_into_fp32_accumulators():
-    a = run_ranks(_train, 2, "stock", True, True)
-    b = run_ranks(_train, 2, "odc", True, True)
+    a, b = run_pair(_train, 2, (True, True))
     # the unsharded gradients reach the reduction in bf16 (stock's widening pass is skipped) and land in fp32
     assert b[0][2] == {(torch.bfloat16, torch.float32)}
     assert a[0][0] == pytest.approx(b[0][0], rel=2e-2), (a[0][0], b[0][0])
@@ -136,7 +133,6 @@ def _train_zero(rank, world, mode):
 
 
 def test_fsdp1_rank_with_zero_microbatches():
-    a = run_ranks(_train_zero, 2, "stock")
-    b = run_ranks(_train_zero, 2, "odc")
+    a, b = run_pair(_train_zero, 2)
     for k in a[0]:
         torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)

@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from _mp import run_ranks
+from _mp import run_pair
 
 
 def _make_batches(rank, step, n_micro, vocab=1024):
@@ -80,9 +80,9 @@ def _assert_mostly_close(x, y, rtol, atol, outliers=0.01, outlier_atol=5e-3):
 
 
 def _compare(world, **kw):
-    a = run_ranks(_train, world, "stock", 4, kw.get("uneven", False), kw.get("mesh", (world,)), 0, kw.get("mp", False))
-    b = run_ranks(_train, world, "odc", 4, kw.get("uneven", False), kw.get("mesh", (world,)), kw.get("hpz", 0),
-                  kw.get("mp", False), env=kw.get("env"))
+    a, b = run_pair(_train, world, (4, kw.get("uneven", False), kw.get("mesh", (world,)), 0, kw.get("mp", False)),
+                    (4, kw.get("uneven", False), kw.get("mesh", (world,)), kw.get("hpz", 0), kw.get("mp", False)),
+                    env=kw.get("env"))
     la, lb = a[0][0], b[0][0]
     tol = 2e-2 if kw.get("mp") else 1e-4
     assert la == pytest.approx(lb, rel=tol), (la, lb)
@@ -175,8 +175,7 @@ def _train_fused(rank, world, mode):
 
 
 def test_fsdp2_hsdp_hpz_checkpointing_fused_adamw():
-    a = run_ranks(_train_fused, 4, "stock")
-    b = run_ranks(_train_fused, 4, "odc")
+    a, b = run_pair(_train_fused, 4)
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-3), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
@@ -255,8 +254,7 @@ def _train_partial(rank, world, mode):
 
 @pytest.mark.parametrize("segments", ["1", "0"])
 def test_fsdp2_frozen_parameters_and_skipped_branches(segments):
-    a = run_ranks(_train_partial, 2, "stock")
-    b = run_ranks(_train_partial, 2, "odc", env={"ODC_REDUCE_SEGMENTS": segments})
+    a, b = run_pair(_train_partial, 2, env={"ODC_REDUCE_SEGMENTS": segments})
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-5), (a[0][0], b[0][0])
     for k in a[0][1]:
         torch.testing.assert_close(a[0][1][k], b[0][1][k], rtol=1e-5, atol=1e-6)
@@ -306,8 +304,7 @@ def _train_zero(rank, world, mode):
 
 
 def test_fsdp2_rank_with_zero_microbatches():
-    a = run_ranks(_train_zero, 2, "stock")
-    b = run_ranks(_train_zero, 2, "odc")
+    a, b = run_pair(_train_zero, 2)
     for k in a[0]:
         torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
         torch.testing.assert_close(b[0][k], b[1][k], rtol=0, atol=0)
@@ -352,8 +349,7 @@ def _train_no_sync(rank, world, mode):
 
 
 def test_fsdp2_gradient_sync_toggle_written_for_lockstep_fsdp_still_works():
-    a = run_ranks(_train_no_sync, 2, "stock")
-    b = run_ranks(_train_no_sync, 2, "odc")
+    a, b = run_pair(_train_no_sync, 2)
     for k in a[0]:
         torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
 
@@ -408,7 +404,6 @@ def _train_variants(rank, world, mode, variant):
 
 @pytest.mark.parametrize("variant", ["keep_unsharded", "explicit_unshard", "prefetch"])
 def test_fsdp2_stock_knobs_keep_working(variant):
-    a = run_ranks(_train_variants, 2, "stock", variant)
-    b = run_ranks(_train_variants, 2, "odc", variant)
+    a, b = run_pair(_train_variants, 2, (variant,))
     for k in a[0]:
         torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
