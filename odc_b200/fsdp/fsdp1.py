@@ -45,6 +45,7 @@ class _State:
     gather: Optional[GatherService] = None
     next_index = 0
     in_shard: Optional[FlatParamHandle] = None
+    touched: set = set()   # keys of flat parameters this rank reduced a gradient for in this minibatch
 
 
 _S = _State
@@ -163,6 +164,7 @@ def _reduce_grad(state: _FSDPState, handle: FlatParamHandle) -> None:
     if not reduction.has_accumulation(handle._odc_key):
         reduction.register(handle._odc_key, padded.numel() // state.world_size, padded.dtype, state.process_group)
     reduction.scatter_accumulate(handle._odc_key, padded, state.process_group, scale=1.0 / factor)
+    _S.touched.add(handle._odc_key)
     # marks "a gradient was produced" for stock bookkeeping; the real value is assigned in pre_optimizer_step
     flat_param._saved_grad_shard = reduction.get_accumulation(handle._odc_key)
 
@@ -228,9 +230,13 @@ def pre_optimizer_step(fsdp_model) -> None:
     if not isinstance(fsdp_model, _FSDPState):
         raise AssertionError("pass the root FSDP module")
     reduction, _ = _services()
-    reduction.sync()
+    # flat parameters that no rank produced a gradient for keep ``.grad is None``, as under stock FSDP
+    used = set()
+    for other in reduction.sync(payload=sorted(_S.touched, key=str)):
+        used.update(other or ())
+    _S.touched = set()
     for h in _handles(fsdp_model):
-        if not reduction.has_accumulation(h._odc_key):
+        if not reduction.has_accumulation(h._odc_key) or h._odc_key not in used:
             continue
         acc = reduction.get_accumulation(h._odc_key)
         fp = h.flat_param
@@ -288,6 +294,7 @@ def unpatch_fsdp1() -> None:
     _S.patched = False
     _S.reduction = _S.gather = None
     _S.next_index = 0
+    _S.touched = set()
 
 
 def stop() -> None:

@@ -67,6 +67,9 @@ class _GroupInfo:
     reduce_calls: int = 0
     divide: Dict[str, Any] = field(default_factory=dict)
     replica_fresh: bool = False               # the optimizer already wrote the low-precision copy
+    position: Dict[int, int] = field(default_factory=dict)   # id(fsdp_param) -> index in the group
+    touched: set = field(default_factory=set)  # parameters this rank reduced a gradient for in this minibatch
+    used: Optional[set] = None                 # union of `touched` over all ranks (None: not known, treat as all)
 
     @property
     def acc_key(self) -> str:
@@ -179,6 +182,7 @@ def _pin_group(group: FSDPParamGroup, index: int) -> None:
         offs[id(params[i])] = o
         o += numels[i]
     info = _GroupInfo(index, group, key, master, replica, numels, trainable, o, offs)
+    info.position = {id(p): i for i, p in enumerate(params)}
     hpz = getattr(group, "_odc_hpz_size", 0)
     if _S.enable_hpz and hpz:
         ranks = control.group_ranks(group.mesh_info.shard_process_group)
@@ -326,6 +330,7 @@ def _odc_foreach_reduce(fsdp_params, unsharded_grads, reduce_scatter_group, redu
             _S.reduction.scatter_accumulate(info.acc_key, rs_input, reduce_scatter_group)
             event = reduce_scatter_stream.record_event()
     info.reduce_calls += 1
+    info.touched.update(info.position[id(p)] for p in fsdp_params)
     info.divide = dict(factor=gradient_divide_factor, all_reduce_group=all_reduce_group,
                        all_reduce_hook=all_reduce_hook, orig_dtype=orig_dtype)
     return rs_input, event, event, None, None, None
@@ -409,7 +414,15 @@ def pre_optimizer_step(model, materialize_grads: bool = True) -> None:
     """
     _require_patched()
     infos = _infos_of(model)
-    _S.reduction.sync()
+    # which parameters received a gradient from ANY rank: the others keep ``.grad is None`` (as under stock FSDP,
+    # where an optimizer skips them) instead of taking a step on an all-zero gradient
+    mine = {info.index: sorted(info.touched) for info in infos}
+    everyone = _S.reduction.sync(payload=mine)
+    for info in infos:
+        info.used = set()
+        for other in everyone:
+            info.used.update((other or {}).get(info.index, ()))
+        info.touched = set()
     for info in infos:
         with nvtx_range(f"odc::update_gradients:{info.group._module_fqn}"):
             if materialize_grads:
@@ -465,6 +478,8 @@ def _update_gradients(info: _GroupInfo) -> None:
     if orig_dtype is not None and out.dtype != orig_dtype:
         out = out.to(orig_dtype)
     for i in info.trainable:
+        if info.used is not None and i not in info.used:
+            continue  # no rank produced a gradient for this parameter in this minibatch
         p = group.fsdp_params[i]
         o = info.acc_offsets[id(p)]
         new_grad = torch.as_strided(out, size=p.sharded_size, stride=p.contiguous_sharded_stride, storage_offset=o)
@@ -586,6 +601,23 @@ def get_symm_buffer_memory_breakdown() -> Dict[str, float]:
 # ------------------------------------------------------------------------------------------
 # optimizer on the flat shards
 # ------------------------------------------------------------------------------------------
+def _used_ranges(info: _GroupInfo, steps: List[int]):
+    """``(start, stop, step)`` element ranges of the group's flat shard whose parameters received a gradient.
+
+    ``steps[i]`` is the number of updates parameter i has had including this one; adjacent parameters with the same
+    count are merged (the usual case is one range for the whole group).
+    """
+    ranges, start = [], 0
+    for i, n in enumerate(info.numels):
+        if n and (info.used is None or i in info.used):
+            if ranges and ranges[-1][1] == start and ranges[-1][2] == steps[i]:
+                ranges[-1] = (ranges[-1][0], start + n, steps[i])
+            else:
+                ranges.append((start, start + n, steps[i]))
+        start += n
+    return ranges
+
+
 class FusedAdamW:
     """AdamW that runs once per parameter group directly on the flat symmetric shard.
 
@@ -601,6 +633,7 @@ class FusedAdamW:
         self.model, self.lr, self.betas, self.eps, self.weight_decay = model, lr, betas, eps, weight_decay
         self.step_count = 0
         self.state: Dict[int, Dict[str, torch.Tensor]] = {}
+        self.param_steps: Dict[int, List[int]] = {}   # group index -> updates applied to each of its parameters
         self._clip_scale = 1.0
 
     def _groups(self) -> List[_GroupInfo]:
@@ -650,9 +683,16 @@ class FusedAdamW:
             if st is None:
                 st = {"m": torch.zeros_like(info.master), "v": torch.zeros_like(info.master)}
                 self.state[info.index] = st
-            ops.fused_adamw_(info.master, acc, st["m"], st["v"], info.replica, self.lr, self.betas[0],
-                             self.betas[1], self.eps, self.weight_decay, self.step_count,
-                             self._clip_scale / _divide_factor(info))
+            # bias correction counts the updates a parameter has actually had (one that no rank used is skipped)
+            steps = self.param_steps.setdefault(info.index, [self.step_count - 1] * len(info.numels))
+            for i in range(len(steps)):
+                if info.used is None or i in info.used:
+                    steps[i] += 1
+            for a, b, t in _used_ranges(info, steps):
+                ops.fused_adamw_(info.master[a:b], acc[a:b], st["m"][a:b], st["v"][a:b],
+                                 None if info.replica is None else info.replica[a:b], self.lr, self.betas[0],
+                                 self.betas[1], self.eps, self.weight_decay, t,
+                                 self._clip_scale / _divide_factor(info))
             info.replica_fresh = info.replica is not None
         self._clip_scale = 1.0
 
@@ -662,10 +702,12 @@ class FusedAdamW:
 
     def state_dict(self) -> Dict[str, Any]:
         return {"step": self.step_count, "state": {k: {n: t.clone() for n, t in v.items()} for k, v in self.state.items()},
+                "param_steps": {k: list(v) for k, v in self.param_steps.items()},
                 "hyper": dict(lr=self.lr, betas=self.betas, eps=self.eps, weight_decay=self.weight_decay)}
 
     def load_state_dict(self, sd: Dict[str, Any]) -> None:
         self.step_count = sd["step"]
         self.state = {k: {n: t.clone() for n, t in v.items()} for k, v in sd["state"].items()}
+        self.param_steps = {k: list(v) for k, v in sd.get("param_steps", {}).items()}
         for k, v in sd.get("hyper", {}).items():
             setattr(self, k, v)

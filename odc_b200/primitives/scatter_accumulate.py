@@ -145,11 +145,16 @@ class ReductionService:
             slots.zero_()
 
     # -- once per minibatch ------------------------------------------------------------------
-    def sync(self, pg: Optional[dist.ProcessGroup] = None) -> None:
-        """Collective over all ranks: wait until every contribution addressed to this rank has landed."""
+    def sync(self, pg: Optional[dist.ProcessGroup] = None, payload=None) -> list:
+        """Collective over all ranks: wait until every contribution addressed to this rank has landed.
+
+        ``payload`` (any picklable object) rides on the one host exchange this call makes; the list of every
+        rank's payload is returned, so callers need no collective of their own at the minibatch boundary.
+        """
         with nvtx_range("odc::scatter_accumulate_sync"):
             me = control.rank()
-            everyone = control.all_gather_object(dict(self.dispatched))
+            gathered = control.all_gather_object((dict(self.dispatched), payload))
+            everyone = [d for d, _ in gathered]
             self.expected_total = sum(d.get(me, 0) for d in everyone)
             self.transport.wait_arrivals(self.counter, self.expected_total)
             if self.deterministic:
@@ -158,6 +163,7 @@ class ReductionService:
                     acc.zero_()
                     for r in range(slots.shape[0]):
                         acc.add_(slots[r])
+            return [x for _, x in gathered]
 
     def stop(self) -> None:
         self._sync_device()

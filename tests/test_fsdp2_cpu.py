@@ -407,3 +407,71 @@ def test_fsdp2_stock_knobs_keep_working(variant):
     a, b = run_pair(_train_variants, 2, (variant,))
     for k in a[0]:
         torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
+
+
+def _train_unused(rank, world, mode, fused):
+    """In minibatch 1 no rank uses `b` (one parameter of the root group) nor the `side` unit.
+
+    Stock FSDP leaves their ``.grad`` at None and AdamW skips them: no weight decay, no moment update.  The
+    on-demand engine has to do the same, although their accumulators exist and are (all-zero) "complete".
+    """
+    import torch.nn as nn
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Linear(24, 24)
+            self.b = nn.Linear(24, 24)
+            self.side = nn.Sequential(nn.Linear(24, 24), nn.Tanh())
+            self.head = nn.Linear(24, 5)
+
+        def forward(self, x, extras):
+            h = torch.tanh(self.a(x))
+            if extras:
+                h = h + self.b(h)
+                h = h + self.side(h)
+            return self.head(h)
+
+    torch.manual_seed(0)
+    model = Net()
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 64 << 20)
+        fsdp2.patch_fsdp2()
+    fully_shard(model.side)
+    fully_shard(model)
+    if mode == "odc":
+        for m in (model.side, model):
+            fsdp2.patch_lazy_init(m)
+    use_fused = fused and mode == "odc"
+    opt = (fsdp2.FusedAdamW(model, lr=1e-2, weight_decay=0.1) if use_fused
+           else torch.optim.AdamW(model.parameters(), lr=1e-2, weight_decay=0.1))
+    for step in range(3):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        for i in range(2):
+            g = torch.Generator().manual_seed(1000 * step + 10 * i + rank)
+            x = torch.randn(6, 24, generator=g)
+            y = torch.randint(0, 5, (6,), generator=g)
+            nn.functional.cross_entropy(model(x, extras=step != 1), y).backward()
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model, materialize_grads=not use_fused)
+            if step == 1 and not use_fused:
+                assert model.b.weight.grad is None and model.side[0].weight.grad is None
+                assert model.a.weight.grad is not None
+        opt.step()
+        opt.zero_grad()
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    if mode == "odc":
+        fsdp2.stop()
+    return full
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_fsdp2_parameters_no_rank_used_are_left_alone(fused):
+    a, b = run_pair(_train_unused, 2, (fused,))
+    for k in a[0]:
+        torch.testing.assert_close(a[0][k], b[0][k], rtol=2e-5, atol=2e-6)
