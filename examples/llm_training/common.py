@@ -28,6 +28,20 @@ class Timer:
         self.sink[self.name] = self.sink.get(self.name, 0.0) + time.perf_counter() - self.t0
 
 
+def init_device(args, rank):
+    """Process group + device of this rank: one GPU over NCCL, or (``--cpu``) a CPU rank over gloo."""
+    import torch.distributed as dist
+    if args.cpu:
+        dev = torch.device("cpu")
+        dist.init_process_group("gloo")
+        torch.set_num_threads(max(1, (os.cpu_count() or 2) // int(os.environ.get("WORLD_SIZE", "1"))))
+        return dev
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    return dev
+
+
 def build_sequences(args, vocab):
     if args.dataset != "synthetic":
         return torch.load(args.dataset)

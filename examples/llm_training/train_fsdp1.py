@@ -12,7 +12,7 @@ from torch.distributed.fsdp import MixedPrecision
 from torch.distributed.fsdp.wrap import ModuleWrapPolicy
 
 from args import get_args
-from common import Timer, log_metrics, make_dataset, mark_done, memory_metrics
+from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics
 
 import odc_b200 as odc
 from odc_b200.data import to_device
@@ -27,9 +27,7 @@ if ODC:
 def main():
     args = get_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    dev = torch.device("cuda", torch.cuda.current_device())
-    dist.init_process_group("nccl", device_id=dev)
+    dev = init_device(args, rank)
     if ODC:
         odc.init_nvshmem(dev)
     cfg = get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)

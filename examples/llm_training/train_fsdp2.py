@@ -14,7 +14,7 @@ from torch.distributed.device_mesh import init_device_mesh
 from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
 from args import get_args
-from common import Timer, log_metrics, make_dataset, mark_done, memory_metrics
+from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics
 
 import odc_b200 as odc
 from odc_b200.data import to_device
@@ -30,9 +30,7 @@ HSDP = os.environ.get("HSDP", "0") == "1"
 def main():
     args = get_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
-    dev = torch.device("cuda", torch.cuda.current_device())
-    dist.init_process_group("nccl", device_id=dev)
+    dev = init_device(args, rank)
     cfg = get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)
     if ODC:
         odc.init_nvshmem(dev)
@@ -40,8 +38,8 @@ def main():
     with torch.device(dev):
         model = DecoderLM(cfg)
     model.reset_parameters(seed=0)
-    mesh = init_device_mesh("cuda", (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard")) if HSDP \
-        else init_device_mesh("cuda", (world,))
+    mesh = init_device_mesh(dev.type, (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard")) if HSDP \
+        else init_device_mesh(dev.type, (world,))
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
     raf = (world // 2 if not HSDP else max(1, world // 4)) if HPZ else True
     for layer in model.layers:

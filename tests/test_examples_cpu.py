@@ -1,4 +1,5 @@
-"""The FSDP2 example script runs end to end on CPU ranks (gloo), with and without on-demand communication."""
+"""The example scripts run end to end on CPU ranks (gloo), with and without on-demand communication."""
+import json
 import os
 import subprocess
 import sys
@@ -17,3 +18,24 @@ def test_fsdp2_example_cpu(env, tmp_path):
     r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert "step 9 loss" in r.stdout
+
+
+@pytest.mark.parametrize("script,env,packing", [
+    ("train_fsdp2.py", {"ODC": "1"}, "DynamicDiffMicro"),      # ranks get different numbers of microbatches
+    ("train_fsdp2.py", {"ODC": "0"}, "DynamicSameMicro"),      # lock-step baseline
+    ("train_fsdp1.py", {"ODC": "1"}, "DynamicDiffMicro"),
+])
+def test_llm_trainers_cpu(script, env, packing, tmp_path):
+    e = dict(os.environ, **env, ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path))
+    port = 29720 + (3 if script.endswith("1.py") else 0) + (1 if env["ODC"] == "0" else 0)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "examples/llm_training", script), "--cpu",
+           "--model_name", "tiny", "--steps", "2", "--minibatch_size", "4", "--num-sequences", "32",
+           "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512",
+           "--packing_method", packing, "--run_name", "cpu_smoke"]
+    r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert [l["step"] for l in lines] == [0, 1]
+    assert all(l["loss"] == l["loss"] and l["tokens"] > 0 for l in lines)
+    assert (tmp_path / "cpu_smoke.done").exists()
