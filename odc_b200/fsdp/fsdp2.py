@@ -711,3 +711,74 @@ class FusedAdamW:
         self.param_steps = {k: list(v) for k, v in sd.get("param_steps", {}).items()}
         for k, v in sd.get("hyper", {}).items():
             setattr(self, k, v)
+
+    # -- the layout ``torch.optim.AdamW`` has under FSDP2, so checkpoints move between the two ------------------
+    def _param_slots(self):
+        """``(name, info, index in group, fsdp_param, element offset in the flat shard)`` in model order."""
+        root = self.model._get_fsdp_state()
+        if root._is_root is None:
+            root._lazy_init()  # moves the shards into the heap and creates the per-group records used below
+        names = {id(prm): n for n, prm in self.model.named_parameters()}
+        order = {n: k for k, n in enumerate(names.values())}
+        slots = []
+        for info in self._groups():
+            off = 0
+            for i, p in enumerate(info.group.fsdp_params):
+                slots.append((names[id(p.sharded_param)], info, i, p, off))
+                off += info.numels[i]
+        return sorted(slots, key=lambda slot: order[slot[0]])
+
+    def _moments(self, info: _GroupInfo) -> Dict[str, torch.Tensor]:
+        st = self.state.get(info.index)
+        if st is None:
+            st = self.state[info.index] = {"m": torch.zeros_like(info.master), "v": torch.zeros_like(info.master)}
+        return st
+
+    @torch.no_grad()
+    def full_state_dict(self) -> Dict[str, Any]:
+        """Unsharded state keyed by parameter name, in the format of a full ``AdamW`` state dict (collective).
+
+        It is what ``get_optimizer_state_dict(..., full_state_dict=True)`` returns for ``torch.optim.AdamW`` on the
+        same model — ``step`` / ``exp_avg`` / ``exp_avg_sq`` per parameter plus one parameter group — so a run can
+        be resumed with either optimizer, under either engine.
+        """
+        state = {}
+        for name, info, i, p, off in self._param_slots():
+            st = self._moments(info)
+            steps = self.param_steps.get(info.index, [self.step_count] * len(info.numels))
+            entry = {"step": torch.tensor(float(steps[i]))}
+            for key, flat in (("exp_avg", st["m"]), ("exp_avg_sq", st["v"])):
+                local = torch.as_strided(flat, p.sharded_size, p.contiguous_sharded_stride, off)
+                entry[key] = p.to_sharded_dtensor(local).full_tensor().cpu()
+            state[name] = entry
+        probe = torch.optim.AdamW([torch.zeros(1, requires_grad=True)], lr=self.lr, betas=tuple(self.betas),
+                                  eps=self.eps, weight_decay=self.weight_decay)
+        group = dict(probe.state_dict()["param_groups"][0])
+        group["params"] = list(state.keys())
+        return {"state": state, "param_groups": [group]}
+
+    @torch.no_grad()
+    def load_full_state_dict(self, sd: Dict[str, Any]) -> None:
+        """Inverse of :meth:`full_state_dict`; also takes what stock FSDP2 + ``torch.optim.AdamW`` saved (collective)."""
+        from torch.distributed.tensor import DTensor, distribute_tensor
+        steps = []
+        for name, info, i, p, off in self._param_slots():
+            st = self._moments(info)
+            per_param = self.param_steps.setdefault(info.index, [0] * len(info.numels))
+            entry = sd["state"].get(name)
+            if entry is None:  # a parameter that had not been updated yet when the checkpoint was written
+                per_param[i] = 0
+                continue
+            ref = p.sharded_param
+            for key, flat in (("exp_avg", st["m"]), ("exp_avg_sq", st["v"])):
+                src = entry[key]
+                if not isinstance(src, DTensor):
+                    src = distribute_tensor(src.to(device=flat.device, dtype=flat.dtype), ref.device_mesh, ref.placements)
+                torch.as_strided(flat, p.sharded_size, p.contiguous_sharded_stride, off).copy_(src.to_local())
+            per_param[i] = int(float(entry["step"]))
+            steps.append(per_param[i])
+        self.step_count = max(steps, default=0)
+        if sd.get("param_groups"):
+            g = sd["param_groups"][0]
+            self.lr, self.betas, self.eps = g.get("lr", self.lr), tuple(g.get("betas", self.betas)), g.get("eps", self.eps)
+            self.weight_decay = g.get("weight_decay", self.weight_decay)

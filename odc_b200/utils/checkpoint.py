@@ -57,6 +57,9 @@ class Checkpointer:
     def load_optim(self, model, opt) -> None:
         path = os.path.join(self.folder, self.last_training_time, OPTIM_FILE)
         full = torch.load(path, mmap=True, weights_only=True, map_location="cpu")
+        if hasattr(opt, "load_full_state_dict"):  # FusedAdamW: same file format as torch.optim.AdamW
+            opt.load_full_state_dict(full)
+            return
         set_optimizer_state_dict(model, opt, full, options=StateDictOptions(full_state_dict=True,
                                                                            broadcast_from_rank0=True))
 
@@ -74,7 +77,9 @@ class Checkpointer:
     def save(self, model, optim=None) -> str:
         model_sd = self._model_state(model)
         optim_sd = None
-        if optim is not None:
+        if optim is not None and hasattr(optim, "full_state_dict"):
+            optim_sd = optim.full_state_dict()  # FusedAdamW writes the layout torch.optim.AdamW has
+        elif optim is not None:
             optim_sd = get_optimizer_state_dict(model, optim, options=StateDictOptions(full_state_dict=True,
                                                                                        cpu_offload=True))
         stamp = str(int(time.time() * 1000))

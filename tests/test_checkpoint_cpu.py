@@ -109,3 +109,80 @@ def _roundtrip(rank, world, folder, dcp_api, direction):
 def test_checkpoint_roundtrip(dcp_api, direction):
     with tempfile.TemporaryDirectory() as folder:
         assert all(run_ranks(_roundtrip, 2, folder, dcp_api, direction))
+
+
+def _tiny(mesh, seed):
+    from torch.distributed.fsdp import fully_shard
+
+    from odc_b200.models import DecoderLM, get_config
+    model = DecoderLM(get_config("tiny"))
+    model.reset_parameters(seed=seed)
+    for layer in model.layers:
+        fully_shard(layer, mesh=mesh)
+    fully_shard(model, mesh=mesh)
+    return model
+
+
+def _minibatch(model, opt, rank, step, engine_on, fused):
+    from odc_b200.data import LengthSpec, make_minibatch
+    from odc_b200.fsdp import fsdp2
+    if engine_on:
+        fsdp2.pre_minibatch_start(model)
+    for mb in make_minibatch(rank, step, 1024, LengthSpec("uniform", lo=16, hi=64), 2, 64, seed=5):
+        model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"],
+              loss_scale=mb["loss_scale"]).backward()
+    if engine_on:
+        fsdp2.pre_optimizer_step(model, materialize_grads=not fused)
+    opt.step()
+    opt.zero_grad()
+
+
+def _resume(rank, world, folder, writer_kind, reader_kind):
+    """Write after two minibatches, resume in a fresh model with the same or the other optimizer / engine."""
+    from torch.distributed.device_mesh import init_device_mesh
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+    from odc_b200.utils.checkpoint import Checkpointer
+    mesh = init_device_mesh("cpu", (world,))
+    odc.init_nvshmem("cpu", 256 << 20)
+
+    def make(kind, seed):
+        on = kind == "fused"
+        if on:
+            fsdp2.patch_fsdp2()
+        else:
+            fsdp2.unpatch_fsdp2()
+        model = _tiny(mesh, seed)
+        if on:
+            for m in list(model.layers) + [model]:
+                fsdp2.patch_lazy_init(m)
+        opt = (fsdp2.FusedAdamW(model, lr=2e-3, weight_decay=0.05) if on
+               else torch.optim.AdamW(model.parameters(), lr=2e-3, weight_decay=0.05))
+        return model, opt, on
+
+    model, opt, on = make(writer_kind, 1)
+    for step in range(2):
+        _minibatch(model, opt, rank, step, on, on)
+    ck = Checkpointer(folder)
+    ck.save(model, opt)
+    _minibatch(model, opt, rank, 2, on, on)          # the uninterrupted run
+    want = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+
+    model2, opt2, on2 = make(reader_kind, 2)         # different initial weights: the load must replace them
+    ck2 = Checkpointer(folder)
+    ck2.load_model(model2)
+    ck2.load_optim(model2, opt2)
+    _minibatch(model2, opt2, rank, 2, on2, on2)
+    got = {k: v.full_tensor().clone() for k, v in model2.state_dict().items()}
+    if on2:
+        fsdp2.stop()
+    return want, got
+
+
+@pytest.mark.parametrize("writer,reader", [("fused", "fused"), ("fused", "torch"), ("torch", "fused")])
+def test_resume_with_fused_or_torch_adamw(writer, reader):
+    with tempfile.TemporaryDirectory() as folder:
+        want, got = run_ranks(_resume, 2, folder, writer, reader)[0]
+    for k in want:
+        torch.testing.assert_close(got[k], want[k], rtol=1e-5, atol=1e-6)
