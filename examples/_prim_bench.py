@@ -14,8 +14,14 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (900 nominal)
 
 
+CPU = os.environ.get("ODC_BENCH_CPU", "0") == "1"  # functional run on CPU ranks (gloo + host-shm heap)
+
+
 def setup():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    if CPU:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        return rank, world, torch.device("cpu")
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -23,10 +29,36 @@ def setup():
     return rank, world, dev
 
 
+def sync():
+    if not CPU:
+        torch.cuda.synchronize()
+
+
+def reduce_scatter_sum(out: torch.Tensor, inp: torch.Tensor) -> None:
+    """The library collective the on-demand reduction is compared with (gloo has none: all-reduce, keep my row)."""
+    if not CPU:
+        dist.reduce_scatter_tensor(out, inp)
+        return
+    full = inp.clone()
+    dist.all_reduce(full)
+    out.copy_(full.view(dist.get_world_size(), -1)[dist.get_rank()])
+
+
 def device_time_ms(fn, iters: int, warmup: int = 3) -> float:
-    """Median over iterations of the max-over-ranks device time of ``fn`` (CUDA events)."""
+    """Median over iterations of the max-over-ranks device time of ``fn`` (CUDA events; wall clock on CPU ranks)."""
     for _ in range(warmup):
         fn()
+    if CPU:
+        import time
+        ts = []
+        for _ in range(iters):
+            dist.barrier()
+            t0 = time.perf_counter()
+            fn()
+            t = torch.tensor([(time.perf_counter() - t0) * 1e3])
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ts.append(float(t))
+        return statistics.median(ts)
     torch.cuda.synchronize()
     ts = []
     for _ in range(iters):

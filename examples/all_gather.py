@@ -9,7 +9,7 @@ Payload per rank = shard_bytes * (W-1) crosses NVLink inbound; bandwidth = paylo
 import torch
 import torch.distributed as dist
 
-from _prim_bench import NVLINK_GBS, device_time_ms, emit, setup, sizes_from_argv
+from _prim_bench import NVLINK_GBS, device_time_ms, emit, setup, sizes_from_argv, sync
 
 
 def main():
@@ -22,7 +22,7 @@ def main():
         n = nbytes // 2
         shard = reg.allocate_symm_buffer(f"s{nbytes}", (n,), torch.bfloat16)
         shard.copy_(torch.randn(n, device=dev).bfloat16())
-        torch.cuda.synchronize(); dist.barrier()
+        sync(); dist.barrier()
         out = torch.empty(world * n, dtype=torch.bfloat16, device=dev)
         ref = torch.empty_like(out)
         iters = 20 if nbytes <= (128 << 20) else 8

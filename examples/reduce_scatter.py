@@ -12,7 +12,7 @@ import sys
 import torch
 import torch.distributed as dist
 
-from _prim_bench import NVLINK_GBS, device_time_ms, emit, setup, sizes_from_argv
+from _prim_bench import NVLINK_GBS, device_time_ms, emit, reduce_scatter_sum, setup, sizes_from_argv, sync
 
 
 def main():
@@ -38,13 +38,13 @@ def main():
             red.sync()
 
         def nccl_fn():
-            dist.reduce_scatter_tensor(rs_out, x)
+            reduce_scatter_sum(rs_out, x)
             ref_acc.add_(rs_out)
 
-        acc.zero_(); ref_acc.zero_(); torch.cuda.synchronize(); dist.barrier()
+        acc.zero_(); ref_acc.zero_(); sync(); dist.barrier()
         t_odc = device_time_ms(odc_fn, iters)
         t_nccl = device_time_ms(nccl_fn, iters)
-        torch.cuda.synchronize(); dist.barrier()
+        sync(); dist.barrier()
         assert torch.equal(acc, ref_acc), f"scatter_accumulate mismatch at {nbytes}: {(acc - ref_acc).abs().max()}"
         payload = nbytes * (world - 1)
         row = dict(op="scatter_accumulate", world=world, dtype=str(dtype), shard_bytes=nbytes, ms=t_odc,

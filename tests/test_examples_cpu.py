@@ -39,3 +39,18 @@ def test_llm_trainers_cpu(script, env, packing, tmp_path):
     assert [l["step"] for l in lines] == [0, 1]
     assert all(l["loss"] == l["loss"] and l["tokens"] > 0 for l in lines)
     assert (tmp_path / "cpu_smoke.done").exists()
+
+
+@pytest.mark.parametrize("script,port", [("all_gather.py", 29731), ("reduce_scatter.py", 29732)])
+def test_primitive_benchmarks_cpu(script, port, tmp_path):
+    """The two micro-benchmarks check their result against the library collective; run them small on CPU ranks."""
+    e = dict(os.environ, ODC_BENCH_CPU="1", ODC_SYMMETRIC_SIZE="64M", ODC_OUT_DIR=str(tmp_path))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "examples", script),
+           "--size-min=4096", "--size-max=65536"]
+    r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    out = [f for f in os.listdir(tmp_path) if f.endswith(".json")]
+    assert len(out) == 1
+    rows = json.load(open(tmp_path / out[0]))
+    assert [row["shard_bytes"] for row in rows] == [4096, 8192, 16384, 32768, 65536]
