@@ -142,6 +142,12 @@ class HostShmHeap(SymmetricHeap):
         self._alloc = OffsetAllocator(self.nbytes)
         self._base = self._maps[self.rank].data_ptr()
         control.host_barrier()
+        # every rank of the node has mapped and opened the files: drop the names now, so that nothing is left in
+        # /dev/shm however the job ends (mappings and descriptors keep the memory alive)
+        try:
+            os.unlink(self._paths[self.rank])
+        except FileNotFoundError:
+            pass
 
     def alloc(self, nbytes: int) -> int:
         return self._alloc.alloc(nbytes)
