@@ -20,6 +20,7 @@ from __future__ import annotations
 import fcntl
 import logging
 import os
+import threading
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -139,6 +140,7 @@ class HostShmHeap(SymmetricHeap):
             r: torch.from_file(p, shared=True, size=self.nbytes, dtype=torch.uint8) for r, p in self._paths.items()
         }
         self._lock_fds = {r: os.open(p, os.O_RDWR) for r, p in self._paths.items()}
+        self._mutexes = {r: threading.Lock() for r in self._paths}
         self._alloc = OffsetAllocator(self.nbytes)
         self._base = self._maps[self.rank].data_ptr()
         control.host_barrier()
@@ -179,18 +181,26 @@ class HostShmHeap(SymmetricHeap):
         return None
 
     class _Locked:
-        def __init__(self, fd):
-            self.fd = fd
+        """File lock between processes plus a mutex between the threads of this process.
+
+        ``flock`` belongs to the open file description, so two threads that share the descriptor (the trainer and
+        the inter-node server threads of one rank) would both "hold" it; the mutex is what keeps them apart.
+        """
+
+        def __init__(self, fd, mutex):
+            self.fd, self.mutex = fd, mutex
 
         def __enter__(self):
+            self.mutex.acquire()
             fcntl.flock(self.fd, fcntl.LOCK_EX)
 
         def __exit__(self, *exc):
             fcntl.flock(self.fd, fcntl.LOCK_UN)
+            self.mutex.release()
 
     def owner_lock(self, r: int):
         """Exclusive lock of rank ``r``'s region: makes a read-modify-write by one producer atomic."""
-        return HostShmHeap._Locked(self._lock_fds[r])
+        return HostShmHeap._Locked(self._lock_fds[r], self._mutexes[r])
 
     def close(self) -> None:
         control.host_barrier()

@@ -73,3 +73,15 @@ def run_pair(fn, world, stock_args=(), odc_args=None, env=None, timeout=300):
     res = run_ranks(_pair_entry, world, fn, stock_args, stock_args if odc_args is None else tuple(odc_args),
                     env=env, timeout=timeout)
     return [r[0] for r in res], [r[1] for r in res]
+
+
+def assert_mostly_close(x, y, rtol, atol, outliers=0.01, outlier_atol=5e-3):
+    """Close everywhere, except that a few elements may differ by an Adam step or two.
+
+    The fp32 sum of the gradient contributions depends on their arrival order; where a gradient is almost zero
+    that rounding noise can flip the normalised Adam update of single elements, so a small fraction of elements is
+    allowed a looser absolute bound.
+    """
+    bad = (x - y).abs() > atol + rtol * y.abs()
+    assert float(bad.float().mean()) <= outliers, f"{int(bad.sum())} of {bad.numel()} elements differ"
+    torch.testing.assert_close(x, y, rtol=rtol, atol=outlier_atol)
