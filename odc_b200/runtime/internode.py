@@ -120,6 +120,7 @@ class InterNodeEndpoint:
         self._tables: Dict[int, torch.Tensor] = {}
         self.served = {"get": 0, "add": 0}
         self.rejected = 0  # connections that failed the challenge
+        self._stat_lock = threading.Lock()  # the counters are bumped from several server threads
         self.sent = {"get": 0, "add": 0, "bytes": 0}
         if self.cuda:
             from .. import _ext
@@ -162,7 +163,8 @@ class InterNodeEndpoint:
 
     def _serve(self, conn: socket.socket) -> None:
         if not self._authenticate(conn):
-            self.rejected += 1
+            with self._stat_lock:
+                self.rejected += 1
             conn.close()
             return
         if self.cuda:
@@ -190,7 +192,8 @@ class InterNodeEndpoint:
                         self._read_region(offset, numel, dt, staging)
                         conn.sendall(_REPLY.pack(0, nb))
                         conn.sendall(memoryview(staging.numpy())[:nb])
-                        self.served["get"] += 1
+                        with self._stat_lock:
+                            self.served["get"] += 1
                     elif op == OP_ADD:
                         src_dt, dst_dt = _DTYPES[src_c], _DTYPES[dst_c]
                         nb = numel * _itemsize(src_dt)
@@ -199,7 +202,8 @@ class InterNodeEndpoint:
                         _recv_exact(conn, memoryview(staging.numpy())[:nb])
                         self._add_region(offset, numel, src_dt, dst_dt, scale, ctr_off, staging)
                         conn.sendall(_REPLY.pack(0, 0))
-                        self.served["add"] += 1
+                        with self._stat_lock:
+                            self.served["add"] += 1
                     else:
                         raise ValueError(f"unknown operation {op}")
                 except (IndexError, ValueError, RuntimeError) as e:  # report to the client, keep serving
