@@ -9,11 +9,18 @@ import pytest
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port() -> int:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 @pytest.mark.parametrize("env", [{"ODC": "1"}, {"ODC": "1", "HPZ": "1"}, {"ODC": "0"}])
 def test_fsdp2_example_cpu(env, tmp_path):
     e = dict(os.environ, **env, ODC_SYMMETRIC_SIZE="256M")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", str(29700 + len(env) + (1 if env.get("ODC") == "0" else 0)),
+           "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(REPO, "examples/FSDP2/example.py"), "--cpu", "--checkpoint-dir", str(tmp_path)]
     r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
@@ -27,7 +34,7 @@ def test_fsdp2_example_cpu(env, tmp_path):
 ])
 def test_llm_trainers_cpu(script, env, packing, tmp_path):
     e = dict(os.environ, **env, ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path))
-    port = 29720 + (3 if script.endswith("1.py") else 0) + (1 if env["ODC"] == "0" else 0)
+    port = _free_port()
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "examples/llm_training", script), "--cpu",
            "--model_name", "tiny", "--steps", "2", "--minibatch_size", "4", "--num-sequences", "32",
@@ -41,12 +48,12 @@ def test_llm_trainers_cpu(script, env, packing, tmp_path):
     assert (tmp_path / "cpu_smoke.done").exists()
 
 
-@pytest.mark.parametrize("script,port", [("all_gather.py", 29731), ("reduce_scatter.py", 29732)])
-def test_primitive_benchmarks_cpu(script, port, tmp_path):
+@pytest.mark.parametrize("script", ["all_gather.py", "reduce_scatter.py"])
+def test_primitive_benchmarks_cpu(script, tmp_path):
     """The two micro-benchmarks check their result against the library collective; run them small on CPU ranks."""
     e = dict(os.environ, ODC_BENCH_CPU="1", ODC_SYMMETRIC_SIZE="64M", ODC_OUT_DIR=str(tmp_path))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "examples", script),
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(REPO, "examples", script),
            "--size-min=4096", "--size-max=65536"]
     r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
