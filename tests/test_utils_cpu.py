@@ -77,7 +77,9 @@ def test_clock_sampler_parses_nvidia_smi_output(tmp_path, monkeypatch):
     from odc_b200.utils.clocks import ClockSampler
     import time
     s = ClockSampler(gpu_index=0).start()
-    time.sleep(0.5)
+    deadline = time.time() + 20.0           # the fake tool prints its three rows at once; wait until they are on disk
+    while time.time() < deadline and sum(1 for _ in open(s.path)) < 3:
+        time.sleep(0.05)
     out = s.stop()
     assert out["samples"] == 3 and out["sm_max_mhz"] == 1965.0
     assert out["sm_mhz"] == pytest.approx(1360.0)                 # median of the samples taken under load
