@@ -283,3 +283,38 @@ def imbalance_report(lengths: Sequence[int], world: int, max_token_len: int,
     return {"lockstep_cost": lockstep, "ondemand_cost": ondemand, "ideal_cost": ideal,
             "lockstep_bubble": lockstep / ideal - 1.0, "ondemand_bubble": ondemand / ideal - 1.0,
             "microbatches_lockstep": [len(r) for r in same], "microbatches_ondemand": [len(r) for r in diff]}
+
+
+def report_main(argv=None) -> None:
+    """``python -m odc_b200.data``: predicted idle share of lock-step vs per-rank microbatching."""
+    import argparse
+    import json
+
+    import numpy as np
+
+    from .synthetic import LengthSpec, sample_lengths
+    ap = argparse.ArgumentParser(description=report_main.__doc__)
+    ap.add_argument("--world", type=int, default=8)
+    ap.add_argument("--sequences", type=int, default=256, help="sequences in one global minibatch")
+    ap.add_argument("--max-token-len", type=int, default=16384)
+    ap.add_argument("--dist", default="lognormal", choices=["lognormal", "longtail", "uniform"])
+    ap.add_argument("--median", type=float, default=512.0)
+    ap.add_argument("--sigma", type=float, default=1.0)
+    ap.add_argument("--cap", type=int, default=8192)
+    ap.add_argument("--cost-model", default="linear", choices=["linear", "fit"])
+    ap.add_argument("--minibatches", type=int, default=20)
+    ap.add_argument("--seed", type=int, default=0)
+    a = ap.parse_args(argv)
+    spec = {"lognormal": LengthSpec("lognormal", lo=16, median=a.median, sigma=a.sigma, cap=min(a.cap, a.max_token_len)),
+            "longtail": LengthSpec("longtail", long=(a.cap // 2, min(a.cap, a.max_token_len))),
+            "uniform": LengthSpec("uniform", lo=16, hi=min(a.cap, a.max_token_len))}[a.dist]
+    rng = np.random.default_rng(a.seed)
+    cost = get_cost_fn(a.cost_model)
+    lock, ond = [], []
+    for _ in range(a.minibatches):
+        r = imbalance_report(sample_lengths(spec, a.sequences, rng), a.world, a.max_token_len, cost)
+        lock.append(r["lockstep_bubble"])
+        ond.append(r["ondemand_bubble"])
+    print(json.dumps({"world": a.world, "sequences": a.sequences, "dist": a.dist, "minibatches": a.minibatches,
+                      "lockstep_idle_share_mean": float(np.mean(lock)), "ondemand_idle_share_mean": float(np.mean(ond)),
+                      "lockstep_idle_share_max": float(np.max(lock)), "ondemand_idle_share_max": float(np.max(ond))}))

@@ -108,3 +108,14 @@ def test_batched_dataset_limits_and_pads():
     mbs = ds[0]
     assert sum(mb["num_seqs"] for mb in mbs) >= 3 and all(mb["num_tokens"] <= 4096 for mb in mbs)
     assert "rank 0" in ds.last_debug
+
+
+def test_report_cli_shows_the_long_tail_bubble(capsys):
+    import json
+
+    from odc_b200.data.packing import report_main
+    report_main(["--world", "8", "--sequences", "64", "--dist", "longtail", "--max-token-len", "32768", "--cap", "32768",
+                 "--minibatches", "5"])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["lockstep_idle_share_mean"] > 3 * out["ondemand_idle_share_mean"]
+    assert 0.0 <= out["ondemand_idle_share_mean"] < 0.1
