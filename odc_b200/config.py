@@ -58,6 +58,20 @@ def wait_timeout_ms() -> int:
     return int(os.environ.get("ODC_WAIT_TIMEOUT_MS", "60000"))
 
 
+def sync_by_posting() -> bool:
+    """``ODC_SYNC_POSTING=0``: ``ReductionService.sync`` always exchanges dispatch counts on the host.
+
+    By default a ``sync`` that carries no payload makes the counts known by one-sided stores into the owners.
+    """
+    return os.environ.get("ODC_SYNC_POSTING", "1") not in ("0", "false")
+
+
+def heartbeat_s() -> float:
+    """``ODC_HEARTBEAT_S`` > 0: publish a host heartbeat every second and, before each once-per-minibatch
+    synchronisation, treat a peer whose last beat is older than this many seconds as failed (0: off)."""
+    return float(os.environ.get("ODC_HEARTBEAT_S", "0"))
+
+
 def debug_bounds() -> bool:
     """Turn on offset/peer-index checks inside the communication kernels."""
     return os.environ.get("ODC_DEBUG_BOUNDS", "0") not in ("0", "", "false")

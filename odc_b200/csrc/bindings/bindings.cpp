@@ -40,7 +40,12 @@ int kind_of(at::ScalarType t) {
   }
 }
 
-// ring of self-resetting completion counters used by scatter_accumulate launches
+// Ring of self-resetting completion counters used by scatter_accumulate launches.  A slot is zero again once the
+// last CTA of its launch has finished, so a slot may be handed out again only after that launch has run: with
+// kDoneSlots slots this holds while fewer than kDoneSlots such launches are queued or running per device.  CUDA
+// itself blocks the launching thread long before that many kernels are pending on a device (its launch queue holds
+// on the order of a thousand), which is what bounds the number in flight.
+constexpr unsigned long long kDoneSlots = 16384;
 unsigned int* next_done_slot(int device) {
   static std::mutex mu;
   static std::unordered_map<int, Tensor> rings;
@@ -48,12 +53,12 @@ unsigned int* next_done_slot(int device) {
   std::lock_guard<std::mutex> lock(mu);
   auto it = rings.find(device);
   if (it == rings.end()) {
-    auto t = torch::zeros({1024}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
+    auto t = torch::zeros({static_cast<int64_t>(kDoneSlots)}, torch::dtype(torch::kInt32).device(torch::kCUDA, device));
     it = rings.emplace(device, t).first;
     seq[device] = 0;
   }
   unsigned long long s = seq[device]++;
-  return reinterpret_cast<unsigned int*>(it->second.data_ptr<int>()) + (s % 1024);
+  return reinterpret_cast<unsigned int*>(it->second.data_ptr<int>()) + (s % kDoneSlots);
 }
 
 // ---------------------------------------------------------------------------------------- heap
@@ -85,7 +90,7 @@ Tensor reconstruct_tensor(const std::string& blob, std::vector<int64_t> shape, a
 
 // ---------------------------------------------------------------------------------------- comm
 void gather(Tensor out2d, Tensor table, int64_t n, at::ScalarType src_dtype, int my_index, bool checkb,
-            Tensor status) {
+            Tensor status, int64_t src_region_elems) {
   c10::cuda::CUDAGuard g(out2d.device());
   odc::bind_device(out2d.get_device());
   const int nranks = static_cast<int>(table.numel());
@@ -96,30 +101,31 @@ void gather(Tensor out2d, Tensor table, int64_t n, at::ScalarType src_dtype, int
   TORCH_CHECK(narrow || src_dtype == out2d.scalar_type(), "gather: only same-dtype or fp32->bf16");
   check(odc::launch_gather(table.data_ptr<int64_t>() ? reinterpret_cast<const long long*>(table.data_ptr<int64_t>()) : nullptr,
                            out2d.data_ptr(), static_cast<size_t>(n), ssz, dsz, narrow, nranks, my_index, checkb,
-                           status.data_ptr<int>(), sm_count(), cur_stream()),
+                           status.data_ptr<int>(), sm_count(), cur_stream(),
+                           checkb ? static_cast<size_t>(src_region_elems) : 0),
         "gather launch");
 }
 
 void scatter_accumulate(Tensor inp2d, Tensor acc_table, Tensor ctr_table, int64_t n, at::ScalarType acc_dtype,
-                        int my_index, double scale, bool checkb, Tensor status) {
+                        int my_index, double scale, bool checkb, Tensor status, int64_t acc_region_elems) {
   c10::cuda::CUDAGuard g(inp2d.device());
   odc::bind_device(inp2d.get_device());
   const int nranks = static_cast<int>(acc_table.numel());
   TORCH_CHECK(inp2d.is_contiguous() && inp2d.numel() == n * nranks, "scatter_accumulate: bad input shape");
-  (void)checkb;
   check(odc::launch_scatter_accumulate(inp2d.data_ptr(), kind_of(inp2d.scalar_type()),
                                        reinterpret_cast<const long long*>(acc_table.data_ptr<int64_t>()),
                                        kind_of(acc_dtype),
                                        reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()),
                                        static_cast<size_t>(n), nranks, my_index, static_cast<float>(scale),
                                        next_done_slot(inp2d.get_device()), sm_count(), cur_stream(),
-                                       status.data_ptr<int>()),
+                                       status.data_ptr<int>(), checkb ? acc_region_elems : 0),
         "scatter_accumulate launch");
 }
 
 bool scatter_accumulate_segments(std::vector<Tensor> grads, std::vector<int64_t> chunk_numels,
                                  std::vector<int64_t> dst_offsets, Tensor acc_table, Tensor ctr_table,
-                                 at::ScalarType acc_dtype, int my_index, double scale) {
+                                 at::ScalarType acc_dtype, int my_index, double scale, bool checkb,
+                                 c10::optional<Tensor> status, int64_t acc_region_elems) {
   // Returns false (nothing launched) when the list does not fit this path; the caller then flattens the gradients.
   if (grads.empty() || grads.size() > static_cast<size_t>(odc::kMaxScatterSegments) || acc_dtype != at::kFloat) return false;
   TORCH_CHECK(grads.size() == chunk_numels.size() && grads.size() == dst_offsets.size(),
@@ -143,7 +149,9 @@ bool scatter_accumulate_segments(std::vector<Tensor> grads, std::vector<int64_t>
                                                 reinterpret_cast<const long long*>(acc_table.data_ptr<int64_t>()),
                                                 reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()), nranks,
                                                 my_index, static_cast<float>(scale),
-                                                next_done_slot(grads[0].get_device()), sm_count(), cur_stream()),
+                                                next_done_slot(grads[0].get_device()), sm_count(), cur_stream(),
+                                                (checkb && status.has_value()) ? acc_region_elems : 0,
+                                                status.has_value() ? status->data_ptr<int>() : nullptr),
         "scatter_accumulate_segments launch");
   return true;
 }
@@ -155,6 +163,35 @@ void wait_counter(Tensor counter, int64_t expected, int64_t timeout_ms, Tensor s
                                  static_cast<unsigned long long>(timeout_ms) * 1000000ull, status.data_ptr<int>(),
                                  cur_stream()),
         "wait_counter launch");
+}
+
+void post_counts(std::vector<int64_t> slot_addrs, std::vector<int64_t> counts, int64_t epoch, int device) {
+  c10::cuda::CUDAGuard g(c10::Device(c10::kCUDA, static_cast<c10::DeviceIndex>(device)));
+  odc::bind_device(device);
+  TORCH_CHECK(slot_addrs.size() == counts.size() && slot_addrs.size() <= size_t(odc::kMaxPostedCounts),
+              "post_counts: at most ", odc::kMaxPostedCounts, " owners");
+  odc::PostedCounts pc{};
+  pc.n = static_cast<int>(slot_addrs.size());
+  for (int i = 0; i < pc.n; ++i) {
+    TORCH_CHECK(slot_addrs[i] != 0 && (slot_addrs[i] & 7) == 0, "post_counts: bad slot address");
+    TORCH_CHECK(counts[i] >= 0 && counts[i] < (int64_t(1) << 32), "post_counts: count out of range");
+    pc.slot_addr[i] = slot_addrs[i];
+    pc.value[i] = (static_cast<unsigned long long>(epoch) << 32) | static_cast<unsigned long long>(counts[i]);
+  }
+  check(odc::launch_post_counts(pc, cur_stream()), "post_counts launch");
+}
+
+void wait_posted(Tensor slots, int64_t nprod, int64_t epoch, Tensor counter, int64_t timeout_ms, Tensor status,
+                 Tensor expected_out) {
+  c10::cuda::CUDAGuard g(counter.device());
+  odc::bind_device(counter.get_device());
+  TORCH_CHECK(slots.scalar_type() == at::kLong && slots.numel() >= nprod && expected_out.scalar_type() == at::kLong,
+              "wait_posted: int64 slots (one per producer) and an int64 output word");
+  check(odc::launch_wait_posted(slots.data_ptr(), static_cast<int>(nprod), static_cast<unsigned long long>(epoch),
+                                counter.data_ptr(), static_cast<unsigned long long>(timeout_ms) * 1000000ull,
+                                status.data_ptr<int>(), reinterpret_cast<unsigned long long*>(expected_out.data_ptr()),
+                                cur_stream()),
+        "wait_posted launch");
 }
 
 // ---------------------------------------------------------------------------------------- ops
@@ -519,10 +556,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tensor_from_ptr", &tensor_from_ptr);
   m.def("get_ipc_handle", &get_ipc_handle);
   m.def("reconstruct_tensor", &reconstruct_tensor);
-  m.def("gather", &gather);
-  m.def("scatter_accumulate", &scatter_accumulate);
-  m.def("scatter_accumulate_segments", &scatter_accumulate_segments);
+  // the trailing *_region_elems arguments are the DECLARED lengths the debug checks (check = true) hold the launch to
+  m.def("gather", &gather, py::arg("out2d"), py::arg("table"), py::arg("n"), py::arg("src_dtype"), py::arg("my_index"),
+        py::arg("check"), py::arg("status"), py::arg("src_region_elems") = 0);
+  m.def("scatter_accumulate", &scatter_accumulate, py::arg("inp2d"), py::arg("acc_table"), py::arg("ctr_table"),
+        py::arg("n"), py::arg("acc_dtype"), py::arg("my_index"), py::arg("scale"), py::arg("check"), py::arg("status"),
+        py::arg("acc_region_elems") = 0);
+  m.def("scatter_accumulate_segments", &scatter_accumulate_segments, py::arg("grads"), py::arg("chunk_numels"),
+        py::arg("dst_offsets"), py::arg("acc_table"), py::arg("ctr_table"), py::arg("acc_dtype"), py::arg("my_index"),
+        py::arg("scale"), py::arg("check") = false, py::arg("status") = py::none(), py::arg("acc_region_elems") = 0);
   m.def("wait_counter", &wait_counter);
+  m.def("post_counts", &post_counts);
+  m.def("wait_posted", &wait_posted);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("rope_qkv", &rope_qkv);

@@ -10,13 +10,17 @@ namespace odc {
 enum DType : int { kF32 = 0, kBF16 = 1, kF16 = 2 };
 
 // ---- communication -------------------------------------------------------------------------
+// Debug launches (ODC_DEBUG_BOUNDS=1): `check` / a non-zero `src_region_elems` / `acc_len` make the kernel verify,
+// before it touches anything, that the rotation start names a member of the group, that no table entry is null or
+// misaligned, and that the elements it is about to read (gather) or add (scatter) fit the DECLARED length of the
+// registered region.  A refused launch sets kErrBounds / kErrPeerIndex in the status word and returns normally.
 cudaError_t launch_gather(const long long* peers, void* out, size_t n, int src_elem_size, int dst_elem_size,
                           bool src_is_f32_dst_is_bf16, int nranks, int start, bool check, int* status,
-                          int sm_count, cudaStream_t stream);
+                          int sm_count, cudaStream_t stream, size_t src_region_elems = 0);
 cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long long* accs, int acc_kind,
                                       const long long* ctrs, size_t n, int nranks, int start, float scale,
                                       unsigned int* done_slot, int sm_count, cudaStream_t stream,
-                                      int* status_for_bulk = nullptr);
+                                      int* status_for_bulk = nullptr, long long acc_len = 0);
 // scatter_accumulate taken straight from up to kMaxScatterSegments contiguous gradient tensors (fp32 accumulators
 // only).  The caller fills count/src/chunk/total/dst; the launcher derives tile_prefix and vec.
 constexpr int kMaxScatterSegments = 32;
@@ -31,9 +35,24 @@ struct ScatterSegments {
 };
 cudaError_t launch_scatter_accumulate_segments(ScatterSegments segs, int in_kind, const long long* accs,
                                                const long long* ctrs, int nranks, int start, float scale,
-                                               unsigned int* done_slot, int sm_count, cudaStream_t stream);
+                                               unsigned int* done_slot, int sm_count, cudaStream_t stream,
+                                               long long acc_len = 0, int* status = nullptr);
 cudaError_t launch_wait_counter(const void* ctr, unsigned long long expected, unsigned long long budget_ns,
                                 int* status, cudaStream_t stream);
+// One-sided exchange of the dispatch counts (what `sync` needs to know how many arrivals to wait for).
+// post: value[i] = (synchronisation number << 32) | contributions sent so far to owner i, stored with a system-scope
+// release at slot_addr[i] (this producer's slot on owner i).  wait: collect nprod postings of `epoch` from the
+// local slots, then wait until the arrival counter reaches their sum; bounded, reports through `status`.
+constexpr int kMaxPostedCounts = 72;
+struct PostedCounts {
+  int n;
+  long long slot_addr[kMaxPostedCounts];
+  unsigned long long value[kMaxPostedCounts];
+};
+cudaError_t launch_post_counts(const PostedCounts& pc, cudaStream_t stream);
+cudaError_t launch_wait_posted(const void* slots, int nprod, unsigned long long epoch, const void* ctr,
+                               unsigned long long budget_ns, int* status, unsigned long long* expected_out,
+                               cudaStream_t stream);
 
 // ---- single-primitive test kernels (device_prims.cu) ---------------------------------------------
 cudaError_t launch_put_block(void* remote_dst, const void* local_src, size_t bytes, cudaStream_t s);

@@ -35,8 +35,16 @@ __device__ __forceinline__ float bf16_hi(uint32_t u) { return __uint_as_float(u 
 // bytes-per-row copy; src rows are peers' buffers, dst rows are consecutive in `out`.
 __global__ void __launch_bounds__(kThreads)
 gather_copy_kernel(const long long* __restrict__ peers, unsigned char* __restrict__ out, size_t row_bytes,
-                   int nranks, int start, int vec_ok, int check, int* status) {
-  if (check) {  // debug build of the launch: refuse null or misaligned peer addresses instead of faulting
+                   int nranks, int start, int vec_ok, int check, int* status, size_t src_region_bytes) {
+  if (check) {  // debug launch: refuse instead of faulting; every thread takes the same branch
+    if (start < 0 || start >= nranks) {
+      if (threadIdx.x == 0) report(status, kErrPeerIndex, start, nranks);
+      return;
+    }
+    if (src_region_bytes != 0 && row_bytes > src_region_bytes) {  // would read past the registered shard
+      if (threadIdx.x == 0) report(status, kErrBounds, -1, static_cast<int>(src_region_bytes / 16));
+      return;
+    }
     for (int p = 0; p < nranks; ++p) {
       if (peers[p] == 0 || (vec_ok && (peers[p] & 15) != 0)) {
         if (threadIdx.x == 0) report(status, kErrBounds, p, 0);
@@ -79,7 +87,23 @@ gather_copy_kernel(const long long* __restrict__ peers, unsigned char* __restric
 // ---------------------------------------------------------------- gather, fp32 -> bf16 --------
 __global__ void __launch_bounds__(kThreads)
 gather_f32_to_bf16_kernel(const long long* __restrict__ peers, __nv_bfloat16* __restrict__ out, size_t n,
-                          int nranks, int start) {
+                          int nranks, int start, int check, int* status, size_t src_region_elems) {
+  if (check) {
+    if (start < 0 || start >= nranks) {
+      if (threadIdx.x == 0) report(status, kErrPeerIndex, start, nranks);
+      return;
+    }
+    if (src_region_elems != 0 && n > src_region_elems) {
+      if (threadIdx.x == 0) report(status, kErrBounds, -1, static_cast<int>(src_region_elems / 16));
+      return;
+    }
+    for (int p = 0; p < nranks; ++p) {
+      if (peers[p] == 0 || (peers[p] & 15) != 0) {
+        if (threadIdx.x == 0) report(status, kErrBounds, p, 0);
+        return;
+      }
+    }
+  }
   const size_t nvec = n / 8;  // 8 floats in (2 x 16 B), 8 bf16 out (16 B)
   constexpr size_t kTile = size_t(kThreads) * 2;
   const size_t tiles_per_row = (nvec + kTile - 1) / kTile;
@@ -140,11 +164,43 @@ __device__ __forceinline__ void finish_and_signal(const long long* ctrs, int nra
   }
 }
 
+// Debug launch (acc_len != 0): `extent` elements starting at each owner's accumulator base must fit the declared
+// accumulator length, the rotation start must name a member of the group and no table entry may be null or
+// misaligned.  A refused launch touches no accumulator; it still signals arrival so that no owner waits for it, and
+// the producer's host raises from the status word.  Uniform across the grid: every thread takes the same branch.
+// Returns 0: proceed; 1: refused, counters usable (signal arrival); 2: refused, the tables themselves are bad.
+__device__ __forceinline__ int scatter_refused(const long long* accs, const long long* ctrs, int nranks, int start,
+                                               long long extent, long long acc_len, int* status) {
+  if (acc_len == 0) return 0;
+  int code = kOk, detail = 0, seen = 0;
+  bool tables_ok = true;
+  for (int p = 0; p < nranks; ++p)
+    if (accs[p] == 0 || (accs[p] & 3) != 0 || ctrs[p] == 0 || (ctrs[p] & 7) != 0) {
+      code = kErrBounds; detail = p; tables_ok = false; break;
+    }
+  if (!tables_ok) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) report(status, code, detail, seen);
+    return 2;
+  }
+  if (start < 0 || start >= nranks) {
+    code = kErrPeerIndex; detail = start; seen = nranks;
+  } else if (extent > acc_len) {
+    code = kErrBounds; detail = -1; seen = static_cast<int>(acc_len < 0x7fffffff ? acc_len : 0x7fffffff);
+  }
+  if (code == kOk) return 0;
+  if (threadIdx.x == 0 && blockIdx.x == 0) report(status, code, detail, seen);
+  return 1;
+}
+
 template <typename InT>
 __global__ void __launch_bounds__(kThreads)
 scatter_acc_f32_kernel(const InT* __restrict__ inp, const long long* __restrict__ accs,
                        const long long* __restrict__ ctrs, size_t n, int nranks, int start, float scale,
-                       unsigned int* done_slot, int vec_ok) {
+                       unsigned int* done_slot, int vec_ok, long long acc_len, int* status) {
+  if (const int refused = scatter_refused(accs, ctrs, nranks, start, static_cast<long long>(n), acc_len, status)) {
+    if (refused == 1) finish_and_signal(ctrs, nranks, done_slot);
+    return;
+  }
   constexpr int kPerVec = 4;  // one 16-byte reduction = 4 floats
   const size_t nvec = n / kPerVec;
   const bool aligned = vec_ok != 0;
@@ -200,7 +256,15 @@ template <typename InT>
 __global__ void __launch_bounds__(kThreads)
 scatter_acc_segments_kernel(const __grid_constant__ ScatterSegments segs, const long long* __restrict__ accs,
                             const long long* __restrict__ ctrs, int nranks, int start, float scale,
-                            unsigned int* done_slot) {
+                            unsigned int* done_slot, long long acc_len, int* status) {
+  {
+    long long extent = 0;
+    for (int s = 0; s < segs.count; ++s) extent = max(extent, segs.dst[s] + min(segs.chunk[s], segs.total[s]));
+    if (const int refused = scatter_refused(accs, ctrs, nranks, start, extent, acc_len, status)) {
+      if (refused == 1) finish_and_signal(ctrs, nranks, done_slot);
+      return;
+    }
+  }
   constexpr long long kTileElems = static_cast<long long>(kTileVecs) * 4;
   const long long tiles_per_owner = segs.tile_prefix[segs.count];
   const long long total_tiles = tiles_per_owner * nranks;
@@ -251,7 +315,11 @@ scatter_acc_segments_kernel(const __grid_constant__ ScatterSegments segs, const 
 __global__ void __launch_bounds__(kThreads)
 scatter_acc_bf16_kernel(const __nv_bfloat16* __restrict__ inp, const long long* __restrict__ accs,
                         const long long* __restrict__ ctrs, size_t n, int nranks, int start, float scale,
-                        unsigned int* done_slot) {
+                        unsigned int* done_slot, long long acc_len, int* status) {
+  if (const int refused = scatter_refused(accs, ctrs, nranks, start, static_cast<long long>(n), acc_len, status)) {
+    if (refused == 1) finish_and_signal(ctrs, nranks, done_slot);
+    return;
+  }
   const bool aligned = (n % 2) == 0;
   const size_t total = n * nranks;
   if (aligned) {
@@ -286,10 +354,14 @@ constexpr int kBulkSmem = kBulkStages * kBulkBytes + 64;
 __global__ void __launch_bounds__(32)
 scatter_acc_bulk_kernel(const float* __restrict__ inp, const long long* __restrict__ accs,
                         const long long* __restrict__ ctrs, size_t n, int nranks, int start,
-                        unsigned int* done_slot, int* status) {
+                        unsigned int* done_slot, int* status, long long acc_len) {
   extern __shared__ __align__(128) unsigned char bulk_smem[];
   using namespace sm100;
   __shared__ int abort_flag;
+  if (const int refused = scatter_refused(accs, ctrs, nranks, start, static_cast<long long>(n), acc_len, status)) {
+    if (refused == 1) finish_and_signal(ctrs, nranks, done_slot);
+    return;
+  }
   const uint32_t buf0 = smem_u32(bulk_smem);
   const uint32_t bar0 = buf0 + kBulkStages * kBulkBytes;
   const size_t row_bytes = n * sizeof(float);
@@ -348,6 +420,48 @@ __global__ void wait_counter_kernel(const unsigned long long* ctr, unsigned long
   if (threadIdx.x == 0 && blockIdx.x == 0) bounded_wait_ge(ctr, expected, budget_ns, status, /*detail=*/0);
 }
 
+// ---------------------------------------------------------------- one-sided count posting ---------------------
+// `sync` without a host collective: every producer stores, on each owner, how many contributions it has sent to
+// that owner so far (cumulative, low 32 bits) together with the number of the synchronisation it belongs to (high
+// 32 bits), in the slot reserved for that producer.  The owner's wait kernel collects one posting of the current
+// synchronisation from every producer, adds the counts up and then waits for its arrival counter to reach the
+// sum.  Both waits are bounded and report through the status word.
+__global__ void post_counts_kernel(const __grid_constant__ PostedCounts pc) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < pc.n)
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(pc.slot_addr[i]), "l"(pc.value[i]) : "memory");
+}
+
+__global__ void wait_posted_kernel(const unsigned long long* slots, int nprod, unsigned long long epoch,
+                                   const unsigned long long* ctr, unsigned long long budget_ns, int* status,
+                                   unsigned long long* expected_out) {
+  const int lane = threadIdx.x;
+  unsigned long long sum = 0;
+  bool ok = true;
+  const uint64_t t0 = globaltimer_ns();
+  for (int p = lane; p < nprod && ok; p += 32) {
+    unsigned long long v = ld_acquire_sys(slots + p);
+    while ((v >> 32) < epoch) {
+      __nanosleep(256);
+      if (globaltimer_ns() - t0 > budget_ns) {
+        report(status, kErrWaitTimeout, 1000 + p, static_cast<int>(v >> 32));  // producer p never posted
+        ok = false;
+        break;
+      }
+      v = ld_acquire_sys(slots + p);
+    }
+    sum += v & 0xffffffffull;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  ok = __all_sync(0xffffffffu, ok);
+  if (lane == 0 && ok) {
+    if (expected_out != nullptr) *expected_out = sum;
+    const uint64_t spent = globaltimer_ns() - t0;
+    bounded_wait_ge(ctr, sum, budget_ns > spent ? budget_ns - spent : 0, status, /*detail=*/0);
+  }
+}
+
 int grid_for(size_t tiles, int sm_count) {
   // ODC_COMM_CTAS caps the grid of the communication kernels: fewer CTAs leave more of each SM to the GEMMs
   // they overlap with, at the price of fewer bytes in flight on the links
@@ -364,26 +478,28 @@ int grid_for(size_t tiles, int sm_count) {
 
 cudaError_t launch_gather(const long long* peers, void* out, size_t n, int src_elem_size, int dst_elem_size,
                           bool src_is_f32_dst_is_bf16, int nranks, int start, bool check, int* status,
-                          int sm_count, cudaStream_t stream) {
+                          int sm_count, cudaStream_t stream, size_t src_region_elems) {
   if (n == 0 || nranks == 0) return cudaSuccess;
   if (src_is_f32_dst_is_bf16) {
     const size_t tiles = ((n / 8 + kThreads * 2 - 1) / (kThreads * 2) + 1) * nranks;
     gather_f32_to_bf16_kernel<<<grid_for(tiles, sm_count), kThreads, 0, stream>>>(
-        peers, static_cast<__nv_bfloat16*>(out), n, nranks, start);
+        peers, static_cast<__nv_bfloat16*>(out), n, nranks, start, check ? 1 : 0, status, src_region_elems);
   } else {
     if (src_elem_size != dst_elem_size) return cudaErrorInvalidValue;
     const size_t row_bytes = n * src_elem_size;
     const int vec_ok = ((row_bytes % 16) == 0 || nranks == 1) && (reinterpret_cast<uintptr_t>(out) % 16) == 0;
     const size_t tiles = ((row_bytes / 16 + kTileVecs - 1) / kTileVecs + 1) * nranks;
     gather_copy_kernel<<<grid_for(tiles, sm_count), kThreads, 0, stream>>>(
-        peers, static_cast<unsigned char*>(out), row_bytes, nranks, start, vec_ok, check ? 1 : 0, status);
+        peers, static_cast<unsigned char*>(out), row_bytes, nranks, start, vec_ok, check ? 1 : 0, status,
+        src_region_elems * src_elem_size);
   }
   return cudaGetLastError();
 }
 
 cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long long* accs, int acc_kind,
                                       const long long* ctrs, size_t n, int nranks, int start, float scale,
-                                      unsigned int* done_slot, int sm_count, cudaStream_t stream, int* status_for_bulk) {
+                                      unsigned int* done_slot, int sm_count, cudaStream_t stream, int* status_for_bulk,
+                                      long long acc_len) {
   if (nranks == 0) return cudaSuccess;
   const size_t tiles = ((n / 4 + kTileVecs - 1) / kTileVecs + 1) * nranks;
   const int grid = grid_for(tiles, sm_count);
@@ -405,16 +521,18 @@ cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long l
     const size_t bulk_tiles = ((n * sizeof(float) + kBulkBytes - 1) / kBulkBytes) * nranks;
     const int bulk_grid = bulk_tiles < size_t(sm_count) ? static_cast<int>(bulk_tiles) : sm_count;
     scatter_acc_bulk_kernel<<<bulk_grid, 32, kBulkSmem, stream>>>(static_cast<const float*>(inp), accs, ctrs, n, nranks,
-                                                                start, done_slot, status_for_bulk);
+                                                                start, done_slot, status_for_bulk, acc_len);
   } else if (acc_kind == kF32 && in_kind == kF32) {
     scatter_acc_f32_kernel<float><<<grid, kThreads, 0, stream>>>(static_cast<const float*>(inp), accs, ctrs, n,
-                                                                 nranks, start, scale, done_slot, vec_ok);
+                                                                 nranks, start, scale, done_slot, vec_ok, acc_len,
+                                                                 status_for_bulk);
   } else if (acc_kind == kF32 && in_kind == kBF16) {
     scatter_acc_f32_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(inp), accs, ctrs, n, nranks, start, scale, done_slot, vec_ok);
+        static_cast<const __nv_bfloat16*>(inp), accs, ctrs, n, nranks, start, scale, done_slot, vec_ok, acc_len,
+        status_for_bulk);
   } else if (acc_kind == kBF16 && in_kind == kBF16) {
     scatter_acc_bf16_kernel<<<grid, kThreads, 0, stream>>>(static_cast<const __nv_bfloat16*>(inp), accs, ctrs, n,
-                                                          nranks, start, scale, done_slot);
+                                                          nranks, start, scale, done_slot, acc_len, status_for_bulk);
   } else {
     return cudaErrorInvalidValue;
   }
@@ -423,7 +541,8 @@ cudaError_t launch_scatter_accumulate(const void* inp, int in_kind, const long l
 
 cudaError_t launch_scatter_accumulate_segments(ScatterSegments segs, int in_kind, const long long* accs,
                                                const long long* ctrs, int nranks, int start, float scale,
-                                               unsigned int* done_slot, int sm_count, cudaStream_t stream) {
+                                               unsigned int* done_slot, int sm_count, cudaStream_t stream,
+                                               long long acc_len, int* status) {
   if (nranks == 0) return cudaSuccess;
   if (segs.count < 0 || segs.count > kMaxScatterSegments) return cudaErrorInvalidValue;
   constexpr long long kTileElems = static_cast<long long>(kTileVecs) * 4;
@@ -441,13 +560,29 @@ cudaError_t launch_scatter_accumulate_segments(ScatterSegments segs, int in_kind
   segs.tile_prefix[segs.count] = tiles;
   const int grid = grid_for(static_cast<size_t>(tiles) * nranks + 1, sm_count);
   if (in_kind == kF32) {
-    scatter_acc_segments_kernel<float><<<grid, kThreads, 0, stream>>>(segs, accs, ctrs, nranks, start, scale, done_slot);
+    scatter_acc_segments_kernel<float><<<grid, kThreads, 0, stream>>>(segs, accs, ctrs, nranks, start, scale, done_slot,
+                                                                      acc_len, status);
   } else if (in_kind == kBF16) {
     scatter_acc_segments_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(segs, accs, ctrs, nranks, start, scale,
-                                                                            done_slot);
+                                                                            done_slot, acc_len, status);
   } else {
     return cudaErrorInvalidValue;
   }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_post_counts(const PostedCounts& pc, cudaStream_t stream) {
+  if (pc.n <= 0) return cudaSuccess;
+  if (pc.n > kMaxPostedCounts) return cudaErrorInvalidValue;
+  post_counts_kernel<<<(pc.n + 127) / 128, 128, 0, stream>>>(pc);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wait_posted(const void* slots, int nprod, unsigned long long epoch, const void* ctr,
+                               unsigned long long budget_ns, int* status, unsigned long long* expected_out,
+                               cudaStream_t stream) {
+  wait_posted_kernel<<<1, 32, 0, stream>>>(static_cast<const unsigned long long*>(slots), nprod, epoch,
+                                           static_cast<const unsigned long long*>(ctr), budget_ns, status, expected_out);
   return cudaGetLastError();
 }
 

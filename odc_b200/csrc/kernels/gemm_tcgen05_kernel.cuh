@@ -488,7 +488,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (prev == gridDim.x - 1) {
         *p.done_slot = 0;
         __threadfence_system();
-        if (!*abort_flag)
+        // A partial sum must never be counted as a contribution: no arrival if ANY CTA of this launch gave up
+        // (each one records that in the global status word before it leaves), not only this last one.
+        const bool clean = !*abort_flag && (p.status == nullptr || *reinterpret_cast<volatile int*>(p.status) == 0);
+        if (clean)
           for (int r = 0; r < p.nranks; ++r)
             signal_add_release_sys(reinterpret_cast<unsigned long long*>(p.ctr_ptrs[r]), 1ull);
       }

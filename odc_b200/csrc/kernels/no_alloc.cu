@@ -3,6 +3,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <stdint.h>
 #include <stdio.h>
 
 #include <mutex>
@@ -132,6 +133,13 @@ extern "C" int odc_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   }
   if (rows < 0) return fail(err, err_len, 3, "rows must be non-negative");
   if (!dy || !x || !w || !rstd || !dx || !dw) return fail(err, err_len, 4, "null pointer argument");
+  // the kernels read and write dy/x/w/dx sixteen bytes at a time and rstd/dw as floats: refuse a
+  // pointer that is not aligned for that (a sliced tensor, say) instead of letting the GPU fault
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+       reinterpret_cast<uintptr_t>(dx)) & 15)
+    return fail(err, err_len, 9, "dy, x, w and dx must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(rstd) | reinterpret_cast<uintptr_t>(dw)) & 3)
+    return fail(err, err_len, 10, "rstd and dw must be 4-byte aligned");
 
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);

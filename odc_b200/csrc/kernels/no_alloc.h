@@ -21,9 +21,13 @@ extern "C" {
 // rstd (fp32 [rows], as produced by the forward pass).  All pointers are device memory owned by
 // the caller; `stream` is a cudaStream_t.  Returns 0 on success; otherwise a non-zero code and a
 // message in `err` (if err_len > 0).  Requirements: cols a multiple of 8 and at most
-// ODC_NOALLOC_MAX_COLS (larger widths are refused, nothing is launched); rows >= 0.
+// ODC_NOALLOC_MAX_COLS (larger widths are refused, nothing is launched); rows >= 0; dy, x, w and dx
+// 16-byte aligned, rstd and dw 4-byte aligned (a misaligned pointer is refused with an error code,
+// nothing is launched).
 //
-// * Nothing is allocated or freed, by this function or by anything it calls.
+// * No device memory is allocated or freed, by this function or by anything it calls.  (The CUDA
+//   runtime may still load this library's GPU code on the first launch in a process; that is the
+//   runtime's own one-time work, not a per-call allocation.)
 // * The workspace is one array shared by every call on a GPU; each GPU that loads the library
 //   holds ODC_NOALLOC_SCRATCH_BYTES of it until the process exits.  Every call overwrites the
 //   part it reads, so nothing needs clearing between calls, but two calls that overlap on the

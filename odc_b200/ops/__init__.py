@@ -35,6 +35,20 @@ def _ext():
     return loader.load()
 
 
+def check_status() -> None:
+    """Raise if a kernel of this package gave up on a bounded wait since the last check (one small D2H copy + sync).
+
+    The FSDP integrations and the reduction service read the same per-device word at every once-per-minibatch
+    synchronisation; code that uses the ops on their own calls this where it would otherwise trust the results.
+    """
+    from ..runtime.status import check_status_word
+    word = _ext().kernel_status()
+    host = word.cpu()
+    if int(host[0]) != 0:
+        word.zero_()
+        check_status_word(int(host[0]), int(host[1]), int(host[2]))
+
+
 def gemm_backend() -> str:
     return os.environ.get("ODC_GEMM", "tcgen05")
 

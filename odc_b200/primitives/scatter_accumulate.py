@@ -10,8 +10,9 @@ What differs: there is no mailbox, no request/ack word and no watcher process
 (scatter_accumulate.py:267-491).  The producer's kernel issues vector ``red.global.add``
 through the peer mapping into the owner's accumulator — each gradient byte crosses NVLink once
 and is never staged — and finishes by bumping an arrival counter on every owner with a
-system-scope release.  ``sync`` exchanges the per-owner dispatch counts on the host and then
-runs one bounded device wait until the local counter has caught up.  The counter is cumulative
+system-scope release.  ``sync`` makes the per-owner dispatch counts known to the owners — each producer
+stores its count in its slot on the owner (no host collective), or, when a payload rides along, through one host
+exchange — and then runs one bounded device wait until the local counter has caught up.  The counter is cumulative
 and never reset, so no acknowledgement travels back to the producer and ``input`` may be reused
 as soon as the call's kernel has run (stream order).
 """
@@ -32,6 +33,7 @@ from ..utils.nvtx import nvtx_range
 logger = logging.getLogger("odc_b200")
 
 COUNTER_KEY = "odc_arrival_counter"
+POSTED_KEY = "odc_posted_counts"
 
 
 def accumulation_key(key: Hashable) -> str:
@@ -55,6 +57,11 @@ class ReductionService:
         self.slots: Dict[Hashable, torch.Tensor] = {}
         self.counter = self.registry.get_or_create_symm_buffer(COUNTER_KEY, (8,), torch.int64)
         self.counter.zero_()
+        # slot p: what producer p has told this rank about its dispatches (synchronisation number << 32 | count)
+        self.posted = self.registry.get_or_create_symm_buffer(POSTED_KEY, (max(8, control.world_size()),), torch.int64)
+        self.posted.zero_()
+        self.epoch = 0
+        control.heartbeat()  # starts publishing (if enabled) before the barrier, so every peer is seen alive after it
         self._sync_device()
         control.host_barrier()
         self.calls = 0
@@ -153,10 +160,21 @@ class ReductionService:
         """
         with nvtx_range("odc::scatter_accumulate_sync"):
             me = control.rank()
-            gathered = control.all_gather_object((dict(self.dispatched), payload))
-            everyone = [d for d, _ in gathered]
-            self.expected_total = sum(d.get(me, 0) for d in everyone)
-            self.transport.wait_arrivals(self.counter, self.expected_total)
+            world = list(range(control.world_size()))
+            self.epoch += 1
+            control.check_peers_alive()  # host-side liveness first: a rank that left is reported, not waited for
+            if payload is None and config.sync_by_posting() and self.transport.supports_posting(world):
+                # No host collective: every producer stores its cumulative count on each owner, and the owner's
+                # wait collects the postings of this synchronisation before it waits for the arrivals themselves.
+                self.transport.post_counts(self.posted, world, me, self.epoch,
+                                           [self.dispatched.get(r, 0) for r in world])
+                self.transport.wait_posted(self.posted, self.counter, len(world), self.epoch)
+                gathered = [(None, None)] * len(world)
+            else:
+                gathered = control.all_gather_object((dict(self.dispatched), payload))
+                everyone = [d for d, _ in gathered]
+                self.expected_total = sum(d.get(me, 0) for d in everyone)
+                self.transport.wait_arrivals(self.counter, self.expected_total)
             if self.deterministic:
                 for key, slots in self.slots.items():  # fixed order: rank 0 first
                     acc = self.accumulations[key]

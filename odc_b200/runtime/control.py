@@ -22,6 +22,7 @@ from .. import config
 _control_pg: Optional[dist.ProcessGroup] = None
 _comm_stream = None
 _local_world_pg = None
+_heartbeat = None
 
 
 def world_size() -> int:
@@ -38,18 +39,47 @@ def control_group() -> Optional[dist.ProcessGroup]:
     if not dist.is_initialized() or dist.get_world_size() == 1:
         return None
     if _control_pg is None:
-        if dist.get_backend() == "gloo":
-            _control_pg = dist.group.WORLD
-        else:
-            _control_pg = dist.new_group(backend="gloo")
+        # A group of its own even when WORLD is gloo already: the budget of every bounded wait also bounds the host
+        # collectives, so a rank that never joins ends the exchange with an error instead of blocking its peers for
+        # the backend's default (half an hour).  Heap bootstrap and allocation run on it too, hence the floor.
+        from datetime import timedelta
+        _control_pg = dist.new_group(backend="gloo",
+                                     timeout=timedelta(milliseconds=max(1000, config.wait_timeout_ms())))
     return _control_pg
 
 
 def reset_control_group() -> None:
-    global _control_pg, _local_world_pg, _comm_stream
+    global _control_pg, _local_world_pg, _comm_stream, _heartbeat
     _control_pg = None
     _local_world_pg = None
     _comm_stream = None
+    if _heartbeat is not None:
+        _heartbeat.stop_background()
+    _heartbeat = None
+
+
+def heartbeat():
+    """The job's host-side liveness channel (``ODC_HEARTBEAT_S`` > 0), created on first use; else None.
+
+    It publishes from a background thread once a second, so a rank counts as alive while its process runs, however
+    long its microbatches take; a rank that exits between steps calls ``mark_leaving`` or simply stops publishing.
+    """
+    global _heartbeat
+    if config.heartbeat_s() <= 0 or not dist.is_initialized() or dist.get_world_size() == 1:
+        return None
+    if _heartbeat is None:
+        from torch.distributed.distributed_c10d import _get_default_store
+        from .status import Heartbeat
+        _heartbeat = Heartbeat(_get_default_store(), dist.get_rank(), dist.get_world_size())
+        _heartbeat.start_background(1.0)
+    return _heartbeat
+
+
+def check_peers_alive() -> None:
+    """Raise ``PeerFailure`` if a peer stopped publishing heartbeats (no-op unless ``ODC_HEARTBEAT_S`` is set)."""
+    hb = heartbeat()
+    if hb is not None:
+        hb.assert_alive(config.heartbeat_s())
 
 
 def all_gather_object(obj: Any) -> List[Any]:
@@ -57,7 +87,11 @@ def all_gather_object(obj: Any) -> List[Any]:
     if pg is None:
         return [obj]
     out: List[Any] = [None] * dist.get_world_size()
-    dist.all_gather_object(out, obj, group=pg)
+    try:
+        dist.all_gather_object(out, obj, group=pg)
+    except (RuntimeError, dist.DistBackendError) as e:  # a peer never joined or went away: the group's timeout ran out
+        from .status import PeerFailure
+        raise PeerFailure(f"rank {rank()}: host exchange failed, a peer did not take part: {e}") from e
     return out
 
 

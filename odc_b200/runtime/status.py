@@ -63,11 +63,41 @@ class Heartbeat:
 
     def __init__(self, store, rank: int, world: int, prefix: str = "odc_hb"):
         self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
+        self._thread = None
+        self._stop = None
+        self._step = 0
 
-    def beat(self, step: int) -> None:
-        self.store.set(f"{self.prefix}/{self.rank}", f"{step}:{time.time():.3f}")
+    def beat(self, step: Optional[int] = None) -> None:
+        if step is not None:
+            self._step = step
+        self.store.set(f"{self.prefix}/{self.rank}", f"{self._step}:{time.time():.3f}")
+
+    def start_background(self, interval_s: float = 1.0) -> None:
+        """Publish from a daemon thread every ``interval_s`` seconds until ``stop_background`` (or process exit)."""
+        import threading
+        if self._thread is not None:
+            return
+        self._stop = threading.Event()
+        self.beat()
+
+        def run():
+            while not self._stop.wait(interval_s):
+                try:
+                    self.beat()
+                except Exception:
+                    return  # the store went away with the job
+
+        self._thread = threading.Thread(target=run, name="odc-heartbeat", daemon=True)
+        self._thread.start()
+
+    def stop_background(self) -> None:
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2.0)
+            self._thread = None
 
     def mark_leaving(self) -> None:
+        self.stop_background()  # or the publishing thread would overwrite the farewell
         self.store.set(f"{self.prefix}/{self.rank}", "gone:0")
 
     def read(self) -> Dict[int, Optional[tuple]]:
@@ -84,19 +114,14 @@ class Heartbeat:
                 out[r] = None
         return out
 
-    def dead_peers(self, max_age_s: float, min_step: Optional[int] = None) -> List[int]:
+    def dead_peers(self, max_age_s: float) -> List[int]:
+        """Peers that never published, said they were leaving, or whose last beat is older than ``max_age_s``."""
         now = time.time()
         dead = []
         for r, v in self.read().items():
             if r == self.rank:
                 continue
-            if v is None:
-                dead.append(r)
-            elif v[0] == "gone":
-                dead.append(r)
-            elif now - v[1] > max_age_s:
-                dead.append(r)
-            elif min_step is not None and int(v[0]) < min_step and now - v[1] > max_age_s:
+            if v is None or v[0] == "gone" or now - v[1] > max_age_s:
                 dead.append(r)
         return dead
 

@@ -53,6 +53,20 @@ class Transport:
         """
         return False
 
+    # -- one-sided exchange of dispatch counts (``sync`` without a host collective) --------------------------------
+    def supports_posting(self, ranks: Sequence[int]) -> bool:
+        """True when this transport can store a word directly on every one of ``ranks``."""
+        return False
+
+    def post_counts(self, slots_local: torch.Tensor, ranks: Sequence[int], my_slot: int, epoch: int,
+                    counts: Sequence[int]) -> None:
+        """Store ``(epoch << 32) | counts[i]`` in slot ``my_slot`` of buffer ``slots_local`` on ``ranks[i]``."""
+        raise NotImplementedError
+
+    def wait_posted(self, slots_local: torch.Tensor, counter_local: torch.Tensor, nprod: int, epoch: int) -> None:
+        """Collect one posting of ``epoch`` from each of ``nprod`` producers, then wait for that many arrivals."""
+        raise NotImplementedError
+
 
 class HostShmTransport(Transport):
     def __init__(self, registry: SymmBufferRegistry):
@@ -109,6 +123,28 @@ class HostShmTransport(Transport):
                     f"arrived within {config.wait_timeout_ms()} ms")
             time.sleep(0.0002)
 
+    def supports_posting(self, ranks):
+        return all(self.heap.is_local(r) for r in ranks)
+
+    def post_counts(self, slots_local, ranks, my_slot, epoch, counts):
+        slots = self.registry.get_peer_tensors(slots_local)
+        for r, c in zip(ranks, counts):
+            with self.heap.owner_lock(r):
+                slots[r][my_slot] = (int(epoch) << 32) | int(c)
+
+    def wait_posted(self, slots_local, counter_local, nprod, epoch):
+        deadline = time.monotonic() + config.wait_timeout_ms() / 1e3
+        while True:
+            words = [int(v) for v in slots_local[:nprod]]
+            if all((w >> 32) >= epoch for w in words):
+                break
+            if time.monotonic() > deadline:
+                late = [p for p, w in enumerate(words) if (w >> 32) < epoch]
+                raise OdcTimeoutError(f"rank {self.heap.rank}: producers {late} did not post their dispatch counts "
+                                      f"for synchronisation {epoch} within {config.wait_timeout_ms()} ms")
+            time.sleep(0.0002)
+        self.wait_arrivals(counter_local, sum(w & 0xFFFFFFFF for w in words))
+
 
 class NvlinkP2PTransport(Transport):
     def __init__(self, registry: SymmBufferRegistry):
@@ -117,22 +153,26 @@ class NvlinkP2PTransport(Transport):
         self.ext = _ext.load()
         self.registry = registry
         self.heap: SymmetricHeap = registry.heap
-        # [0] error code, [1] detail, [2] observed value, [3] spare — written by kernels that give up
-        self.status = torch.zeros(4, dtype=torch.int32, device=self.heap.device)
+        # [0] error code, [1] detail, [2] observed value, [3] spare — written by kernels that give up.  ONE word per
+        # device, shared with the GEMM, attention and fused compute+communication kernels, so that the copy `check`
+        # makes at every synchronisation point also sees a pipeline wait that ran out inside one of those.
+        with torch.cuda.device(self.heap.device):
+            self.status = self.ext.kernel_status()
         self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self._expected = None
         self.launches = 0
 
     def gather(self, out2d, src_local, ranks, my_index):
         table = self.registry.peer_ptr_table(src_local, ranks)
-        self.ext.gather(out2d, table, src_local.numel(), src_local.dtype, my_index, config.debug_bounds(),
-                        self.status)
+        self.ext.gather(out2d, table, out2d.shape[1], src_local.dtype, my_index, config.debug_bounds(),
+                        self.status, src_local.numel())
         self.launches += 1
 
     def scatter_add(self, inp2d, acc_local, counter_local, ranks, my_index, scale=1.0):
         acc_table = self.registry.peer_ptr_table(acc_local, ranks)
         ctr_table = self.registry.peer_ptr_table(counter_local, ranks)
-        self.ext.scatter_accumulate(inp2d, acc_table, ctr_table, acc_local.numel(), acc_local.dtype,
-                                    my_index, float(scale), config.debug_bounds(), self.status)
+        self.ext.scatter_accumulate(inp2d, acc_table, ctr_table, inp2d.shape[1], acc_local.dtype,
+                                    my_index, float(scale), config.debug_bounds(), self.status, acc_local.numel())
         self.launches += 1
 
     def scatter_add_segments(self, grads, chunk_numels, dst_offsets, acc_local, counter_local, ranks, my_index,
@@ -141,7 +181,8 @@ class NvlinkP2PTransport(Transport):
         ctr_table = self.registry.peer_ptr_table(counter_local, ranks)
         done = self.ext.scatter_accumulate_segments(list(grads), [int(c) for c in chunk_numels],
                                                     [int(o) for o in dst_offsets], acc_table, ctr_table,
-                                                    acc_local.dtype, my_index, float(scale))
+                                                    acc_local.dtype, my_index, float(scale), config.debug_bounds(),
+                                                    self.status, acc_local.numel())
         if done:
             self.launches += 1
         return bool(done)
@@ -151,8 +192,28 @@ class NvlinkP2PTransport(Transport):
         self.launches += 1
         self.check()
 
+    def supports_posting(self, ranks):
+        return len(ranks) <= 72 and all(self.heap.is_local(r) for r in ranks)
+
+    def post_counts(self, slots_local, ranks, my_slot, epoch, counts):
+        addrs = [a + 8 * my_slot for a in self.registry.peer_ptrs(slots_local, ranks)]
+        self.ext.post_counts(addrs, [int(c) for c in counts], int(epoch), self.heap.device.index or 0)
+        self.launches += 1
+
+    def wait_posted(self, slots_local, counter_local, nprod, epoch):
+        if self._expected is None:
+            self._expected = torch.zeros(1, dtype=torch.int64, device=self.heap.device)
+        self.ext.wait_posted(slots_local, int(nprod), int(epoch), counter_local, config.wait_timeout_ms(), self.status,
+                             self._expected)
+        self.launches += 1
+        self.check()
+
     def check(self) -> None:
-        """Read the device status word (one small D2H copy + stream sync) and raise if a kernel gave up."""
+        """Read the device status word (one small D2H copy + stream sync) and raise if a kernel gave up.
+
+        The word is shared by every kernel of this package on the device, so a GEMM / attention pipeline wait that
+        ran out since the last check surfaces here too, at the latest at the next synchronisation point.
+        """
         self._status_host.copy_(self.status, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         code = int(self._status_host[0])
@@ -179,9 +240,12 @@ class InterNodeTransport(Transport):
 
     def _pieces(self, numel: int, n_peers: int):
         """``(start, length)`` pieces so that one round of requests stages at most ``ODC_MAX_BUFFER_SIZE`` elements."""
-        cap = config.max_buffer_elems()
-        step = numel if cap <= 0 else max(64, cap // max(1, n_peers) // 64 * 64)
-        return [(s0, min(step, numel - s0)) for s0 in range(0, numel, step)] or [(0, 0)]
+        from ..primitives.splitter import BufferSplitter
+        splitter = BufferSplitter()
+        if splitter.enabled and splitter.max_buffer_size % max(1, n_peers) != 0:
+            # the staging cap need not divide by this group's size: use the largest multiple that fits
+            splitter = BufferSplitter(max(n_peers, splitter.max_buffer_size // n_peers * n_peers))
+        return list(splitter.segments(numel, max(1, n_peers))) or [(0, 0)]
 
     def gather(self, out2d, src_local, ranks, my_index):
         off = self.registry.offset_of(src_local)

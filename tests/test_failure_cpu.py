@@ -41,6 +41,78 @@ def test_wait_reports_a_missing_contribution():
     assert all(res)  # every owner was told to expect one more arrival than it received
 
 
+def _never_posts(rank, world):
+    """One-sided count exchange: rank 1 never reaches `sync`, so its posting is missing on every owner."""
+    import odc_b200 as odc
+    from odc_b200.runtime.status import OdcTimeoutError
+    odc.init_nvshmem("cpu", 32 << 20)
+    red = odc.ReductionService(accumulation_dtype=torch.float32)
+    red.register("g", 64, torch.float32)
+    red.scatter_accumulate("g", torch.ones(world * 64))
+    if rank == 1:
+        return "absent"          # between steps, nothing in flight; it simply does not take part
+    with pytest.raises(OdcTimeoutError, match="did not post"):
+        red.sync()
+    return "reported"
+
+
+def test_sync_reports_a_producer_that_never_posts():
+    assert run_ranks(_never_posts, 2, env={"ODC_WAIT_TIMEOUT_MS": "400"}) == ["reported", "absent"]
+
+
+def _never_joins_host_exchange(rank, world):
+    """`sync` with a payload uses one host exchange; its group carries the wait budget, so an absent rank is an error."""
+    import time
+
+    import odc_b200 as odc
+    from odc_b200.runtime.status import PeerFailure
+    odc.init_nvshmem("cpu", 32 << 20)
+    red = odc.ReductionService(accumulation_dtype=torch.float32)
+    red.register("g", 64, torch.float32)
+    if rank == 1:
+        time.sleep(3.0)          # stays alive (so the store stays up) but never calls sync
+        return "absent"
+    t0 = time.monotonic()
+    with pytest.raises(PeerFailure, match="did not take part"):
+        red.sync(payload={"anything": 1})
+    assert time.monotonic() - t0 < 30
+    return "reported"
+
+
+def test_host_exchange_is_bounded_by_the_wait_budget():
+    assert run_ranks(_never_joins_host_exchange, 2, env={"ODC_WAIT_TIMEOUT_MS": "1000"}) == ["reported", "absent"]
+
+
+def _left_between_steps(rank, world):
+    """With ODC_HEARTBEAT_S set, `sync` learns on the host that a peer left, before it waits for anything."""
+    import time
+
+    import odc_b200 as odc
+    from odc_b200.runtime import control
+    from odc_b200.runtime.status import PeerFailure
+    odc.init_nvshmem("cpu", 32 << 20)
+    red = odc.ReductionService(accumulation_dtype=torch.float32)
+    red.register("g", 64, torch.float32)
+    red.scatter_accumulate("g", torch.ones(world * 64))
+    red.sync()                   # a normal minibatch first: everyone is alive
+    control.host_barrier()
+    if rank == 1:
+        control.heartbeat().mark_leaving()
+        time.sleep(1.5)
+        return "left"
+    time.sleep(0.5)
+    t0 = time.monotonic()
+    with pytest.raises(PeerFailure, match="stopped publishing"):
+        red.sync()
+    assert time.monotonic() - t0 < 1.0   # no wait budget was spent
+    return "detected"
+
+
+def test_sync_checks_heartbeats_first():
+    res = run_ranks(_left_between_steps, 2, env={"ODC_HEARTBEAT_S": "30", "ODC_WAIT_TIMEOUT_MS": "20000"})
+    assert res == ["detected", "left"]
+
+
 def _heartbeat(rank, world):
     import time
 

@@ -388,3 +388,88 @@ def test_scatter_accumulate_segments_emulated_ranks(ext, world, dtype):
     assert not ext.scatter_accumulate_segments([grads[0]] * 33, [chunks[0]] * 33, [0] * 33, _table(accs), _table(ctrs),
                                                torch.float32, 0, 1.0)
     assert not ext.scatter_accumulate_segments(grads, chunks, offsets, _table(accs), _table(ctrs), torch.bfloat16, 0, 1.0)
+
+
+# ------------------------------------------------------------------------------------ debug bounds checks
+def test_debug_bounds_refuse_a_short_declared_region(ext):
+    """ODC_DEBUG_BOUNDS launches: a row longer than the DECLARED region is refused on valid memory.
+
+    Every buffer here is fully allocated, only the declared length is made too short, so nothing out of range
+    is ever touched; a refused launch leaves the destination untouched and reports through the status word.
+    """
+    world, n = 2, 4096
+    from odc_b200.runtime.status import ERR_BOUNDS, ERR_PEER_INDEX
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    # gather
+    shards = [torch.ones(n, device="cuda").bfloat16() * (r + 1) for r in range(world)]
+    out = torch.zeros(world, n, dtype=torch.bfloat16, device="cuda")
+    ext.gather(out, _table(shards), n, torch.bfloat16, 0, True, status, n - 8)
+    torch.cuda.synchronize()
+    assert int(status[0]) == ERR_BOUNDS and float(out.abs().sum()) == 0
+    status.zero_()
+    ext.gather(out, _table(shards), n, torch.bfloat16, 5, True, status, n)      # start index outside the group
+    torch.cuda.synchronize()
+    assert int(status[0]) == ERR_PEER_INDEX and float(out.abs().sum()) == 0
+    status.zero_()
+    ext.gather(out, _table(shards), n, torch.bfloat16, 1, True, status, n)      # exact fit passes
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0 and torch.equal(out, torch.stack(shards))
+    # scatter_accumulate (fp32 and bf16 sources, fp32 and bf16 accumulators)
+    for in_dtype, acc_dtype in [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                (torch.bfloat16, torch.bfloat16)]:
+        accs = [torch.zeros(n, dtype=acc_dtype, device="cuda") for _ in range(world)]
+        ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+        x = torch.ones(world, n, device="cuda").to(in_dtype)
+        status.zero_()
+        ext.scatter_accumulate(x, _table(accs), _table(ctrs), n, acc_dtype, 0, 1.0, True, status, n - 4)
+        torch.cuda.synchronize()
+        assert int(status[0]) == ERR_BOUNDS
+        assert all(float(a.float().abs().sum()) == 0 for a in accs)
+        assert all(int(c[0]) == 1 for c in ctrs)   # the owners are not left waiting for the refused contribution
+        status.zero_()
+        ext.scatter_accumulate(x, _table(accs), _table(ctrs), n, acc_dtype, 0, 1.0, True, status, n)
+        torch.cuda.synchronize()
+        assert int(status[0]) == 0 and all(float(a.float().sum()) == n for a in accs)
+    # segmented scatter: the second tensor would end past the declared accumulator length
+    accs = [torch.zeros(3 * n, device="cuda") for _ in range(world)]
+    ctrs = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(world)]
+    grads = [torch.ones(world * n, device="cuda"), torch.ones(world * 2 * n, device="cuda")]
+    status.zero_()
+    assert ext.scatter_accumulate_segments(grads, [n, 2 * n], [0, n], _table(accs), _table(ctrs), torch.float32, 0, 1.0,
+                                           True, status, 3 * n - 4)
+    torch.cuda.synchronize()
+    assert int(status[0]) == ERR_BOUNDS and all(float(a.sum()) == 0 for a in accs)
+    status.zero_()
+    assert ext.scatter_accumulate_segments(grads, [n, 2 * n], [0, n], _table(accs), _table(ctrs), torch.float32, 0, 1.0,
+                                           True, status, 3 * n)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0 and all(float(a.sum()) == 3 * n for a in accs)
+
+
+def test_posted_counts_and_bounded_wait(ext):
+    """One-sided dispatch-count exchange, with the producers emulated by separate posts into one owner's slots."""
+    nprod = 5
+    slots = torch.zeros(8, dtype=torch.int64, device="cuda")
+    ctr = torch.zeros(8, dtype=torch.int64, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    expected = torch.zeros(1, dtype=torch.int64, device="cuda")
+    counts = [3, 0, 7, 1, 2]
+    for p, c in enumerate(counts):
+        ext.post_counts([slots.data_ptr() + 8 * p], [c], 1, 0)
+    ctr[0] = sum(counts)
+    ext.wait_posted(slots, nprod, 1, ctr, 500, status, expected)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0 and int(expected[0]) == sum(counts)
+    assert [int(v) >> 32 for v in slots[:nprod]] == [1] * nprod
+    # a synchronisation that one producer never posts for: the wait runs out and names the producer
+    for p, c in enumerate(counts[:-1]):
+        ext.post_counts([slots.data_ptr() + 8 * p], [c + 1], 2, 0)
+    ext.wait_posted(slots, nprod, 2, ctr, 50, status, expected)
+    torch.cuda.synchronize()
+    assert status[:3].tolist() == [1, 1000 + nprod - 1, 1]
+    # all postings there, but fewer arrivals than announced: the arrival wait runs out instead
+    status.zero_()
+    ext.post_counts([slots.data_ptr() + 8 * (nprod - 1)], [counts[-1] + 1], 2, 0)
+    ext.wait_posted(slots, nprod, 2, ctr, 50, status, expected)
+    torch.cuda.synchronize()
+    assert status[:3].tolist() == [1, 0, sum(counts)] and int(expected[0]) == sum(counts) + nprod

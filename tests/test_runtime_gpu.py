@@ -124,3 +124,32 @@ def test_deterministic_reduction_mode_gpu(monkeypatch):
         red.stop()
     finally:
         odc.finalize_distributed()
+
+
+def test_pipeline_status_surfaces_at_the_next_sync(single_rank_pg):
+    """A GEMM / attention pipeline wait that ran out is recorded in the device's status word; the communication
+    service reads that same word at every synchronisation point and raises.  The word is pre-set here by hand:
+    nothing on the GPU is made to stall."""
+    import odc_b200 as odc
+    from odc_b200 import _ext
+    from odc_b200.runtime.status import ERR_PIPELINE_TIMEOUT, OdcTimeoutError
+    torch.cuda.set_device(0)
+    odc.init_nvshmem(torch.device("cuda", 0), 1 << 30)
+    try:
+        red = odc.ReductionService(accumulation_dtype=torch.float32)
+        x = torch.ones(1 << 12, device="cuda")
+        red.scatter_accumulate("k", x)
+        red.sync()                                   # clean
+        word = _ext.load().kernel_status()
+        assert word.data_ptr() == red.transport.status.data_ptr()
+        word.copy_(torch.tensor([ERR_PIPELINE_TIMEOUT, 3, 17, 0], dtype=torch.int32))
+        red.scatter_accumulate("k", x)
+        with pytest.raises(OdcTimeoutError, match="pipeline"):
+            red.sync()
+        assert int(word[0]) == 0                     # reported once, then cleared
+        red.scatter_accumulate("k", x)
+        red.sync()
+        assert float(red.get_accumulation("k").sum()) == 3 * (1 << 12)
+        red.stop()
+    finally:
+        odc.finalize_distributed()
