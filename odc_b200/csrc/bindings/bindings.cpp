@@ -410,7 +410,7 @@ bool gemm_wgrad_scatter_tma(Tensor dy, Tensor x, std::vector<int64_t> acc_addrs,
 }
 
 Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<Tensor> bias, int64_t rows_per_rank,
-                   int start_rank) {
+                   int start_rank, c10::optional<Tensor> residual) {
   c10::cuda::CUDAGuard g(x.device());
   odc::bind_device(x.get_device());
   TORCH_CHECK(x.dim() == 2 && w_local.dim() == 2 && x.size(1) == w_local.size(1), "gemm_gather: x [M,K], w_local [N,K]");
@@ -424,11 +424,19 @@ Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<T
     TORCH_CHECK(bias->scalar_type() == at::kBFloat16 && bias->numel() == N, "gemm_gather: bias bf16 [N]");
     bias_ptr = bias->data_ptr();
   }
+  const void* res_ptr = nullptr;
+  long long ldr = 0;
+  if (residual.has_value()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == M &&
+                    residual->size(1) == N && residual->stride(1) == 1, "gemm_gather: residual bf16 [M,N]");
+    res_ptr = residual->data_ptr();
+    ldr = residual->stride(0);
+  }
   check(odc::gemm_gather_nt(x.data_ptr(), reinterpret_cast<const long long*>(shard_table.data_ptr<int64_t>()),
                             w_local.data_ptr(), y.data_ptr(), bias_ptr, M, N, K, x.stride(0), y.stride(0),
                             static_cast<int>(rows_per_rank), static_cast<int>(shard_table.numel()), start_rank,
                             reinterpret_cast<unsigned int*>(flags.data_ptr<int>()),
-                            gemm_status(x.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+                            gemm_status(x.get_device()).data_ptr<int>(), sm_count(), cur_stream(), res_ptr, ldr),
         "gemm_gather");
   return y;
 }
@@ -586,7 +594,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grid_barrier_test", &grid_barrier_test);
   m.def("gemm_wgrad_scatter", &gemm_wgrad_scatter);
   m.def("gemm_wgrad_scatter_tma", &gemm_wgrad_scatter_tma);
-  m.def("gemm_gather", &gemm_gather);
+  m.def("gemm_gather", &gemm_gather, py::arg("x"), py::arg("shard_table"), py::arg("w_local"), py::arg("bias"),
+        py::arg("rows_per_rank"), py::arg("start_rank"), py::arg("residual") = py::none());
   m.def("gemm_gather_dgrad", &gemm_gather_dgrad);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);

@@ -112,7 +112,7 @@ cudaError_t gemm_wgrad_scatter_tma(const void* dy, const void* x, int tokens, in
 cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_local, void* y, const void* bias,
                            int M, int N, int K, long long ldx, long long ldy, int rows_per_rank, int nranks,
                            int start_rank, unsigned int* panel_flags, int* status, int sm_count,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
 // dX[M, k_in] = dY[M, n_out] W[n_out, k_in] with W row-sharded as above: the gathered rows are the reduction
 // dimension, so the k-loop of every output tile follows the arrival of the 256-row groups (first tile of a CTA)
 // and later tiles find the whole weight in w_local.  group_flags needs ceil(n_out / 256) words.

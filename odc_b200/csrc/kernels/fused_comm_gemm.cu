@@ -106,7 +106,7 @@ cudaError_t gemm_wgrad_scatter_tma(const void* dy, const void* x, int tokens, in
 cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_local, void* y, const void* bias,
                            int M, int N, int K, long long ldx, long long ldy, int rows_per_rank, int nranks,
                            int start_rank, unsigned int* panel_flags, int* status, int sm_count,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const void* residual, long long ldr) {
   if (M == 0 || N == 0 || nranks == 0) return cudaSuccess;
   if (K == 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(y)) & 15)
@@ -138,6 +138,11 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   p.panel_flags = panel_flags;
   p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.start_rank = start_rank;
   p.w_rows = N; p.w_cols = K;
+  if (residual != nullptr) {
+    if ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15)) return cudaErrorInvalidValue;
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.ldr = ldr;
+  }
   cudaError_t e = cudaMemsetAsync(panel_flags, 0, sizeof(unsigned int) * p.tiles_n, stream);
   if (e != cudaSuccess) return e;
   // every CTA also fetches, so use the whole machine even when there are few tiles

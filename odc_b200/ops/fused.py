@@ -49,29 +49,37 @@ def _gather_weight(reg: SymmBufferRegistry, weight_shard: torch.Tensor, ranks, o
 
 
 def gather_linear(x: torch.Tensor, weight_shard: torch.Tensor, out_features: int,
-                  pg: Optional[dist.ProcessGroup] = None, bias: Optional[torch.Tensor] = None
-                  ) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``weight_shard``: this rank's ``[rows_per_rank, K]`` rows of ``W`` (a symmetric-heap tensor)."""
+                  pg: Optional[dist.ProcessGroup] = None, bias: Optional[torch.Tensor] = None,
+                  residual: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``weight_shard``: this rank's ``[rows_per_rank, K]`` rows of ``W`` (a symmetric-heap tensor).
+
+    ``bias`` and ``residual`` (``[..., out_features]``) are added in the kernel's epilogue."""
     reg = SymmBufferRegistry.get_instance()
     ranks = control.group_ranks(pg)
     me = control.rank()
     rows_per, K = weight_shard.shape
     x2 = x.reshape(-1, x.shape[-1])
+    res2 = None if residual is None else residual.reshape(-1, out_features)
     if _spans_nodes(reg, ranks):
         from . import gemm
         w_full = _gather_weight(reg, weight_shard, ranks, out_features)
-        y = gemm(x2, w_full, "nt", bias=bias) if x2.is_cuda else torch.nn.functional.linear(x2, w_full.to(x2.dtype), bias)
+        if x2.is_cuda:
+            y = gemm(x2, w_full, "nt", bias=bias, residual=res2)
+        else:
+            y = torch.nn.functional.linear(x2, w_full.to(x2.dtype), bias)
+            y = y if res2 is None else y + res2
     elif x2.is_cuda:
         from .. import _ext
         from . import _count
         table = reg.peer_ptr_table(weight_shard, ranks)
         w_full = torch.empty(out_features, K, dtype=weight_shard.dtype, device=x.device)
-        y = _ext.load().gemm_gather(x2, table, w_full, bias, rows_per, ranks.index(me) if me in ranks else 0)
+        y = _ext.load().gemm_gather(x2, table, w_full, bias, rows_per, ranks.index(me) if me in ranks else 0, res2)
         _count()
     else:
         peers = reg.get_peer_tensors(weight_shard)
         w_full = torch.cat([peers[r] for r in ranks], dim=0)[:out_features].clone()
         y = torch.nn.functional.linear(x2, w_full.to(x2.dtype), bias)
+        y = y if res2 is None else y + res2
     return y.view(*x.shape[:-1], out_features), w_full
 
 

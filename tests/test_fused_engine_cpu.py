@@ -1,0 +1,104 @@
+"""The fused-kernel decoder engine (``parallel.FusedDecoderLM``) against stock FSDP2 on CPU ranks (gloo)."""
+import pytest
+import torch
+
+from _mp import assert_mostly_close, run_pair
+
+
+def _make_batches(rank, step, n_micro, vocab=1024):
+    from odc_b200.data import LengthSpec, make_minibatch
+    return make_minibatch(rank, step, vocab, LengthSpec("uniform", lo=16, hi=128), n_micro, 128, seed=7)
+
+
+def _train(rank, world, mode, steps, uneven, variant):
+    import torch.distributed as dist
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.models import DecoderLM, get_config
+    from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
+
+    over = {}
+    if "bias_tied" in variant:
+        over.update(qkv_bias=True, tie_embeddings=True)
+    if "ac" in variant:
+        over.update(activation_checkpointing=True)
+    cfg = get_config("tiny", **over)
+    torch.manual_seed(0)
+    if mode == "stock":
+        model = DecoderLM(cfg)
+        model.reset_parameters(seed=0)
+        if cfg.qkv_bias:   # zero biases would hide a wrong bias gradient
+            with torch.no_grad():
+                for layer in model.layers:
+                    layer.attn.bqkv.normal_(0, 0.02, generator=torch.Generator().manual_seed(5))
+        for layer in model.layers:
+            fully_shard(layer)
+        fully_shard(model)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    else:
+        odc.init_nvshmem("cpu", 256 << 20)
+        src = DecoderLM(cfg)
+        src.reset_parameters(seed=0)
+        if cfg.qkv_bias:
+            with torch.no_grad():
+                for layer in src.layers:
+                    layer.attn.bqkv.normal_(0, 0.02, generator=torch.Generator().manual_seed(5))
+        model = FusedDecoderLM(cfg, device="cpu", source=src, keep_weight="keep" in variant)
+        opt = FusedOptimizer(model, lr=1e-3)
+    losses = []
+    for step in range(steps):
+        if mode == "odc":
+            model.start_minibatch()
+        mine = (2 + rank) if uneven else 2
+        n_micro = mine
+        if uneven and mode == "stock":
+            n_micro = 2 + world - 1      # lock-step FSDP must run the same count: pad with zero-weight work
+        total = torch.zeros(())
+        for i in range(n_micro):
+            real = i < mine
+            mb = _make_batches(rank, step, mine)[i if real else 0]
+            if mode == "odc" and "defer" in variant:
+                model.set_requires_gradient_sync(i == n_micro - 1)
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"],
+                         labels=mb["labels"], loss_scale=mb["loss_scale"])
+            if not real:
+                loss = loss * 0.0
+            loss.backward()
+            total += loss.detach()
+        if mode == "odc":
+            model.finish_minibatch()
+            if "clip" in variant:
+                opt.clip_grad_norm_(0.5)
+        elif "clip" in variant:
+            torch.nn.utils.clip_grad_norm_(model.parameters(), 0.5)
+        opt.step()
+        opt.zero_grad()
+        dist.all_reduce(total)
+        losses.append(float(total))
+    if mode == "stock":
+        full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    else:
+        full = model.full_state_dict()
+        if "roundtrip" in variant:   # whole-model state out and back in: nothing changes
+            osd = opt.full_state_dict()
+            model.load_full_state_dict(full)
+            opt.load_full_state_dict(osd)
+            again = model.full_state_dict()
+            assert all(torch.equal(full[k], again[k]) for k in full)
+            assert torch.equal(opt.full_state_dict()["exp_avg"]["norm.weight"], osd["exp_avg"]["norm.weight"])
+        model.stop()
+    return losses, full
+
+
+@pytest.mark.parametrize("uneven,variant", [(False, "plain,roundtrip"), (True, "defer,clip"), (False, "bias_tied,keep,ac"),
+                                            (True, "bias_tied,defer")])
+def test_fused_engine_matches_stock_fsdp2(uneven, variant):
+    world = 2
+    a, b = run_pair(_train, world, (3, uneven, variant))
+    la, lb = a[0][0], b[0][0]
+    assert la == pytest.approx(lb, rel=1e-4), (la, lb)
+    assert set(a[0][1]) == set(b[0][1])
+    for k in a[0][1]:
+        assert a[0][1][k].shape == b[0][1][k].shape, k
+        assert_mostly_close(b[0][1][k], a[0][1][k], rtol=5e-3, atol=2e-4)

@@ -281,3 +281,194 @@ def test_ipc_handle_across_processes():
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     _launch(IPC, 2, timeout=300, env={"PYTORCH_NO_CUDA_MEMORY_CACHING": "1"})
+
+
+# ------------------------------------------------------------------------------------------------------------
+# FSDP2 variants on real GPUs (4 ranks): HSDP 2x2, a secondary partition smaller than the shard group, and the
+# fused optimizer against torch.optim.AdamW.  OPTS is replaced per test.
+# ------------------------------------------------------------------------------------------------------------
+FSDP2_VARIANT = """
+from torch.distributed.device_mesh import init_device_mesh
+from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+from odc_b200.fsdp import fsdp2
+from odc_b200.models import DecoderLM, get_config
+from odc_b200.data import LengthSpec, make_minibatch, to_device
+OPTS = dict(__OPTS__)
+
+def run(use_odc, fused_opt=False):
+    cfg = get_config("tiny", hidden_size=512, intermediate_size=1536, num_heads=8, num_kv_heads=2, vocab_size=4096)
+    with torch.device(dev):
+        model = DecoderLM(cfg)
+    model.reset_parameters(seed=0)
+    hpz = OPTS.get("hpz", 0) if use_odc else 0
+    if use_odc:
+        fsdp2.patch_fsdp2(enable_hpz=bool(hpz))
+    kw = dict(mp_policy=MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32))
+    if OPTS.get("mesh"):
+        kw["mesh"] = init_device_mesh("cuda", OPTS["mesh"], mesh_dim_names=("rep", "shard"))
+    if hpz:
+        kw["reshard_after_forward"] = hpz
+    for layer in model.layers:
+        fully_shard(layer, **kw)
+    fully_shard(model, **kw)
+    if use_odc:
+        for m in list(model.layers) + [model]:
+            fsdp2.patch_lazy_init(m)
+    opt = fsdp2.FusedAdamW(model, lr=1e-3) if fused_opt else torch.optim.AdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for step in range(3):
+        if use_odc:
+            fsdp2.pre_minibatch_start(model)
+        tot = torch.zeros((), device=dev)
+        for i in range(2):
+            mb = to_device(make_minibatch(rank, step, cfg.vocab_size, LengthSpec("uniform", lo=32, hi=300), 2, 1024, seed=5)[i], dev)
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"], loss_scale=mb["loss_scale"])
+            loss.backward()
+            tot += loss.detach()
+        if use_odc:
+            fsdp2.pre_optimizer_step(model, materialize_grads=not fused_opt)
+        opt.step(); opt.zero_grad()
+        dist.all_reduce(tot)
+        losses.append(float(tot))
+    sd = {k: v.full_tensor().float().cpu() for k, v in model.state_dict().items()}
+    if use_odc:
+        fsdp2.unpatch_fsdp2()
+    return losses, sd
+
+odc.init_nvshmem(dev, 4 << 30)
+l_odc, sd_odc = run(True, OPTS.get("fused_opt", False))
+l_ref, sd_ref = run(False)
+for a, b in zip(l_odc, l_ref):
+    assert abs(a - b) <= 2e-2 * abs(b), (l_odc, l_ref)
+for k in sd_ref:
+    torch.testing.assert_close(sd_odc[k], sd_ref[k], rtol=5e-2, atol=5e-3)
+from odc_b200 import _ext
+assert _ext.load().kernel_status()[0].item() == 0
+odc.finalize_distributed()
+"""
+
+
+@pytest.mark.parametrize("name,opts,world", [
+    ("hsdp_2x2", "mesh=(2, 2)", 4),
+    ("hpz_2_of_4", "hpz=2", 4),
+    ("hsdp_2x2_fused_adamw", "mesh=(2, 2), fused_opt=True", 4),
+    ("fused_adamw_vs_torch_adamw", "fused_opt=True", 2),
+])
+def test_fsdp2_variants_match_stock_over_nvlink(name, opts, world):
+    if _ngpu() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _launch(FSDP2_VARIANT.replace("__OPTS__", opts), world, timeout=600)
+
+
+FSDP1_UNEVEN = FSDP1.replace("for i in range(2):", "for i in range(2 + (rank if use_odc else world - 1)):").replace(
+    "LengthSpec(\"uniform\", lo=32, hi=300), 2, 1024, seed=5)[i], dev)",
+    "LengthSpec(\"uniform\", lo=32, hi=300), 2 + rank, 1024, seed=5)[i if i < 2 + rank else 0], dev)").replace(
+    "            loss.backward()", "            loss = loss if i < 2 + rank else loss * 0.0\n            loss.backward()")
+
+
+def test_fsdp1_unequal_microbatch_counts_over_nvlink():
+    """Ranks run 2 and 3 microbatches; the stock run pads the shorter rank with zero-weight work."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert "2 + rank" in FSDP1_UNEVEN and "loss * 0.0" in FSDP1_UNEVEN
+    _launch(FSDP1_UNEVEN, 2, timeout=600)
+
+
+GATHER_SUBSET = """
+import random
+reg = odc.init_nvshmem(dev, 2 << 30)
+g = odc.GatherService()
+n = (1 << 18) + 8
+shard = reg.allocate_symm_buffer("w", (n,), torch.bfloat16)
+shard.copy_((torch.arange(n, device=dev) % 251 + 256 * rank).bfloat16())
+torch.cuda.synchronize(); dist.barrier()
+rng = random.Random(1234 + rank)
+for trial in range(8):
+    peers = rng.sample(range(world), rng.randint(1, world))      # any subset, in any order, with or without this rank
+    out = torch.empty(len(peers) * n, dtype=torch.bfloat16, device=dev)
+    g.gather_ranks(out, shard, peers)
+    want = torch.cat([(torch.arange(n, device=dev) % 251 + 256 * r).bfloat16() for r in peers])
+    assert torch.equal(out, want), (trial, peers)
+torch.cuda.synchronize(); dist.barrier()
+odc.finalize_distributed()
+"""
+
+
+def test_gather_from_random_peer_subsets_over_nvlink():
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(GATHER_SUBSET, min(_ngpu(), 8), timeout=300)
+
+
+FUSED_ENGINE = """
+from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+from odc_b200.models import DecoderLM, get_config
+from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
+from odc_b200.data import LengthSpec, make_minibatch, to_device
+DEFER = __DEFER__
+cfg = get_config("tiny", hidden_size=512, intermediate_size=1536, num_heads=8, num_kv_heads=2, vocab_size=4096,
+                 tie_embeddings=True)
+
+def batches(step, count):
+    return make_minibatch(rank, step, cfg.vocab_size, LengthSpec("uniform", lo=32, hi=300), count, 1024, seed=5)
+
+def run(fused):
+    mine = 2 + rank
+    if fused:
+        model = FusedDecoderLM(cfg, device=dev, seed=0)
+        opt = FusedOptimizer(model, lr=1e-3)
+    else:
+        with torch.device(dev):
+            model = DecoderLM(cfg)
+        model.reset_parameters(seed=0)
+        mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+        for layer in model.layers:
+            fully_shard(layer, mp_policy=mp)
+        fully_shard(model, mp_policy=mp)
+        opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for step in range(3):
+        if fused:
+            model.start_minibatch()
+        n_micro = mine if fused else 2 + world - 1
+        tot = torch.zeros((), device=dev)
+        for i in range(n_micro):
+            real = i < mine
+            mb = to_device(batches(step, mine)[i if real else 0], dev)
+            if fused and DEFER:
+                model.set_requires_gradient_sync(i == n_micro - 1)
+            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"], loss_scale=mb["loss_scale"])
+            if not real:
+                loss = loss * 0.0
+            loss.backward()
+            tot += loss.detach()
+        if fused:
+            model.finish_minibatch()
+        opt.step(); opt.zero_grad()
+        dist.all_reduce(tot)
+        losses.append(float(tot))
+    if fused:
+        sd = {k: v.float().cpu() for k, v in model.full_state_dict().items()}
+    else:
+        sd = {k: v.full_tensor().float().cpu() for k, v in model.state_dict().items()}
+    return losses, sd, model
+
+odc.init_nvshmem(dev, 4 << 30)
+l_f, sd_f, fm = run(True)
+l_ref, sd_ref, _ = run(False)
+for a, b in zip(l_f, l_ref):
+    assert abs(a - b) <= 2e-2 * abs(b), (l_f, l_ref)
+for k in sd_ref:
+    torch.testing.assert_close(sd_f[k], sd_ref[k], rtol=5e-2, atol=5e-3)
+from odc_b200 import _ext
+assert _ext.load().kernel_status()[0].item() == 0
+fm.stop()
+"""
+
+
+@pytest.mark.parametrize("defer", [False, True])
+def test_fused_engine_matches_stock_fsdp2_over_nvlink(defer):
+    """The decoder on the gather+GEMM / weight-gradient+scatter kernels: unequal microbatch counts, 3 optimizer steps."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    _launch(FUSED_ENGINE.replace("__DEFER__", str(defer)), 2, timeout=600)

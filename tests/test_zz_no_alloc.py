@@ -8,6 +8,7 @@ calls in a row with different data and widths, so that a result depending on wha
 call left in the shared workspace would show.
 """
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -56,13 +57,14 @@ def test_no_alloc_rmsnorm_bwd_matches_regular_entry_point():
         dx32, dw32 = _fp32_reference(dy, x, w, 1e-5)
         dx = torch.empty_like(x)           # outputs are the caller's
         dw = torch.full((cols,), float("nan"), device="cuda")
+        gc.collect()                       # nothing of the reference computation is freed between the two readings
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
         free_before, _ = torch.cuda.mem_get_info()
         rc, msg = _call(fn, dy, x, w, rstd, dx, dw, rows, cols)
         torch.cuda.synchronize()
         assert rc == 0, msg
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() <= before
         if call > 0:  # the first launch in a process may make the CUDA runtime load the library's GPU code
             free_after, _ = torch.cuda.mem_get_info()
             assert free_after >= free_before, "the device's free memory shrank across an allocation-free call"
