@@ -11,7 +11,7 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (900 nominal)
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction per GPU of an 8 x B200 node (900 nominal)
 
 
 CPU = os.environ.get("ODC_BENCH_CPU", "0") == "1"  # functional run on CPU ranks (gloo + host-shm heap)

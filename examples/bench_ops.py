@@ -53,7 +53,8 @@ def bench_gemm():
     hbm, tf, kind = peaks()
     shapes = [(8192, 8192, 8192), (16384, 3072, 2048), (16384, 2048, 2048), (16384, 16384, 2048),
               (16384, 2048, 8192), (4096, 128256, 2048), (16384, 6144, 4096), (16384, 28672, 4096)]
-    print(f"{'layout':6} {'M':>6} {'N':>6} {'K':>6} {'ours ms':>9} {'TFLOP/s':>8} {'frac':>6} {'cublas ms':>10} {'ratio':>6}")
+    print(f"{'layout':6} {'M':>6} {'N':>6} {'K':>6} {'1-CTA ms':>9} {'TFLOP/s':>8} {'frac':>6} {'pair ms':>9} {'TFLOP/s':>8} {'frac':>6} "
+          f"{'cublas ms':>10} {'cublas/pair':>11}")
     for (M, N, K) in shapes:
         for layout in ("nt", "nn", "tn"):
             A = torch.randn(M, K, device="cuda").bfloat16()
@@ -61,12 +62,15 @@ def bench_gemm():
             a = A.t().contiguous() if layout == "tn" else A
             b = B.t().contiguous() if layout == "nt" else B
             c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-            t = timed(lambda: ext.gemm(a, b, c, layout, None, False))
+            t = timed(lambda: ext.gemm(a, b, c, layout, None, False, None, 0))      # one CTA per 128 x 256 tile
+            t2 = timed(lambda: ext.gemm(a, b, c, layout, None, False, None, 1))     # CTA pair per 256 x 256 tile
             Ar = a.t() if layout == "tn" else a
             Br = b.t() if layout == "nt" else b
             tr = timed(lambda: torch.matmul(Ar, Br, out=c))
             fl = 2.0 * M * N * K / (t * 1e-3) / 1e12
-            print(f"{layout:6} {M:6d} {N:6d} {K:6d} {t:9.3f} {fl:8.1f} {fl / tf:6.2f} {tr:10.3f} {tr / t:6.2f}   (frac of {kind} {tf:.0f} TFLOP/s)")
+            fl2 = 2.0 * M * N * K / (t2 * 1e-3) / 1e12
+            print(f"{layout:6} {M:6d} {N:6d} {K:6d} {t:9.3f} {fl:8.1f} {fl / tf:6.2f} {t2:9.3f} {fl2:8.1f} {fl2 / tf:6.2f} "
+                  f"{tr:10.3f} {tr / t2:11.2f}   (frac of {kind} {tf:.0f} TFLOP/s)")
             del A, B, a, b, c
 
 

@@ -7,6 +7,7 @@ trace per rank; ``CUDA_PROFILED=1`` brackets the last minibatch with cudaProfile
         examples/llm_training/train_fsdp2.py --model_name llama3.2-1b --packing_method DynamicDiffMicro --max_token_len 16384
 """
 import os
+import time
 
 import torch
 import torch.distributed as dist
@@ -65,6 +66,7 @@ def main():
         with Timer("minibatch_time", times):
             if ODC:
                 fsdp2.pre_minibatch_start(model)
+            t_begin = time.perf_counter()
             total = torch.zeros((), device=dev)
             tokens = 0
             for mb in microbatches:
@@ -77,6 +79,9 @@ def main():
                     if not args.forward_only:
                         loss.backward()
                     total += loss.detach()
+            with Timer("_drain", times):   # this rank's own work is done here; what follows is waiting for the others
+                pass
+            times["work_time"] = times.pop("_drain") + (time.perf_counter() - t_begin)
             if not args.forward_only:
                 with Timer("sync_time", times):
                     if ODC:
@@ -91,6 +96,14 @@ def main():
         dist.all_reduce(total)
         tok = torch.tensor([tokens], device=dev)
         dist.all_reduce(tok)
+        # share of the minibatch each rank spent NOT working on its own microbatches.  Meaningful with ODC=1, where
+        # nothing inside the microbatch loop waits for a peer; under lock-step FSDP the waiting hides inside the
+        # collectives of the loop, so the figure reads near zero there and the throughput shows the cost instead.
+        work = torch.tensor([times["work_time"]], device=dev, dtype=torch.float64)
+        works = [torch.zeros_like(work) for _ in range(world)]
+        dist.all_gather(works, work)
+        span = max(float(w) for w in works)
+        times["idle_share_per_rank"] = [round(1.0 - float(w) / span, 4) for w in works]
         log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
                                  "tokens_per_s": int(tok) / times["minibatch_time"],
                                  "grad_norm": float(grad_norm) if not args.forward_only else 0.0, **times, **memory_metrics()})

@@ -19,7 +19,7 @@ OBJ = os.path.join(CSRC, "build")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-CUDA_SOURCES = ["kernels/comm.cu", "kernels/elementwise.cu", "kernels/gemm_tcgen05.cu", "kernels/attention_tcgen05.cu",
+CUDA_SOURCES = ["kernels/comm.cu", "kernels/elementwise.cu", "kernels/gemm_tcgen05.cu", "kernels/gemm_tcgen05_2cta.cu", "kernels/attention_tcgen05.cu",
                 "kernels/fused_comm_gemm.cu", "kernels/no_alloc.cu", "kernels/device_prims.cu"]
 CPP_SOURCES = ["heap/symm_heap.cpp", "kernels/tensor_map.cpp"]
 BINDING_SOURCES = ["bindings/bindings.cpp"]

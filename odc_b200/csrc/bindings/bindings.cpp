@@ -209,16 +209,22 @@ std::tuple<Tensor, Tensor> rmsnorm_fwd(Tensor x, Tensor w, double eps) {
   return {y, rstd};
 }
 
-std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) {
+std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, bool fixed_order) {
   c10::cuda::CUDAGuard g(x.device());
   odc::bind_device(x.get_device());
+  TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dy.sizes() == x.sizes(), "rmsnorm_bwd: contiguous dy, x [T,H]");
   const int rows = static_cast<int>(x.size(0)), cols = static_cast<int>(x.size(1));
   auto dx = torch::empty_like(x);
   const int grid = odc::rmsnorm_bwd_grid(rows, sm_count());
-  auto partial = torch::empty({grid, cols}, x.options().dtype(at::kFloat));
   auto dw = torch::empty({cols}, x.options().dtype(at::kFloat));
+  Tensor partial;
+  float* partial_ptr = nullptr;
+  if (fixed_order) {  // per-CTA column sums added up in a fixed order by a second pass (bitwise reproducible)
+    partial = torch::empty({grid, cols}, x.options().dtype(at::kFloat));
+    partial_ptr = partial.data_ptr<float>();
+  }
   check(odc::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
-                                partial.data_ptr<float>(), dw.data_ptr<float>(), rows, cols, grid, cur_stream()),
+                                partial_ptr, dw.data_ptr<float>(), rows, cols, grid, cur_stream()),
         "rmsnorm_bwd");
   return {dx, dw};
 }
@@ -333,7 +339,7 @@ Tensor kernel_status() {
 }
 
 void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional<Tensor> bias, bool accumulate,
-          c10::optional<Tensor> residual) {
+          c10::optional<Tensor> residual, int pair) {
   c10::cuda::CUDAGuard g(a.device());
   odc::bind_device(a.get_device());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && c.dim() == 2, "gemm: 2-D operands");
@@ -368,7 +374,8 @@ void gemm(Tensor a, Tensor b, Tensor c, const std::string& layout, c10::optional
   }
   cudaError_t e = odc::gemm_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), kind_of(c.scalar_type()), bias_ptr, M, N, K,
                                  lay, accumulate, a.stride(0), b.stride(0), c.stride(0),
-                                 gemm_status(a.get_device()).data_ptr<int>(), sm_count(), cur_stream(), res_ptr, ldr);
+                                 gemm_status(a.get_device()).data_ptr<int>(), sm_count(), cur_stream(), res_ptr, ldr,
+                                 pair);
   TORCH_CHECK(e == cudaSuccess, "gemm(", layout, ") M=", M, " N=", N, " K=", K, " lda=", a.stride(0), " ldb=", b.stride(0),
               " ldc=", c.stride(0), " align(a,b,c)=", reinterpret_cast<uintptr_t>(a.data_ptr()) % 16, ",",
               reinterpret_cast<uintptr_t>(b.data_ptr()) % 16, ",", reinterpret_cast<uintptr_t>(c.data_ptr()) % 16, ": ",
@@ -577,7 +584,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("post_counts", &post_counts);
   m.def("wait_posted", &wait_posted);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
-  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"),
+        py::arg("fixed_order") = false);
   m.def("rope_qkv", &rope_qkv);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
@@ -586,7 +594,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
   m.def("sumsq", &sumsq);
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("c"), py::arg("layout"), py::arg("bias"),
-        py::arg("accumulate"), py::arg("residual") = py::none());
+        py::arg("accumulate"), py::arg("residual") = py::none(), py::arg("pair") = -1);
   m.def("put_block", &put_block);
   m.def("get_block", &get_block);
   m.def("scalar_put_get", &scalar_put_get);

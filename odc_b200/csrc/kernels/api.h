@@ -91,7 +91,14 @@ cudaError_t launch_sumsq(const void* x, int kind, size_t n, float* out, int sm_c
 struct GemmPlan;
 cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const void* bias, int M, int N, int K,
                       int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
-                      int sm_count, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
+                      int sm_count, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0,
+                      int pair_mode = -1 /* -1: ODC_GEMM_PAIR decides, 0: single-CTA kernel, 1: CTA-pair kernel */);
+
+// Same contract on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles).  Returns cudaErrorNotSupported for shapes it
+// does not take (M or N below 256, bf16 accumulation); gemm_bf16 tries it first unless ODC_GEMM_PAIR=0.
+cudaError_t gemm_bf16_pair(const void* a, const void* b, void* c, int c_kind, const void* bias, int M, int N, int K,
+                           int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
+                           int sm_count, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
 
 // ---- GEMMs fused with the on-demand primitives ---------------------------------------------------
 // dW[n_out, k_in] = dY[tokens, n_out]^T X[tokens, k_in]; row r of dW is added (x scale) into

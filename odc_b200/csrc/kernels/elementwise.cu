@@ -133,14 +133,16 @@ rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, bf16*
   }
 }
 
-// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)).  Each lane accumulates dw for its own columns in
-// registers over all rows it handles; the warps of a CTA then combine through shared memory and the CTA
-// writes one row of partial sums.
-template <int R>
-__global__ void __launch_bounds__(kNormThreads)
+// dx = rstd * (dy*w - x * rstd^2 * mean(dy*w*x)).  A row is handled by R warps and a lane keeps V 16-byte pieces of
+// x and dy in registers (V <= 4, so the kernel fits two CTAs per SM and both keep loads in flight); each lane
+// accumulates dw for its own columns over all rows it handles, the warps of a CTA combine through shared memory,
+// and the CTA then either adds its sums into dw (kAtomic: dw zeroed before the launch, one launch in total) or
+// writes one row of partial sums for a second, fixed-order pass.
+template <int R, int V, bool kAtomic>
+__global__ void __launch_bounds__(kNormThreads, 2)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
-                   const float* __restrict__ rstd_in, bf16* __restrict__ dx, float* __restrict__ partial, int rows,
-                   int cols) {
+                   const float* __restrict__ rstd_in, bf16* __restrict__ dx, float* __restrict__ partial,
+                   float* __restrict__ dw_out, int rows, int cols) {
   extern __shared__ float dw_smem[];  // [cols]
   __shared__ float red[kNormWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -148,9 +150,9 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   constexpr int kRowsPerIter = kNormWarps / R;
   const int nvec = cols / 8;
   for (int c = threadIdx.x; c < cols; c += blockDim.x) dw_smem[c] = 0.f;
-  float dw[kNormVec][8];
+  float dw[V][8];
 #pragma unroll
-  for (int k = 0; k < kNormVec; ++k)
+  for (int k = 0; k < V; ++k)
 #pragma unroll
     for (int i = 0; i < 8; ++i) dw[k][i] = 0.f;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
@@ -161,10 +163,10 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(live ? row : 0) * cols);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + size_t(live ? row : 0) * cols);
     const float rstd = live ? rstd_in[row] : 0.f;
-    uint4 xv[kNormVec], gv[kNormVec];
+    uint4 xv[V], gv[V];
 #pragma unroll
-    for (int k = 0; k < kNormVec; ++k) {
-      const int v = (sub * kNormVec + k) * 32 + lane;
+    for (int k = 0; k < V; ++k) {
+      const int v = (sub * V + k) * 32 + lane;
       if (live && v < nvec) {
         xv[k] = xr[v];
         gv[k] = gr[v];
@@ -172,8 +174,8 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     }
     float dot = 0.f;
 #pragma unroll
-    for (int k = 0; k < kNormVec; ++k) {
-      const int v = (sub * kNormVec + k) * 32 + lane;
+    for (int k = 0; k < V; ++k) {
+      const int v = (sub * V + k) * 32 + lane;
       if (live && v < nvec) {
         float xf[8], gf[8], wf[8];
         unpack8(xv[k], xf);
@@ -191,8 +193,8 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
     const float c = dot * rstd * rstd / cols;
     uint4* dr = reinterpret_cast<uint4*>(dx + size_t(row) * cols);
 #pragma unroll
-    for (int k = 0; k < kNormVec; ++k) {
-      const int v = (sub * kNormVec + k) * 32 + lane;
+    for (int k = 0; k < V; ++k) {
+      const int v = (sub * V + k) * 32 + lane;
       if (v < nvec) {
         float xf[8], gf[8], wf[8], o[8];
         unpack8(xv[k], xf);
@@ -206,16 +208,20 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
   }
   __syncthreads();
 #pragma unroll
-  for (int k = 0; k < kNormVec; ++k) {
-    const int v = (sub * kNormVec + k) * 32 + lane;
+  for (int k = 0; k < V; ++k) {
+    const int v = (sub * V + k) * 32 + lane;
     if (v < nvec) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[v * 8 + i], dw[k][i]);
     }
   }
   __syncthreads();
-  float* prow = partial + size_t(blockIdx.x) * cols;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) prow[c] = dw_smem[c];
+  if constexpr (kAtomic) {
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) atomicAdd(dw_out + c, dw_smem[c]);
+  } else {
+    float* prow = partial + size_t(blockIdx.x) * cols;
+    for (int c = threadIdx.x; c < cols; c += blockDim.x) prow[c] = dw_smem[c];
+  }
 }
 
 __global__ void colsum_kernel(const float* __restrict__ partial, float* __restrict__ out, int parts, int cols) {
@@ -449,12 +455,18 @@ cudaError_t rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, in
   return cudaGetLastError();
 }
 
-template <int R>
+template <int R, int V>
 cudaError_t rmsnorm_bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* partial,
-                          int rows, int cols, int grid, cudaStream_t stream) {
-  rmsnorm_bwd_kernel<R><<<grid, kNormThreads, cols * sizeof(float), stream>>>(
-      static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
-      static_cast<bf16*>(dx), partial, rows, cols);
+                          float* dw, int rows, int cols, int grid, cudaStream_t stream) {
+  if (partial == nullptr) {
+    rmsnorm_bwd_kernel<R, V, true><<<grid, kNormThreads, cols * sizeof(float), stream>>>(
+        static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
+        static_cast<bf16*>(dx), nullptr, dw, rows, cols);
+  } else {
+    rmsnorm_bwd_kernel<R, V, false><<<grid, kNormThreads, cols * sizeof(float), stream>>>(
+        static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
+        static_cast<bf16*>(dx), partial, dw, rows, cols);
+  }
   return cudaGetLastError();
 }
 
@@ -475,16 +487,27 @@ int rmsnorm_bwd_grid(int rows, int sm_count) {
   return want < g ? (want < 1 ? 1 : want) : g;
 }
 
+// partial == nullptr: single launch, the CTAs add their column sums into dw (zeroed here first; the order of the
+// additions varies from run to run).  partial = [grid, cols] scratch: per-CTA sums, then a fixed-order column pass.
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
                                float* partial, float* dw, int rows, int cols, int grid, cudaStream_t stream) {
   if (cols % 8 != 0 || cols > 8192) return cudaErrorInvalidValue;
   cudaError_t e;
-  if (cols <= 2048) e = rmsnorm_bwd_t<1>(dy, x, w, rstd, dx, partial, rows, cols, grid, stream);
-  else if (cols <= 4096) e = rmsnorm_bwd_t<2>(dy, x, w, rstd, dx, partial, rows, cols, grid, stream);
-  else e = rmsnorm_bwd_t<4>(dy, x, w, rstd, dx, partial, rows, cols, grid, stream);
+  if (partial == nullptr) {
+    e = cudaMemsetAsync(dw, 0, sizeof(float) * cols, stream);
+    if (e != cudaSuccess) return e;
+    if (rows == 0) return cudaSuccess;
+  }
+  if (cols <= 1024) e = rmsnorm_bwd_t<1, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
+  else if (cols <= 2048) e = rmsnorm_bwd_t<2, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
+  else if (cols <= 4096) e = rmsnorm_bwd_t<4, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
+  else e = rmsnorm_bwd_t<8, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
   if (e != cudaSuccess) return e;
-  colsum_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(partial, dw, grid, cols);
-  return cudaGetLastError();
+  if (partial != nullptr) {
+    colsum_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(partial, dw, grid, cols);
+    e = cudaGetLastError();
+  }
+  return e;
 }
 
 cudaError_t launch_rope_qkv(const void* in, void* out, const long long* pos, int tokens, int n_q, int n_kv,

@@ -20,6 +20,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 #include <stdexcept>
 #include <string>
@@ -39,9 +41,18 @@ using namespace gemm_impl;
 // ------------------------------------------------------------------------------------------------
 cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const void* bias, int M, int N, int K,
                       int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
-                      int sm_count, cudaStream_t stream, const void* residual, long long ldr) {
+                      int sm_count, cudaStream_t stream, const void* residual, long long ldr, int pair_mode) {
   if (M == 0 || N == 0) return cudaSuccess;
   if (K == 0) return cudaErrorInvalidSymbol;
+  static const bool use_pairs = [] {
+    const char* e = getenv("ODC_GEMM_PAIR");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (pair_mode == 1 || (pair_mode < 0 && use_pairs)) {
+    const cudaError_t e = gemm_bf16_pair(a, b, c, c_kind, bias, M, N, K, layout, accumulate, lda, ldb, ldc, status,
+                                         sm_count, stream, residual, ldr);
+    if (e != cudaErrorNotSupported || pair_mode == 1) return e;
+  }
   const bool a_mn = (layout == 2);
   const bool b_mn = (layout != 0);
   // 16-byte rules of TMA: base addresses, row pitches; and of the vector epilogue: N, ldc

@@ -68,6 +68,7 @@ class _GroupInfo:
     divide: Dict[str, Any] = field(default_factory=dict)
     replica_fresh: bool = False               # the optimizer already wrote the low-precision copy
     position: Dict[int, int] = field(default_factory=dict)   # id(fsdp_param) -> index in the group
+    offsets: List[int] = field(default_factory=list)         # element offset of each fsdp_param in the flat buffers
     touched: set = field(default_factory=set)  # parameters this rank reduced a gradient for in this minibatch
     used: Optional[set] = None                 # union of `touched` over all ranks (None: not known, treat as all)
 
@@ -183,6 +184,7 @@ def _pin_group(group: FSDPParamGroup, index: int) -> None:
         o += numels[i]
     info = _GroupInfo(index, group, key, master, replica, numels, trainable, o, offs)
     info.position = {id(p): i for i, p in enumerate(params)}
+    info.offsets = [sum(numels[:i]) for i in range(len(numels))]
     hpz = getattr(group, "_odc_hpz_size", 0)
     if _S.enable_hpz and hpz:
         ranks = control.group_ranks(group.mesh_info.shard_process_group)
@@ -260,6 +262,19 @@ def _odc_foreach_all_gather(fsdp_params, group, async_op, all_gather_copy_in_str
     dtypes = [[src.dtype] for _ in info.numels]
     nums = [[n] for n in info.numels]
     return AllGatherResult(out, event, None, dtypes, nums, list(info.numels))
+
+
+def _odc_all_gather_inputs(self):
+    """Single-rank shard groups: stock FSDP2 skips the all-gather and builds the unsharded parameter from
+    ``all_gather_inputs``, casting the fp32 shard to the compute dtype on every unshard.  The group's low-precision
+    copy in the heap already holds exactly that (refreshed once per minibatch), so hand out a view of it."""
+    info = _S.by_param.get(id(self))
+    if (info is not None and info.replica is not None and info.hpz is None
+            and self.sharded_state == ShardedState.SHARDED and info.group.mesh_info.shard_mesh_size == 1):
+        i = info.position[id(self)]
+        off = info.offsets[i]
+        return [info.replica[off:off + info.numels[i]]]
+    return _S.originals["all_gather_inputs"].fget(self)
 
 
 # ------------------------------------------------------------------------------------------
@@ -542,12 +557,14 @@ def patch_fsdp2(enable_hpz: bool = False) -> None:
         "record_function": _fsdp_param_group.record_function,
         "_get_post_forward_mesh_info": _fully_shard._get_post_forward_mesh_info,
         "_init_param_group": _fully_shard._init_param_group,
+        "all_gather_inputs": FSDPParam.all_gather_inputs,
     }
     _fsdp_param_group.foreach_all_gather = _odc_foreach_all_gather
     _fsdp_param_group.foreach_reduce = _odc_foreach_reduce
     _fsdp_param_group.record_function = nvtx_record_function
     _fully_shard._get_post_forward_mesh_info = _hpz_get_post_forward_mesh_info
     _fully_shard._init_param_group = _hpz_init_param_group
+    FSDPParam.all_gather_inputs = property(_odc_all_gather_inputs)
     _S.patched = True
 
 
@@ -559,6 +576,7 @@ def unpatch_fsdp2() -> None:
     _fsdp_param_group.record_function = _S.originals["record_function"]
     _fully_shard._get_post_forward_mesh_info = _S.originals["_get_post_forward_mesh_info"]
     _fully_shard._init_param_group = _S.originals["_init_param_group"]
+    FSDPParam.all_gather_inputs = _S.originals["all_gather_inputs"]
     _S.patched = False
     _S.infos, _S.by_param, _S.next_index, _S.pending_hpz = [], {}, 0, None
     _S.reduction = _S.gather = None

@@ -146,8 +146,10 @@ class _RMSNorm(torch.autograd.Function):
     def backward(ctx, dy):
         x2, weight, rstd = ctx.saved_tensors
         dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
-        dx, dw = _ext().rmsnorm_bwd(dy2, x2, weight, rstd)
-        _count(2)
+        from .. import config
+        fixed = config.deterministic()   # fixed-order column sums (two launches) instead of in-kernel atomics (one)
+        dx, dw = _ext().rmsnorm_bwd(dy2, x2, weight, rstd, fixed)
+        _count(2 if fixed else 1)
         return dx.view(ctx.shape), dw.to(weight.dtype), None
 
 

@@ -195,6 +195,37 @@ def test_gemm_layouts(ext, layout, M, N, K):
     torch.testing.assert_close(c32, want + 1 + bias.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
 
 
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (256, 512, 256), (304, 1376, 200), (1000, 264, 1032),
+                                   (4096, 2048, 4096), (16384, 3072, 2048)])
+def test_gemm_cta_pair_layouts(ext, layout, M, N, K):
+    """The CTA-pair (cta_group::2) kernel, forced: 256 x 256 tiles split over two SMs, ragged edges in M, N and K."""
+    K = (K + 7) // 8 * 8 if layout != "tn" else K
+    M = (M + 7) // 8 * 8 if layout == "tn" else M
+    torch.manual_seed(M + N + K)
+    A = torch.randn(M, K, device="cuda").bfloat16()
+    B = torch.randn(K, N, device="cuda").bfloat16()
+    want = A.float() @ B.float()
+    a = A.t().contiguous() if layout == "tn" else A
+    b = B.t().contiguous() if layout == "nt" else B
+    c = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ext.gemm(a, b, c, layout, None, False, None, 1)
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
+    torch.testing.assert_close(c.float(), want, rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    # bias + residual in the epilogue of a bf16 output
+    bias = torch.randn(N, device="cuda").bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16()
+    ext.gemm(a, b, c, layout, bias, False, res, 1)
+    torch.testing.assert_close(c.float(), want + bias.float() + res.float(), rtol=2e-2, atol=2e-2 * math.sqrt(K))
+    # fp32 output with accumulation (TMA reduce-add) and bias
+    c32 = torch.ones(M, N, device="cuda")
+    ext.gemm(a, b, c32, layout, bias, True, None, 1)
+    torch.cuda.synchronize()
+    assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
+    torch.testing.assert_close(c32, want + 1 + bias.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
+
+
 def test_linear_autograd_matches_reference():
     from odc_b200 import ops
     x = torch.randn(3, 100, 512, device="cuda").bfloat16().requires_grad_()
