@@ -46,7 +46,7 @@ cudaError_t gemm_bf16(const void* a, const void* b, void* c, int c_kind, const v
   if (K == 0) return cudaErrorInvalidSymbol;
   static const bool use_pairs = [] {
     const char* e = getenv("ODC_GEMM_PAIR");
-    return e != nullptr && e[0] == '1';
+    return e == nullptr || e[0] != '0';
   }();
   if (pair_mode == 1 || (pair_mode < 0 && use_pairs)) {
     const cudaError_t e = gemm_bf16_pair(a, b, c, c_kind, bias, M, N, K, layout, accumulate, lda, ldb, ldc, status,

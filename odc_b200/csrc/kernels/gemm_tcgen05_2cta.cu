@@ -53,6 +53,20 @@ struct Params {
   int* status;
 };
 
+// Tile order: groups of kGroupM tile rows are walked column by column (rows fastest inside a group), so the pairs
+// that run at the same time share a few A row panels and a few B column panels and both stay in L2 however large
+// the whole operands are.
+constexpr int kGroupM = 16;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
+  const int per_group = kGroupM * tiles_n;
+  const int group = tile / per_group;
+  const int first_m = group * kGroupM;
+  const int gsize = min(tiles_m - first_m, kGroupM);
+  const int in_group = tile - group * per_group;
+  *tm = first_m + in_group % gsize;
+  *tn = in_group / gsize;
+}
+
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&v);
@@ -118,8 +132,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(cta) * BMH;   // this CTA's rows of A and C
-        const int n0 = (tile / p.tiles_m) * BN + static_cast<int>(cta) * BNH;    // this CTA's rows of B
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+        const int m0 = tm * 256 + static_cast<int>(cta) * BMH;   // this CTA's rows of A and C
+        const int n0 = tn * BN + static_cast<int>(cta) * BNH;    // this CTA's rows of B
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
@@ -189,8 +205,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     bool ok = true;
     const uint32_t tempty_leader0 = mapa_shared(tempty0, 0);
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
-      const int m0 = (tile % p.tiles_m) * 256 + static_cast<int>(cta) * BMH;
-      const int n0 = (tile / p.tiles_m) * BN;
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+      const int m0 = tm * 256 + static_cast<int>(cta) * BMH;
+      const int n0 = tn * BN;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!(ok = mbar_wait(tfull0 + 8 * acc, acc_ph, wc, 14))) break;
