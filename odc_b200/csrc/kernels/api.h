@@ -100,6 +100,15 @@ cudaError_t gemm_bf16_pair(const void* a, const void* b, void* c, int c_kind, co
                            int layout, bool accumulate, long long lda, long long ldb, long long ldc, int* status,
                            int sm_count, cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
 
+cudaError_t gemm_wgrad_scatter_pair(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
+                                    long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
+                                    long long acc_offset, int rows_per_rank, int nranks, float scale,
+                                    unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream);
+cudaError_t gemm_gather_pair(bool dgrad, const void* a, const long long* shard_ptrs, void* w_local, void* out,
+                             const void* bias, int M, int w_rows, int w_cols, long long lda, long long ldo,
+                             int rows_per_rank, int nranks, unsigned int* group_flags, int* status, int sm_count,
+                             cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
+
 // ---- GEMMs fused with the on-demand primitives ---------------------------------------------------
 // dW[n_out, k_in] = dY[tokens, n_out]^T X[tokens, k_in]; row r of dW is added (x scale) into
 // accumulator acc_ptrs[r / rows_per_rank] at element acc_offset + (r % rows_per_rank) * k_in.

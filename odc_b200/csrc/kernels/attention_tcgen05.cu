@@ -262,19 +262,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sr + c * 32);
       tmem_ld_wait();
-      float mx = -INFINITY;
+      // four independent chains for the row maximum (and for the row sum below): a single running value would put
+      // 128 dependent operations on the critical path of every key block
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
+        // keys [kv0, kv_hi) are visible to this row; everything from kv_hi on is masked
+        const int kv_hi = min(seq_len, p.causal ? q_rel + 1 : seq_len) - kv0;
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
-          const int kv = kv0 + i;
-          const bool okk = kv < seq_len && (!p.causal || kv <= q_rel);
-          if (!okk) sr[i] = 0xff800000u;  // -inf
-          mx = fmaxf(mx, __uint_as_float(sr[i]));
+          if (i >= kv_hi) sr[i] = 0xff800000u;  // -inf
+          mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[i]));
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
+        for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sr[i]));
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx * p.scale_log2);
       // lazy rescale of the running output (exact: P and l keep using m_used until it is bumped)
       const bool bump = (m_new - m_used > kRescaleThreshold) || (m_used == -INFINITY && m_new > -INFINITY);
@@ -303,14 +306,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (!(ok = mbar_wait(p_empty, (j - 1) & 1, wc, 19))) break;
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int v = 0; v < 16; ++v) {
         float f[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           f[i] = exp2f(fmaf(__uint_as_float(sr[8 * v + i]), p.scale_log2, -m_sub));
-          sum += f[i];
+          sum4[i & 3] += f[i];
         }
         uint4 o;
         o.x = pack2(f[0], f[1]);
@@ -319,7 +322,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         o.w = pack2(f[6], f[7]);
         *reinterpret_cast<uint4*>(p_ptr + swz_chunk_offset(row, v)) = o;
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       // S buffer free for block j+2; P visible to the tensor core (async proxy)
       tc_fence_before();
       fence_proxy_async();

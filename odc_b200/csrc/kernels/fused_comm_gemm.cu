@@ -14,6 +14,8 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "api.h"
@@ -23,6 +25,16 @@
 namespace odc {
 
 using namespace gemm_impl;
+
+// ODC_GEMM_PAIR=0 keeps every GEMM on the single-CTA kernel (for A/B runs); by default shapes of at least one
+// 256 x 256 tile run on CTA pairs.
+static bool pairs_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("ODC_GEMM_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
 
 cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
                                long long ld_x, const long long* acc_ptrs, const long long* ctr_ptrs,
@@ -66,6 +78,12 @@ cudaError_t gemm_wgrad_scatter_tma(const void* dy, const void* x, int tokens, in
                                    unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream) {
   if (n_out == 0 || k_in == 0 || nranks == 0) return cudaSuccess;
   if (tokens == 0) return cudaErrorInvalidValue;
+  if (pairs_enabled()) {  // CTA pairs (256 x 256 tiles) when the shape allows it
+    const cudaError_t e = gemm_wgrad_scatter_pair(dy, x, tokens, n_out, k_in, ld_dy, ld_x, acc_addrs_host, ctr_ptrs,
+                                                  acc_offset, rows_per_rank, nranks, scale, done_slot, status, sm_count,
+                                                  stream);
+    if (e != cudaErrorNotSupported) return e;
+  }
   if (nranks > kMaxOwners || (rows_per_rank % BM) != 0) return cudaErrorNotSupported;  // caller falls back to red.add
   if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x)) & 15) return cudaErrorMisalignedAddress;
   if ((ld_dy % 8) || (ld_x % 8) || (k_in % 8) || (acc_offset % 4)) return cudaErrorInvalidValue;
@@ -109,6 +127,11 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
                            cudaStream_t stream, const void* residual, long long ldr) {
   if (M == 0 || N == 0 || nranks == 0) return cudaSuccess;
   if (K == 0) return cudaErrorInvalidValue;
+  if (pairs_enabled()) {
+    const cudaError_t e = gemm_gather_pair(false, x, shard_ptrs, w_local, y, bias, M, N, K, ldx, ldy, rows_per_rank,
+                                           nranks, panel_flags, status, sm_count, stream, residual, ldr);
+    if (e != cudaErrorNotSupported) return e;
+  }
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(y)) & 15)
     return cudaErrorMisalignedAddress;
   if ((ldx % 8) || (ldy % 8) || (N % 8) || (K % 128)) return cudaErrorInvalidValue;
@@ -157,6 +180,11 @@ cudaError_t gemm_gather_nn(const void* dy, const long long* shard_ptrs, void* w_
   // dx[M, k_in] = dy[M, n_out] * W[n_out, k_in]; W's rows (the reduction dimension) are gathered
   if (M == 0 || k_in == 0 || nranks == 0) return cudaSuccess;
   if (n_out == 0) return cudaErrorInvalidValue;
+  if (pairs_enabled()) {
+    const cudaError_t e = gemm_gather_pair(true, dy, shard_ptrs, w_local, dx, nullptr, M, n_out, k_in, lddy, lddx,
+                                           rows_per_rank, nranks, group_flags, status, sm_count, stream);
+    if (e != cudaErrorNotSupported) return e;
+  }
   if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(dx)) & 15)
     return cudaErrorMisalignedAddress;
   if ((lddy % 8) || (lddx % 8) || (n_out % 8) || (k_in % 128)) return cudaErrorInvalidValue;

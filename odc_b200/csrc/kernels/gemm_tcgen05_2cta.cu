@@ -51,6 +51,29 @@ struct Params {
   int a_mn, b_mn;
   int tiles_m, tiles_n;   // in units of the pair's 256 x 256 tile
   int* status;
+  // kModeScatter: the epilogue adds every 128-row output box into the fp32 accumulator of the rank that owns those rows
+  const long long* ctr_ptrs;   // [nranks] arrival counters
+  int rows_per_rank;           // output rows owned by one rank (a multiple of 128)
+  int nranks;
+  float scale;
+  unsigned int* done_slot;     // self-resetting CTA completion counter
+  // kModeGather: operand B (a row-sharded weight) is assembled from the owners' shards while the GEMM runs
+  const long long* shard_ptrs; // [nranks] base address of each owner's [rows_per_rank, w_cols] bf16 shard
+  unsigned char* b_local;      // local [w_rows, w_cols] bf16 buffer the shards are gathered into (tensor map B covers it)
+  unsigned int* panel_flags;   // [ceil(w_rows / 256)] chunks landed per 256-row group (zeroed before the launch)
+  int w_rows, w_cols;          // gathered matrix: [N, K] when B is K-major (y = x W^T), [K, N] when MN-major (dx = dy W)
+};
+
+constexpr int kModePlain = 0, kModeScatter = 1, kModeGather = 2;
+constexpr int kFetchWarps = 4;
+constexpr int kFetchWarpBytes = 16384;                  // moved by one fetch warp between two flag updates
+constexpr int kFetchChunkBytes = kFetchWarps * kFetchWarpBytes;
+template <int kMode> struct Roles {
+  static constexpr int kThreadsTotal = kThreads + (kMode == kModeGather ? 32 * kFetchWarps : 0);
+};
+constexpr int kMaxOwners = 8;
+struct OwnerMaps {   // one fp32 tensor map per owner's accumulator region (kModeScatter)
+  CUtensorMap m[kMaxOwners];
 };
 
 // Tile order: groups of kGroupM tile rows are walked column by column (rows fastest inside a group), so the pairs
@@ -72,9 +95,11 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+template <int kMode>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Roles<kMode>::kThreadsTotal, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_c, const Params p) {
+                      const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ OwnerMaps owners,
+                      const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -129,6 +154,30 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     if (lane == 0) {
       prefetch_tmap(&tmap_a);
       prefetch_tmap(&tmap_b);
+      // gather mode: wait (bounded) until every chunk of 256-row group `g` of the gathered matrix is in local memory
+      int groups_ready = 0;
+      auto wait_group = [&](int g) -> bool {
+        if (g < groups_ready) return true;
+        const long long group_bytes = static_cast<long long>(min(BN, p.w_rows - g * BN)) * p.w_cols * 2;
+        const unsigned int target =
+            static_cast<unsigned int>((group_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * kFetchWarps;
+        const uint64_t t0 = globaltimer_ns();
+        unsigned int seen;
+        while (true) {
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.panel_flags + g) : "memory");
+          if (seen >= target) break;
+          if (*abort_flag) return false;
+          if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+            *abort_flag = 1;
+            report(p.status, kErrPipelineTimeout, 25, g);
+            return false;
+          }
+          __nanosleep(64);
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> visible to TMA reads
+        if (p.b_mn) groups_ready = g + 1;  // the reduction dimension is walked in order
+        return true;
+      };
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
@@ -136,9 +185,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
         const int m0 = tm * 256 + static_cast<int>(cta) * BMH;   // this CTA's rows of A and C
         const int n0 = tn * BN + static_cast<int>(cta) * BNH;    // this CTA's rows of B
+        if constexpr (kMode == kModeGather) {
+          // B K-major (forward): the 256 weight rows this tile multiplies must have landed in local memory first
+          if (!p.b_mn && !(ok = wait_group(tn))) break;
+        }
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
+          if constexpr (kMode == kModeGather) {
+            // B MN-major (input gradient): the gathered rows are the reduction dimension, 4 k-blocks per group
+            if (p.b_mn && !(ok = wait_group((kb * BK) / BN))) break;
+          }
           if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, wc, 11))) break;
           const uint32_t sa = base + s * kStageBytes;
           const uint32_t sb = sa + kATile;
@@ -197,7 +254,53 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         }
       }
     }
-  } else {
+  } else if (kMode == kModeGather && warp >= 6) {
+    // ------------------------------------------------------------------ shard fetch (every CTA of the grid)
+    // The owners' shards are copied into the local B buffer in address order (= group order): 64 KiB per step and
+    // CTA, 16 KiB per warp with 16 x 16-byte peer loads in flight per lane; after its part a warp makes the stores
+    // visible and counts them on the group's flag.
+    const int fw = warp - 6;
+    const long long total_bytes = static_cast<long long>(p.w_rows) * p.w_cols * 2;
+    const long long shard_bytes = static_cast<long long>(p.rows_per_rank) * p.w_cols * 2;
+    const long long panel_bytes_full = static_cast<long long>(BN) * p.w_cols * 2;  // a multiple of the chunk size
+    const long long n_chunks = (total_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes;
+    for (long long c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+      const long long byte0 = c * kFetchChunkBytes + fw * kFetchWarpBytes;
+      const long long last = min(byte0 + kFetchWarpBytes, total_bytes) - 1;
+      const int owner0 = static_cast<int>(byte0 / shard_bytes);
+      const bool one_owner = byte0 < total_bytes && owner0 == static_cast<int>(last / shard_bytes);
+      const unsigned char* src0 = one_owner
+          ? reinterpret_cast<const unsigned char*>(p.shard_ptrs[owner0]) - static_cast<long long>(owner0) * shard_bytes
+          : nullptr;
+      uint4 r[16];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int v = 0; v < 16; ++v) {
+          const long long b = byte0 + (static_cast<long long>(half * 16 + v) * 32 + lane) * 16;
+          if (b < total_bytes) {
+            if (one_owner) {
+              r[v] = ld_stream_v4(src0 + b);
+            } else {
+              const int owner = static_cast<int>(b / shard_bytes);
+              r[v] = ld_stream_v4(reinterpret_cast<const unsigned char*>(p.shard_ptrs[owner]) + (b - owner * shard_bytes));
+            }
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < 16; ++v) {
+          const long long b = byte0 + (static_cast<long long>(half * 16 + v) * 32 + lane) * 16;
+          if (b < total_bytes) *reinterpret_cast<uint4*>(p.b_local + b) = r[v];
+        }
+      }
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) {
+        const int panel = static_cast<int>((c * kFetchChunkBytes) / panel_bytes_full);
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.panel_flags + panel) : "memory");
+      }
+    }
+  } else if (warp >= 2 && warp < 6) {
     // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
     const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
     uint32_t local_tile = 0;
@@ -227,6 +330,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tmem_ld_wait();
         const int col0 = n0 + bx * cols_per_box;
         if (col0 >= p.N || m0 >= p.M) continue;
+        if constexpr (kMode == kModeScatter) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * p.scale);
+        }
         if (p.bias != nullptr) {
 #pragma unroll
           for (int i = 0; i < 64; ++i)
@@ -270,7 +377,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (lane == 0) mbar_arrive(sready0 + 8 * buf);
         if (warp == 2 && lane == 0) {
           if (mbar_wait(sready0 + 8 * buf, use & 1, wc, 17)) {
-            if (p.accumulate) {
+            if constexpr (kMode == kModeScatter) {
+              // a CTA's 128 rows never straddle two owners (rows_per_rank is a multiple of 128)
+              const int owner = m0 / p.rows_per_rank;
+              tma_reduce_add_2d(&owners.m[owner], staging_u32 + buf * kStagingBytes, col0, m0 - owner * p.rows_per_rank);
+            } else if (p.accumulate) {
               tma_reduce_add_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
             } else {
               tma_store_2d(&tmap_c, staging_u32 + buf * kStagingBytes, col0, m0);
@@ -289,7 +400,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8 * acc);   // the leader may overwrite this accumulator
     }
-    if (warp == 2 && lane == 0) bulk_wait_group0();  // all output boxes are in memory
+    if (warp == 2 && lane == 0) {
+      bulk_wait_group0();  // all output boxes are in memory
+      if constexpr (kMode == kModeScatter) __threadfence_system();
+    }
   }
 
   // ---------------------------------------------------------------------- teardown
@@ -299,6 +413,21 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if constexpr (kMode == kModeScatter) {
+    // the last CTA to finish releases one arrival on every owner's counter, unless any CTA of the launch gave up
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const unsigned int prev = atomicAdd(p.done_slot, 1u);
+      if (prev == gridDim.x - 1) {
+        *p.done_slot = 0;
+        __threadfence_system();
+        const bool clean = !*abort_flag && (p.status == nullptr || *reinterpret_cast<volatile int*>(p.status) == 0);
+        if (clean)
+          for (int r = 0; r < p.nranks; ++r)
+            signal_add_release_sys(reinterpret_cast<unsigned long long*>(p.ctr_ptrs[r]), 1ull);
+      }
+    }
   }
 }
 
@@ -320,7 +449,8 @@ cudaError_t gemm_bf16_pair(const void* a, const void* b, void* c, int c_kind, co
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    attr_err = cudaFuncSetAttribute(gemm_bf16_pair_kernel<kModePlain>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes);
   });
   if (attr_err != cudaSuccess) return attr_err;
 
@@ -356,7 +486,106 @@ cudaError_t gemm_bf16_pair(const void* a, const void* b, void* c, int c_kind, co
   }
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
-  gemm_bf16_pair_kernel<<<2 * pairs, kThreads, kSmemBytes, stream>>>(ta, tb, tc, p);
+  gemm_bf16_pair_kernel<kModePlain><<<2 * pairs, kThreads, kSmemBytes, stream>>>(ta, tb, tc, OwnerMaps{}, p);
+  return cudaGetLastError();
+}
+
+// dW[n_out, k_in] = dY^T X on CTA pairs; every 128 x 32 fp32 output box is added (x scale) into the accumulator of the
+// rank that owns its rows by the TMA unit, through the peer mapping; then one arrival per owner.  Same contract as
+// gemm_wgrad_scatter_tma; returns cudaErrorNotSupported for shapes it does not take.
+cudaError_t gemm_wgrad_scatter_pair(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
+                                    long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
+                                    long long acc_offset, int rows_per_rank, int nranks, float scale,
+                                    unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream) {
+  using namespace gemm_pair;
+  if (n_out < 256 || k_in < 256 || tokens < BK || sm_count < 2) return cudaErrorNotSupported;
+  if (nranks > kMaxOwners || (rows_per_rank % BMH) != 0) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x)) & 15) return cudaErrorMisalignedAddress;
+  if ((ld_dy % 8) || (ld_x % 8) || (k_in % 8) || (acc_offset % 4)) return cudaErrorInvalidValue;
+  if (static_cast<long long>(rows_per_rank) * nranks < n_out) return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_bf16_pair_kernel<kModeScatter>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  CUtensorMap ta, tb;
+  // "tn": A = dY viewed as [K = tokens rows, M = n_out cols], B = X as [K = tokens rows, N = k_in cols]
+  if (!encode_tile_map_2d(&ta, dy, n_out, tokens, ld_dy * 2, 64, 64)) return cudaErrorInvalidValue;
+  if (!encode_tile_map_2d(&tb, x, k_in, tokens, ld_x * 2, 64, 64)) return cudaErrorInvalidValue;
+  OwnerMaps owners{};
+  for (int r = 0; r < nranks; ++r) {
+    float* base = reinterpret_cast<float*>(static_cast<uintptr_t>(acc_addrs_host[r])) + acc_offset;
+    if (!encode_tile_map_2d_f32(&owners.m[r], base, k_in, rows_per_rank, static_cast<uint64_t>(k_in) * 4, 32, BMH))
+      return cudaErrorInvalidValue;
+  }
+  Params p{};
+  p.M = n_out; p.N = k_in; p.K = tokens;
+  p.c_is_f32 = 1;
+  p.a_mn = 1; p.b_mn = 1;
+  p.tiles_m = (n_out + 255) / 256;
+  p.tiles_n = (k_in + BN - 1) / BN;
+  p.status = status;
+  p.ctr_ptrs = ctr_ptrs;
+  p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.scale = scale; p.done_slot = done_slot;
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  gemm_bf16_pair_kernel<kModeScatter><<<2 * pairs, kThreads, kSmemBytes, stream>>>(ta, tb, ta, owners, p);
+  return cudaGetLastError();
+}
+
+// Y[M, N] = X[M, K] W[N, K]^T (dgrad = false) or dX[M, K_in] = dY[M, N_out] W[N_out, K_in] (dgrad = true) on CTA pairs,
+// with W row-sharded over nranks owners and pulled into w_local by four extra warps per CTA while the GEMM runs.
+// Same contracts as gemm_gather_nt / gemm_gather_nn; cudaErrorNotSupported for shapes it does not take.
+cudaError_t gemm_gather_pair(bool dgrad, const void* a, const long long* shard_ptrs, void* w_local, void* out,
+                             const void* bias, int M, int w_rows, int w_cols, long long lda, long long ldo,
+                             int rows_per_rank, int nranks, unsigned int* group_flags, int* status, int sm_count,
+                             cudaStream_t stream, const void* residual, long long ldr) {
+  using namespace gemm_pair;
+  const int N = dgrad ? w_cols : w_rows;   // output columns
+  const int K = dgrad ? w_rows : w_cols;   // reduction length
+  if (M < 256 || N < 256 || K < BK || sm_count < 2) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(out)) & 15)
+    return cudaErrorMisalignedAddress;
+  if ((lda % 8) || (ldo % 8) || (N % 8) || (w_cols % 128)) return cudaErrorInvalidValue;
+  if (static_cast<long long>(rows_per_rank) * nranks < w_rows) return cudaErrorInvalidValue;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_bf16_pair_kernel<kModeGather>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  CUtensorMap ta, tb, tc;
+  if (!encode_tile_map_2d(&ta, a, K, M, lda * 2, 64, BMH)) return cudaErrorInvalidValue;
+  if (!dgrad) {
+    if (!encode_tile_map_2d(&tb, w_local, w_cols, w_rows, static_cast<uint64_t>(w_cols) * 2, 64, BNH)) return cudaErrorInvalidValue;
+  } else {  // B is MN-major: rows = reduction index, box {64 output columns, 64 reduction rows}
+    if (!encode_tile_map_2d(&tb, w_local, w_cols, w_rows, static_cast<uint64_t>(w_cols) * 2, 64, 64)) return cudaErrorInvalidValue;
+  }
+  if (!encode_tile_map_2d(&tc, out, N, M, ldo * 2, 64, BMH)) return cudaErrorInvalidValue;
+  Params p{};
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.M = M; p.N = N; p.K = K;
+  p.b_mn = dgrad ? 1 : 0;
+  p.tiles_m = (M + 255) / 256;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.status = status;
+  p.shard_ptrs = shard_ptrs;
+  p.b_local = static_cast<unsigned char*>(w_local);
+  p.panel_flags = group_flags;
+  p.rows_per_rank = rows_per_rank; p.nranks = nranks;
+  p.w_rows = w_rows; p.w_cols = w_cols;
+  if (residual != nullptr) {
+    if ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15)) return cudaErrorInvalidValue;
+    p.residual = static_cast<const __nv_bfloat16*>(residual);
+    p.ldr = ldr;
+  }
+  cudaError_t e = cudaMemsetAsync(group_flags, 0, sizeof(unsigned int) * ((w_rows + BN - 1) / BN), stream);
+  if (e != cudaSuccess) return e;
+  const int grid = sm_count & ~1;  // every CTA also fetches, so the whole machine runs even when there are few tiles
+  gemm_bf16_pair_kernel<kModeGather><<<grid, Roles<kModeGather>::kThreadsTotal, kSmemBytes, stream>>>(ta, tb, tc, OwnerMaps{}, p);
   return cudaGetLastError();
 }
 
