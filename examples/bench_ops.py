@@ -4,6 +4,7 @@
     python examples/bench_ops.py elementwise     # RMSNorm / RoPE / SwiGLU / CE / AdamW achieved GB/s
     python examples/bench_ops.py comm            # gather / scatter_accumulate with peers emulated on one GPU
     python examples/bench_ops.py attention       # varlen attention fwd/bwd vs flash-attn
+    python examples/bench_ops.py attention_mix   # the same on packs of log-normal sequence lengths (the headline workload)
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs, an L2 flush (256 MB write) between
 timed iterations, median of the timed runs.  Fractions are of the measured peaks in MEASURED_PEAKS.json
@@ -153,6 +154,37 @@ def bench_attention():
               f"[flash-attn {t_r:.3f} ms] | bwd {t_b:.3f} ms {2.5 * flops / t_b / 1e9:.0f} TFLOP/s [flash-attn {t_rb:.3f} ms]")
 
 
+def bench_attention_mix():
+    """The headline workload's length mix: one 16384-token pack of log-normal sequences (median 512, sigma 1.0, cap 8192)."""
+    import numpy as np
+    from flash_attn import flash_attn_varlen_func
+
+    from odc_b200 import ops
+    from odc_b200.data import LengthSpec
+    from odc_b200.data.synthetic import sample_until_budget
+    _, tf, kind = peaks()
+    hq, hkv, d = 32, 8, 64
+    for seed in range(3):
+        lens = sample_until_budget(LengthSpec("lognormal", lo=16, median=512.0, sigma=1.0, cap=8192), 16384,
+                                   np.random.default_rng([1234, seed]))
+        T, mx = sum(lens), max(lens)
+        cu = torch.tensor([0] + list(np.cumsum(lens)), device="cuda", dtype=torch.int32)
+        q = torch.randn(T, hq, d, device="cuda").bfloat16().requires_grad_()
+        k = torch.randn(T, hkv, d, device="cuda").bfloat16().requires_grad_()
+        v = torch.randn(T, hkv, d, device="cuda").bfloat16().requires_grad_()
+        flops = 4.0 * hq * d * sum(n * n for n in lens) / 2
+        t_f = timed(lambda: ops.varlen_attention(q, k, v, cu, mx))
+        t_r = timed(lambda: flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True))
+        o = ops.varlen_attention(q, k, v, cu, mx)
+        do = torch.randn_like(o)
+        t_b = timed(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True))
+        o2 = flash_attn_varlen_func(q, k, v, cu, cu, mx, mx, causal=True)
+        t_rb = timed(lambda: torch.autograd.grad(o2, (q, k, v), do, retain_graph=True))
+        print(f"pack {seed}: T={T} in {len(lens)} sequences (longest {mx}): fwd {t_f:.3f} ms {flops / t_f / 1e9:.0f} TFLOP/s "
+              f"[flash-attn {t_r:.3f} ms, {t_r / t_f:.2f}x] | bwd {t_b:.3f} ms {2.5 * flops / t_b / 1e9:.0f} TFLOP/s "
+              f"[flash-attn {t_rb:.3f} ms, {t_rb / t_b:.2f}x] | fwd+bwd {(t_r + t_rb) / (t_f + t_b):.2f}x")
+
+
 def small_gemm():
     """One forward-shaped GEMM, a few launches: the small case used for ncu captures (operands + output > L2)."""
     from odc_b200 import _ext
@@ -239,6 +271,6 @@ def small_fused():
 
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": bench_gemm, "elementwise": bench_elementwise, "comm": bench_comm, "attention": bench_attention,
+    {"gemm": bench_gemm, "elementwise": bench_elementwise, "comm": bench_comm, "attention": bench_attention, "attention_mix": bench_attention_mix,
      "small_gemm": small_gemm, "small_attention": small_attention, "small_comm": small_comm,
      "small_fused": small_fused}[which]()
