@@ -399,7 +399,7 @@ void gemm_wgrad_scatter(Tensor dy, Tensor x, Tensor acc_table, Tensor ctr_table,
 }
 
 bool gemm_wgrad_scatter_tma(Tensor dy, Tensor x, std::vector<int64_t> acc_addrs, Tensor ctr_table, int64_t acc_offset,
-                            int64_t rows_per_rank, double scale) {
+                            int64_t rows_per_rank, double scale, int start_rank) {
   c10::cuda::CUDAGuard g(dy.device());
   odc::bind_device(dy.get_device());
   TORCH_CHECK(dy.dim() == 2 && x.dim() == 2 && dy.size(0) == x.size(0), "wgrad_scatter: dy [T,N], x [T,K]");
@@ -410,7 +410,7 @@ bool gemm_wgrad_scatter_tma(Tensor dy, Tensor x, std::vector<int64_t> acc_addrs,
       dy.data_ptr(), x.data_ptr(), dy.size(0), dy.size(1), x.size(1), dy.stride(0), x.stride(0), addrs.data(),
       reinterpret_cast<const long long*>(ctr_table.data_ptr<int64_t>()), acc_offset, static_cast<int>(rows_per_rank),
       static_cast<int>(addrs.size()), static_cast<float>(scale), next_done_slot(dy.get_device()),
-      gemm_status(dy.get_device()).data_ptr<int>(), sm_count(), cur_stream());
+      gemm_status(dy.get_device()).data_ptr<int>(), sm_count(), cur_stream(), start_rank);
   if (e == cudaErrorNotSupported) return false;  // shape not eligible: the caller uses the red.add variant
   check(e, "gemm_wgrad_scatter_tma");
   return true;
@@ -448,7 +448,7 @@ Tensor gemm_gather(Tensor x, Tensor shard_table, Tensor w_local, c10::optional<T
   return y;
 }
 
-Tensor gemm_gather_dgrad(Tensor dy, Tensor shard_table, Tensor w_local, int64_t rows_per_rank) {
+Tensor gemm_gather_dgrad(Tensor dy, Tensor shard_table, Tensor w_local, int64_t rows_per_rank, int start_rank) {
   c10::cuda::CUDAGuard g(dy.device());
   odc::bind_device(dy.get_device());
   TORCH_CHECK(dy.dim() == 2 && w_local.dim() == 2 && dy.size(1) == w_local.size(0),
@@ -462,7 +462,7 @@ Tensor gemm_gather_dgrad(Tensor dy, Tensor shard_table, Tensor w_local, int64_t 
                             w_local.data_ptr(), dx.data_ptr(), M, N, K, dy.stride(0), dx.stride(0),
                             static_cast<int>(rows_per_rank), static_cast<int>(shard_table.numel()),
                             reinterpret_cast<unsigned int*>(flags.data_ptr<int>()),
-                            gemm_status(dy.get_device()).data_ptr<int>(), sm_count(), cur_stream()),
+                            gemm_status(dy.get_device()).data_ptr<int>(), sm_count(), cur_stream(), start_rank),
         "gemm_gather_dgrad");
   return dx;
 }
@@ -601,10 +601,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("atomic_test", &atomic_test);
   m.def("grid_barrier_test", &grid_barrier_test);
   m.def("gemm_wgrad_scatter", &gemm_wgrad_scatter);
-  m.def("gemm_wgrad_scatter_tma", &gemm_wgrad_scatter_tma);
+  m.def("gemm_wgrad_scatter_tma", &gemm_wgrad_scatter_tma, py::arg("dy"), py::arg("x"), py::arg("acc_addrs"),
+        py::arg("ctr_table"), py::arg("acc_offset"), py::arg("rows_per_rank"), py::arg("scale"), py::arg("start_rank") = 0);
   m.def("gemm_gather", &gemm_gather, py::arg("x"), py::arg("shard_table"), py::arg("w_local"), py::arg("bias"),
         py::arg("rows_per_rank"), py::arg("start_rank"), py::arg("residual") = py::none());
-  m.def("gemm_gather_dgrad", &gemm_gather_dgrad);
+  m.def("gemm_gather_dgrad", &gemm_gather_dgrad, py::arg("dy"), py::arg("shard_table"), py::arg("w_local"),
+        py::arg("rows_per_rank"), py::arg("start_rank") = 0);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
   m.def("kernel_status", &kernel_status);

@@ -103,11 +103,12 @@ cudaError_t gemm_bf16_pair(const void* a, const void* b, void* c, int c_kind, co
 cudaError_t gemm_wgrad_scatter_pair(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
                                     long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
                                     long long acc_offset, int rows_per_rank, int nranks, float scale,
-                                    unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream);
+                                    unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream,
+                                    int start_rank = 0);
 cudaError_t gemm_gather_pair(bool dgrad, const void* a, const long long* shard_ptrs, void* w_local, void* out,
                              const void* bias, int M, int w_rows, int w_cols, long long lda, long long ldo,
                              int rows_per_rank, int nranks, unsigned int* group_flags, int* status, int sm_count,
-                             cudaStream_t stream, const void* residual = nullptr, long long ldr = 0);
+                             cudaStream_t stream, const void* residual = nullptr, long long ldr = 0, int start_rank = 0);
 
 // ---- GEMMs fused with the on-demand primitives ---------------------------------------------------
 // dW[n_out, k_in] = dY[tokens, n_out]^T X[tokens, k_in]; row r of dW is added (x scale) into
@@ -122,7 +123,8 @@ cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_
 cudaError_t gemm_wgrad_scatter_tma(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
                                    long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
                                    long long acc_offset, int rows_per_rank, int nranks, float scale,
-                                   unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream);
+                                   unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream,
+                                   int start_rank = 0);
 // Y[M, N] = X[M, K] W[N, K]^T with rank r holding rows [r * rows_per_rank, ...) of W at shard_ptrs[r];
 // w_local [N, K] receives the gathered weight; panel_flags needs ceil(N / 256) words.
 cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_local, void* y, const void* bias,
@@ -134,7 +136,8 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
 // and later tiles find the whole weight in w_local.  group_flags needs ceil(n_out / 256) words.
 cudaError_t gemm_gather_nn(const void* dy, const long long* shard_ptrs, void* w_local, void* dx, int M, int n_out,
                            int k_in, long long lddy, long long lddx, int rows_per_rank, int nranks,
-                           unsigned int* group_flags, int* status, int sm_count, cudaStream_t stream);
+                           unsigned int* group_flags, int* status, int sm_count, cudaStream_t stream,
+                           int start_rank = 0);
 
 // ---- varlen attention ------------------------------------------------------------------------
 cudaError_t attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_seqlens,

@@ -75,13 +75,14 @@ cudaError_t gemm_wgrad_scatter(const void* dy, const void* x, int tokens, int n_
 cudaError_t gemm_wgrad_scatter_tma(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
                                    long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
                                    long long acc_offset, int rows_per_rank, int nranks, float scale,
-                                   unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream) {
+                                   unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream,
+                                   int start_rank) {
   if (n_out == 0 || k_in == 0 || nranks == 0) return cudaSuccess;
   if (tokens == 0) return cudaErrorInvalidValue;
   if (pairs_enabled()) {  // CTA pairs (256 x 256 tiles) when the shape allows it
     const cudaError_t e = gemm_wgrad_scatter_pair(dy, x, tokens, n_out, k_in, ld_dy, ld_x, acc_addrs_host, ctr_ptrs,
                                                   acc_offset, rows_per_rank, nranks, scale, done_slot, status, sm_count,
-                                                  stream);
+                                                  stream, start_rank);
     if (e != cudaErrorNotSupported) return e;
   }
   if (nranks > kMaxOwners || (rows_per_rank % BM) != 0) return cudaErrorNotSupported;  // caller falls back to red.add
@@ -129,7 +130,7 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
   if (K == 0) return cudaErrorInvalidValue;
   if (pairs_enabled()) {
     const cudaError_t e = gemm_gather_pair(false, x, shard_ptrs, w_local, y, bias, M, N, K, ldx, ldy, rows_per_rank,
-                                           nranks, panel_flags, status, sm_count, stream, residual, ldr);
+                                           nranks, panel_flags, status, sm_count, stream, residual, ldr, start_rank);
     if (e != cudaErrorNotSupported) return e;
   }
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(y)) & 15)
@@ -176,13 +177,15 @@ cudaError_t gemm_gather_nt(const void* x, const long long* shard_ptrs, void* w_l
 
 cudaError_t gemm_gather_nn(const void* dy, const long long* shard_ptrs, void* w_local, void* dx, int M, int n_out,
                            int k_in, long long lddy, long long lddx, int rows_per_rank, int nranks,
-                           unsigned int* group_flags, int* status, int sm_count, cudaStream_t stream) {
+                           unsigned int* group_flags, int* status, int sm_count, cudaStream_t stream,
+                           int start_rank) {
   // dx[M, k_in] = dy[M, n_out] * W[n_out, k_in]; W's rows (the reduction dimension) are gathered
   if (M == 0 || k_in == 0 || nranks == 0) return cudaSuccess;
   if (n_out == 0) return cudaErrorInvalidValue;
   if (pairs_enabled()) {
     const cudaError_t e = gemm_gather_pair(true, dy, shard_ptrs, w_local, dx, nullptr, M, n_out, k_in, lddy, lddx,
-                                           rows_per_rank, nranks, group_flags, status, sm_count, stream);
+                                           rows_per_rank, nranks, group_flags, status, sm_count, stream, nullptr, 0,
+                                           start_rank);
     if (e != cudaErrorNotSupported) return e;
   }
   if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(w_local) | reinterpret_cast<uintptr_t>(dx)) & 15)

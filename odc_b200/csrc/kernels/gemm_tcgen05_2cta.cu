@@ -62,6 +62,12 @@ struct Params {
   unsigned char* b_local;      // local [w_rows, w_cols] bf16 buffer the shards are gathered into (tensor map B covers it)
   unsigned int* panel_flags;   // [ceil(w_rows / 256)] chunks landed per 256-row group (zeroed before the launch)
   int w_rows, w_cols;          // gathered matrix: [N, K] when B is K-major (y = x W^T), [K, N] when MN-major (dx = dy W)
+  // Rotation of the work order by this rank's position in the group.  Without it every rank would pull the first
+  // owner's rows first (and push into the first owner's accumulator first): one GPU's links saturated, seven idle.
+  // Each rank starts at the rows it owns itself and walks the owners from there, like the stand-alone kernels do.
+  int rot_m, rot_n;            // tile rows / tile columns by which the tile order is rotated
+  int rot_kb;                  // k-blocks by which the k loop is rotated (gathered reduction dimension)
+  long long fetch_rot;         // 64 KiB chunks by which the fetch order is rotated
 };
 
 constexpr int kModePlain = 0, kModeScatter = 1, kModeGather = 2;
@@ -80,14 +86,16 @@ struct OwnerMaps {   // one fp32 tensor map per owner's accumulator region (kMod
 // that run at the same time share a few A row panels and a few B column panels and both stay in L2 however large
 // the whole operands are.
 constexpr int kGroupM = 16;
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int* tm, int* tn) {
-  const int per_group = kGroupM * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, const Params& p, int* tm, int* tn) {
+  const int per_group = kGroupM * p.tiles_n;
   const int group = tile / per_group;
   const int first_m = group * kGroupM;
-  const int gsize = min(tiles_m - first_m, kGroupM);
+  const int gsize = min(p.tiles_m - first_m, kGroupM);
   const int in_group = tile - group * per_group;
-  *tm = first_m + in_group % gsize;
-  *tn = in_group / gsize;
+  int m = first_m + in_group % gsize + p.rot_m;
+  int n = in_group / gsize + p.rot_n;
+  *tm = m >= p.tiles_m ? m - p.tiles_m : m;
+  *tn = n >= p.tiles_n ? n - p.tiles_n : n;
 }
 
 __device__ __forceinline__ uint32_t pack2(float a, float b) {
@@ -155,9 +163,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       prefetch_tmap(&tmap_a);
       prefetch_tmap(&tmap_b);
       // gather mode: wait (bounded) until every chunk of 256-row group `g` of the gathered matrix is in local memory
-      int groups_ready = 0;
+      uint32_t ready[16] = {0};   // groups already seen complete (the first 512; later ones are re-checked)
       auto wait_group = [&](int g) -> bool {
-        if (g < groups_ready) return true;
+        if (g < 512 && ((ready[g >> 5] >> (g & 31)) & 1u)) return true;
         const long long group_bytes = static_cast<long long>(min(BN, p.w_rows - g * BN)) * p.w_cols * 2;
         const unsigned int target =
             static_cast<unsigned int>((group_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * kFetchWarps;
@@ -175,14 +183,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           __nanosleep(64);
         }
         asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> visible to TMA reads
-        if (p.b_mn) groups_ready = g + 1;  // the reduction dimension is walked in order
+        if (g < 512) ready[g >> 5] |= 1u << (g & 31);
         return true;
       };
       uint32_t it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
-        tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+        tile_coords(tile, p, &tm, &tn);
         const int m0 = tm * 256 + static_cast<int>(cta) * BMH;   // this CTA's rows of A and C
         const int n0 = tn * BN + static_cast<int>(cta) * BNH;    // this CTA's rows of B
         if constexpr (kMode == kModeGather) {
@@ -194,14 +202,14 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint32_t ph = (it / kStages) & 1;
           if constexpr (kMode == kModeGather) {
             // B MN-major (input gradient): the gathered rows are the reduction dimension, 4 k-blocks per group
-            if (p.b_mn && !(ok = wait_group((kb * BK) / BN))) break;
+            if (p.b_mn && !(ok = wait_group((((kb + p.rot_kb) % k_blocks) * BK) / BN))) break;
           }
           if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, wc, 11))) break;
           const uint32_t sa = base + s * kStageBytes;
           const uint32_t sb = sa + kATile;
           if (cta == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2 * kStageBytes);   // bytes of both CTAs
           const uint32_t bar = mapa_shared(full0 + 8 * s, 0);
-          const int k0 = kb * BK;
+          const int k0 = (p.rot_kb ? (kb + p.rot_kb) % k_blocks : kb) * BK;
           if (!p.a_mn) {
             tma_load_2d_pair(sa, &tmap_a, bar, k0, m0);                 // box {64 k, 128 rows}
           } else {
@@ -264,7 +272,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const long long shard_bytes = static_cast<long long>(p.rows_per_rank) * p.w_cols * 2;
     const long long panel_bytes_full = static_cast<long long>(BN) * p.w_cols * 2;  // a multiple of the chunk size
     const long long n_chunks = (total_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes;
-    for (long long c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+    for (long long c0 = blockIdx.x; c0 < n_chunks; c0 += gridDim.x) {
+      const long long c = (c0 + p.fetch_rot) % n_chunks;   // this rank's own rows first, then the next owner's, ...
       const long long byte0 = c * kFetchChunkBytes + fw * kFetchWarpBytes;
       const long long last = min(byte0 + kFetchWarpBytes, total_bytes) - 1;
       const int owner0 = static_cast<int>(byte0 / shard_bytes);
@@ -309,7 +318,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t tempty_leader0 = mapa_shared(tempty0, 0);
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local_tile) {
       int tm, tn;
-      tile_coords(tile, p.tiles_m, p.tiles_n, &tm, &tn);
+      tile_coords(tile, p, &tm, &tn);
       const int m0 = tm * 256 + static_cast<int>(cta) * BMH;
       const int n0 = tn * BN;
       const uint32_t acc = local_tile & 1;
@@ -496,7 +505,8 @@ cudaError_t gemm_bf16_pair(const void* a, const void* b, void* c, int c_kind, co
 cudaError_t gemm_wgrad_scatter_pair(const void* dy, const void* x, int tokens, int n_out, int k_in, long long ld_dy,
                                     long long ld_x, const long long* acc_addrs_host, const long long* ctr_ptrs,
                                     long long acc_offset, int rows_per_rank, int nranks, float scale,
-                                    unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream) {
+                                    unsigned int* done_slot, int* status, int sm_count, cudaStream_t stream,
+                                    int start_rank) {
   using namespace gemm_pair;
   if (n_out < 256 || k_in < 256 || tokens < BK || sm_count < 2) return cudaErrorNotSupported;
   if (nranks > kMaxOwners || (rows_per_rank % BMH) != 0) return cudaErrorNotSupported;
@@ -529,6 +539,7 @@ cudaError_t gemm_wgrad_scatter_pair(const void* dy, const void* x, int tokens, i
   p.status = status;
   p.ctr_ptrs = ctr_ptrs;
   p.rows_per_rank = rows_per_rank; p.nranks = nranks; p.scale = scale; p.done_slot = done_slot;
+  p.rot_m = static_cast<int>((static_cast<long long>(start_rank) * rows_per_rank / 256) % p.tiles_m);
   const int tiles = p.tiles_m * p.tiles_n;
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
   gemm_bf16_pair_kernel<kModeScatter><<<2 * pairs, kThreads, kSmemBytes, stream>>>(ta, tb, ta, owners, p);
@@ -541,7 +552,7 @@ cudaError_t gemm_wgrad_scatter_pair(const void* dy, const void* x, int tokens, i
 cudaError_t gemm_gather_pair(bool dgrad, const void* a, const long long* shard_ptrs, void* w_local, void* out,
                              const void* bias, int M, int w_rows, int w_cols, long long lda, long long ldo,
                              int rows_per_rank, int nranks, unsigned int* group_flags, int* status, int sm_count,
-                             cudaStream_t stream, const void* residual, long long ldr) {
+                             cudaStream_t stream, const void* residual, long long ldr, int start_rank) {
   using namespace gemm_pair;
   const int N = dgrad ? w_cols : w_rows;   // output columns
   const int K = dgrad ? w_rows : w_cols;   // reduction length
@@ -577,6 +588,13 @@ cudaError_t gemm_gather_pair(bool dgrad, const void* a, const long long* shard_p
   p.panel_flags = group_flags;
   p.rows_per_rank = rows_per_rank; p.nranks = nranks;
   p.w_rows = w_rows; p.w_cols = w_cols;
+  {
+    const int groups = (w_rows + BN - 1) / BN;
+    const int rot_group = static_cast<int>((static_cast<long long>(start_rank) * rows_per_rank / BN) % groups);
+    if (!dgrad) p.rot_n = rot_group % p.tiles_n;
+    else p.rot_kb = (rot_group * (BN / BK)) % ((K + BK - 1) / BK);
+    p.fetch_rot = static_cast<long long>(rot_group) * (static_cast<long long>(BN) * w_cols * 2 / kFetchChunkBytes);
+  }
   if (residual != nullptr) {
     if ((ldr % 8) || (reinterpret_cast<uintptr_t>(residual) & 15)) return cudaErrorInvalidValue;
     p.residual = static_cast<const __nv_bfloat16*>(residual);

@@ -105,7 +105,8 @@ def gather_dgrad(dy: torch.Tensor, weight_shard: torch.Tensor, out_features: int
         w_full = torch.empty(out_features, K, dtype=weight_shard.dtype, device=dy.device)
         if dy2.stride(1) != 1:
             dy2 = dy2.contiguous()
-        dx = _ext.load().gemm_gather_dgrad(dy2, table, w_full, rows_per)
+        me = control.rank()
+        dx = _ext.load().gemm_gather_dgrad(dy2, table, w_full, rows_per, ranks.index(me) if me in ranks else 0)
         _count()
     else:
         peers = reg.get_peer_tensors(weight_shard)
@@ -152,8 +153,9 @@ def wgrad_scatter(dy: torch.Tensor, x: torch.Tensor, reduction: ReductionService
         if os.environ.get("ODC_WGRAD_SCATTER", "tma") == "tma":
             # output boxes staged in shared memory and added into the owners by the TMA unit; needs
             # rows_per_rank % 128 == 0 and at most 8 owners, otherwise the per-thread red.add variant runs
+            me = control.rank()
             done = ext.gemm_wgrad_scatter_tma(dy2, x2, reg.peer_ptrs(acc, ranks), reg.peer_ptr_table(reduction.counter, ranks),
-                                              param_offset, rows_per_rank, scale)
+                                              param_offset, rows_per_rank, scale, ranks.index(me) if me in ranks else 0)
         if not done:
             ext.gemm_wgrad_scatter(dy2, x2, reg.peer_ptr_table(acc, ranks), reg.peer_ptr_table(reduction.counter, ranks),
                                    param_offset, rows_per_rank, scale)

@@ -298,7 +298,7 @@ def test_gemm_gather_emulated_ranks(ext, world, M, N, K):
     x = torch.randn(M, K, device="cuda").bfloat16()
     bias = torch.randn(N, device="cuda").bfloat16()
     w_local = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
-    y = ext.gemm_gather(x, _table(shards), w_local, bias, rows_per, 1 % world)
+    y = ext.gemm_gather(x, _table(shards), w_local, bias, rows_per, (world - 1) if world > 2 else 1 % world)
     torch.cuda.synchronize()
     assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
     assert torch.equal(w_local, W[:N])
@@ -315,7 +315,7 @@ def test_gemm_gather_dgrad_emulated_ranks(ext, world, M, N, K):
     shards = [W[r * rows_per:(r + 1) * rows_per].clone() for r in range(world)]
     dy = torch.randn(M, N, device="cuda").bfloat16()
     w_local = torch.zeros(N, K, dtype=torch.bfloat16, device="cuda")
-    dx = ext.gemm_gather_dgrad(dy, _table(shards), w_local, rows_per)
+    dx = ext.gemm_gather_dgrad(dy, _table(shards), w_local, rows_per, (world * 5 + 3) % world if world > 2 else world - 1)
     torch.cuda.synchronize()
     assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
     assert torch.equal(w_local, W[:N])
@@ -349,7 +349,9 @@ def test_wgrad_scatter_tma_emulated_ranks(ext, world, T, n_out, k_in):
     for producer in range(2):
         dy = torch.randn(T, n_out, device="cuda").bfloat16()
         x = torch.randn(T, k_in, device="cuda").bfloat16()
-        assert ext.gemm_wgrad_scatter_tma(dy, x, [a.data_ptr() for a in accs], _table(ctrs), off, rows_per, 0.5)
+        # the producer's position in the group only rotates the order in which the owners' tiles are produced
+        assert ext.gemm_wgrad_scatter_tma(dy, x, [a.data_ptr() for a in accs], _table(ctrs), off, rows_per, 0.5,
+                                          (producer * 5 + 1) % world)
         want[:n_out] += 0.5 * (dy.float().t() @ x.float())
     torch.cuda.synchronize()
     assert ext.kernel_status()[0].item() == 0
