@@ -1,10 +1,16 @@
 """CUDA kernels against plain PyTorch fp32 references (single GPU; peers emulated by local buffers)."""
 import math
+import os
 
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+
+# The fused GEMMs can start their walk over the owners at the calling rank's own rows (off by default, read once per
+# process).  Switched on here so that the emulated-rank cases below, which pass non-zero positions, cover the rotated
+# tile, fetch and k orders; position 0 and the other test files cover the unrotated order.
+os.environ.setdefault("ODC_GEMM_ROTATE", "2")
 
 
 @pytest.fixture(scope="module")
