@@ -1,7 +1,10 @@
 """Headline benchmark: training tokens/s on imbalanced variable-length minibatches.
 
 Default workload (--config 3): Llama-3.2-1B-shaped decoder, bf16 compute with fp32 gradient
-accumulation, FSDP2 full shard over N GPUs through this package's on-demand engine; each
+accumulation, parameters, gradients and optimizer state fully sharded over N GPUs, trained through this
+package's on-demand engine (default: the fused-kernel engine, whose linears pull weight shards inside the GEMM
+kernel and reduce weight gradients into their owners from the GEMM epilogue after every microbatch;
+``--engine fsdp2`` runs the on-demand patch of PyTorch FSDP2 instead); each
 minibatch is 8 microbatches per rank, each packed up to 16384 tokens from log-normal sequence
 lengths (median 512, sigma 1.0, cap 8192) seeded independently per rank.  Synthetic token ids,
 random-init weights.  One "step" = one minibatch = forward+backward of every microbatch, the
@@ -175,7 +178,7 @@ def _run_reference(args, odc, ref_fsdp2, line):
 
 # ------------------------------------------------------------------------------------------------------------
 PRESETS = {
-    "3": dict(model="llama3.2-1b", microbatches=8, token_budget=16384, engine="fsdp2", hsdp=False, hpz=0, ac=False,
+    "3": dict(model="llama3.2-1b", microbatches=8, token_budget=16384, engine="fused", hsdp=False, hpz=0, ac=False,
               spec=("lognormal", dict(lo=16, median=512.0, sigma=1.0, cap=8192)),
               seq="lognormal(median 512, sigma 1.0, cap 8192), packed"),
     "4": dict(model="llama3-8b", microbatches=16, token_budget=32768, engine="fsdp2", hsdp=True, hpz=4, ac=True,
@@ -209,7 +212,7 @@ class Arm:
             odc.init_nvshmem(device)
             self.model = FusedDecoderLM(cfg, device=device, seed=0)
             self.opt = FusedOptimizer(self.model, lr=1e-4, weight_decay=0.01)
-            self.parallelism = f"fused-dp{world}"
+            self.parallelism = f"full-shard-dp{world} (fused gather+GEMM / weight-gradient+scatter engine)"
             self.optimizer = "fused"
         elif engine == "fsdp1":
             from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
