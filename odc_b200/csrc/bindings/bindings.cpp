@@ -209,7 +209,8 @@ std::tuple<Tensor, Tensor> rmsnorm_fwd(Tensor x, Tensor w, double eps) {
   return {y, rstd};
 }
 
-std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, bool fixed_order) {
+std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd, bool fixed_order,
+                                       c10::optional<Tensor> dres) {
   c10::cuda::CUDAGuard g(x.device());
   odc::bind_device(x.get_device());
   TORCH_CHECK(dy.is_contiguous() && x.is_contiguous() && dy.sizes() == x.sizes(), "rmsnorm_bwd: contiguous dy, x [T,H]");
@@ -223,8 +224,14 @@ std::tuple<Tensor, Tensor> rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rst
     partial = torch::empty({grid, cols}, x.options().dtype(at::kFloat));
     partial_ptr = partial.data_ptr<float>();
   }
+  const void* dres_ptr = nullptr;
+  if (dres.has_value()) {
+    TORCH_CHECK(dres->is_contiguous() && dres->sizes() == x.sizes() && dres->scalar_type() == at::kBFloat16,
+                "rmsnorm_bwd: residual gradient must be contiguous bf16 of x's shape");
+    dres_ptr = dres->data_ptr();
+  }
   check(odc::launch_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
-                                partial_ptr, dw.data_ptr<float>(), rows, cols, grid, cur_stream()),
+                                partial_ptr, dw.data_ptr<float>(), rows, cols, grid, cur_stream(), dres_ptr),
         "rmsnorm_bwd");
   return {dx, dw};
 }
@@ -585,7 +592,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wait_posted", &wait_posted);
   m.def("rmsnorm_fwd", &rmsnorm_fwd);
   m.def("rmsnorm_bwd", &rmsnorm_bwd, py::arg("dy"), py::arg("x"), py::arg("w"), py::arg("rstd"),
-        py::arg("fixed_order") = false);
+        py::arg("fixed_order") = false, py::arg("dres") = py::none());
   m.def("rope_qkv", &rope_qkv);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

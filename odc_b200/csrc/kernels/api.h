@@ -66,9 +66,11 @@ cudaError_t launch_grid_barrier_test(unsigned int* counter, int* slots, int* out
 // ---- elementwise / normalisation (bf16 activations, fp32 math) -----------------------------
 cudaError_t launch_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int rows, int cols, float eps,
                                int sm_count, cudaStream_t stream);
-// partial: [grid, cols] fp32 scratch, dw: [cols] fp32
+// partial: [grid, cols] fp32 scratch (nullptr: in-kernel atomics into dw), dw: [cols] fp32; dres: optional bf16
+// [rows, cols] gradient that reached x through a residual connection, added to dx in the same pass
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
-                               float* partial, float* dw, int rows, int cols, int grid, cudaStream_t stream);
+                               float* partial, float* dw, int rows, int cols, int grid, cudaStream_t stream,
+                               const void* dres = nullptr);
 int rmsnorm_bwd_grid(int rows, int sm_count);
 cudaError_t launch_rope_qkv(const void* in, void* out, const long long* pos, int tokens, int n_q, int n_kv,
                             int head_dim, float theta, bool inverse, cudaStream_t stream);

@@ -142,7 +142,7 @@ template <int R, int V, bool kAtomic>
 __global__ void __launch_bounds__(kNormThreads, 2)
 rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, const bf16* __restrict__ w,
                    const float* __restrict__ rstd_in, bf16* __restrict__ dx, float* __restrict__ partial,
-                   float* __restrict__ dw_out, int rows, int cols) {
+                   float* __restrict__ dw_out, int rows, int cols, const bf16* __restrict__ dres) {
   extern __shared__ float dw_smem[];  // [cols]
   __shared__ float red[kNormWarps];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -202,6 +202,12 @@ rmsnorm_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ x, cons
         unpack8(wr[v], wf);
 #pragma unroll
         for (int i = 0; i < 8; ++i) o[i] = rstd * (gf[i] * wf[i] - xf[i] * c);
+        if (dres != nullptr) {  // gradient that reached x through the residual path: one pass instead of a separate add
+          float rf[8];
+          unpack8(reinterpret_cast<const uint4*>(dres + size_t(row) * cols)[v], rf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += rf[i];
+        }
         dr[v] = pack8(o);
       }
     }
@@ -457,15 +463,15 @@ cudaError_t rmsnorm_fwd_t(const void* x, const void* w, void* y, float* rstd, in
 
 template <int R, int V>
 cudaError_t rmsnorm_bwd_t(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* partial,
-                          float* dw, int rows, int cols, int grid, cudaStream_t stream) {
+                          float* dw, int rows, int cols, int grid, cudaStream_t stream, const void* dres) {
   if (partial == nullptr) {
     rmsnorm_bwd_kernel<R, V, true><<<grid, kNormThreads, cols * sizeof(float), stream>>>(
         static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
-        static_cast<bf16*>(dx), nullptr, dw, rows, cols);
+        static_cast<bf16*>(dx), nullptr, dw, rows, cols, static_cast<const bf16*>(dres));
   } else {
     rmsnorm_bwd_kernel<R, V, false><<<grid, kNormThreads, cols * sizeof(float), stream>>>(
         static_cast<const bf16*>(dy), static_cast<const bf16*>(x), static_cast<const bf16*>(w), rstd,
-        static_cast<bf16*>(dx), partial, dw, rows, cols);
+        static_cast<bf16*>(dx), partial, dw, rows, cols, static_cast<const bf16*>(dres));
   }
   return cudaGetLastError();
 }
@@ -490,7 +496,8 @@ int rmsnorm_bwd_grid(int rows, int sm_count) {
 // partial == nullptr: single launch, the CTAs add their column sums into dw (zeroed here first; the order of the
 // additions varies from run to run).  partial = [grid, cols] scratch: per-CTA sums, then a fixed-order column pass.
 cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
-                               float* partial, float* dw, int rows, int cols, int grid, cudaStream_t stream) {
+                               float* partial, float* dw, int rows, int cols, int grid, cudaStream_t stream,
+                               const void* dres) {
   if (cols % 8 != 0 || cols > 8192) return cudaErrorInvalidValue;
   cudaError_t e;
   if (partial == nullptr) {
@@ -498,10 +505,10 @@ cudaError_t launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
     if (e != cudaSuccess) return e;
     if (rows == 0) return cudaSuccess;
   }
-  if (cols <= 1024) e = rmsnorm_bwd_t<1, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
-  else if (cols <= 2048) e = rmsnorm_bwd_t<2, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
-  else if (cols <= 4096) e = rmsnorm_bwd_t<4, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
-  else e = rmsnorm_bwd_t<8, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream);
+  if (cols <= 1024) e = rmsnorm_bwd_t<1, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream, dres);
+  else if (cols <= 2048) e = rmsnorm_bwd_t<2, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream, dres);
+  else if (cols <= 4096) e = rmsnorm_bwd_t<4, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream, dres);
+  else e = rmsnorm_bwd_t<8, 4>(dy, x, w, rstd, dx, partial, dw, rows, cols, grid, stream, dres);
   if (e != cudaSuccess) return e;
   if (partial != nullptr) {
     colsum_kernel<<<(cols + 255) / 256, 256, 0, stream>>>(partial, dw, grid, cols);

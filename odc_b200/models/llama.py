@@ -89,6 +89,10 @@ class RMSNorm(nn.Module):
     def forward(self, x):
         return ops.rms_norm(x, self.weight, self.eps)
 
+    def with_residual(self, x):
+        """``(norm(x), x)``; backward folds the residual path's gradient into the norm's backward kernel."""
+        return ops.rms_norm_residual(x, self.weight, self.eps)
+
 
 class Attention(nn.Module):
     def __init__(self, cfg: DecoderConfig):
@@ -127,8 +131,10 @@ class DecoderLayer(nn.Module):
         self.mlp = MLP(cfg)
 
     def forward(self, x, position_ids, cu_seqlens, max_seqlen):
-        x = self.attn(self.attn_norm(x), position_ids, cu_seqlens, max_seqlen, residual=x)
-        return self.mlp(self.mlp_norm(x), residual=x)
+        h, x = self.attn_norm.with_residual(x)
+        x = self.attn(h, position_ids, cu_seqlens, max_seqlen, residual=x)
+        h, x = self.mlp_norm.with_residual(x)
+        return self.mlp(h, residual=x)
 
 
 class DecoderLM(nn.Module):

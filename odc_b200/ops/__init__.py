@@ -159,6 +159,39 @@ def rms_norm(x, weight, eps: float = 1e-6):
     return _RMSNorm.apply(x.contiguous(), weight, eps)
 
 
+class _RMSNormResidual(torch.autograd.Function):
+    """``(rms_norm(x), x)``: the second output carries the residual stream.  Its gradient and the normalised
+    branch's gradient meet again in backward, where ONE kernel forms ``d rms_norm + d residual`` (autograd would
+    otherwise add the two with a separate full pass over the activation)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        x2 = x.reshape(-1, x.shape[-1])
+        y, rstd = _ext().rmsnorm_fwd(x2, weight, eps)
+        _count()
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape), x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x2, weight, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dr2 = None if dres is None else dres.reshape(-1, dres.shape[-1]).contiguous()
+        from .. import config
+        fixed = config.deterministic()
+        dx, dw = _ext().rmsnorm_bwd(dy2, x2, weight, rstd, fixed, dr2)
+        _count(2 if fixed else 1)
+        return dx.view(ctx.shape), dw.to(weight.dtype), None
+
+
+def rms_norm_residual(x, weight, eps: float = 1e-6):
+    """``(rms_norm(x, weight), x)`` for pre-norm blocks: feed the second value to the block's residual add."""
+    if not x.is_cuda:
+        return ref.rms_norm(x, weight, eps), x
+    return _RMSNormResidual.apply(x.contiguous(), weight, eps)
+
+
 # ------------------------------------------------------------------------------------------
 class _Rope(torch.autograd.Function):
     """Rotary embedding applied to the q and k heads of a fused ``[T, (Hq+2Hkv)*D]`` projection."""
@@ -307,9 +340,11 @@ class _LinearCrossEntropy(torch.autograd.Function):
         ext = _ext()
         need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
         dh = torch.empty_like(h) if need_dh else None
-        dw32 = torch.zeros(V, H, dtype=torch.float32, device=h.device) if need_dw else None
+        dw32 = torch.empty(V, H, dtype=torch.float32, device=h.device) if need_dw else None  # written by the first chunk
         loss = torch.zeros((), dtype=torch.float32, device=h.device)
         logits = torch.empty(min(chunk, T), V, dtype=torch.bfloat16, device=h.device)
+        if T == 0 and dw32 is not None:
+            dw32.zero_()
         for s in range(0, T, chunk):
             e = min(T, s + chunk)
             lg = logits[: e - s]
@@ -320,7 +355,7 @@ class _LinearCrossEntropy(torch.autograd.Function):
             if need_dh:
                 gemm(lg, w, "nn", out=dh[s:e])
             if need_dw:
-                gemm(lg, h[s:e], "tn", out=dw32, accumulate=True)
+                gemm(lg, h[s:e], "tn", out=dw32, accumulate=s > 0)
         ctx.save_for_backward(dh, dw32)
         ctx.w_dtype = w.dtype
         return loss

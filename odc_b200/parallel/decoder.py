@@ -149,9 +149,11 @@ class _FusedLinearCrossEntropy(torch.autograd.Function):
             T, H = h.shape
             ext = ops._ext()
             dh = torch.empty_like(h)
-            dw32 = torch.zeros(p.out_features, H, dtype=torch.float32, device=h.device)
+            dw32 = torch.empty(p.out_features, H, dtype=torch.float32, device=h.device)  # written by the first chunk
             loss = torch.zeros((), dtype=torch.float32, device=h.device)
             logits = torch.empty(min(chunk, T), p.out_features, dtype=torch.bfloat16, device=h.device)
+            if T == 0:
+                dw32.zero_()
             for s in range(0, T, chunk):
                 e = min(T, s + chunk)
                 lg = logits[: e - s]
@@ -159,7 +161,7 @@ class _FusedLinearCrossEntropy(torch.autograd.Function):
                 ext.ce_fwd_bwd(lg, labels[s:e], None if loss_scale is None else loss_scale[s:e], loss, ignore_index)
                 ops._count()
                 ops.gemm(lg, w, "nn", out=dh[s:e])
-                ops.gemm(lg, h[s:e], "tn", out=dw32, accumulate=True)
+                ops.gemm(lg, h[s:e], "tn", out=dw32, accumulate=s > 0)
         else:
             with torch.enable_grad():
                 h_ = h.detach().requires_grad_()
@@ -199,13 +201,13 @@ class FusedDecoderLayer(nn.Module):
     def forward(self, x, position_ids, cu_seqlens, max_seqlen):
         c, s, i = self.cfg, self.small, self.i
         T = x.shape[0]
-        h = ops.rms_norm(x, s.view(f"layers.{i}.attn_norm.weight", (c.hidden_size,)), c.rms_eps)
+        h, x = ops.rms_norm_residual(x, s.view(f"layers.{i}.attn_norm.weight", (c.hidden_size,)), c.rms_eps)
         bias = s.view(f"layers.{i}.attn.bqkv", (c.qkv_dim,)) if c.qkv_bias else None
         qkv = self.wqkv(h, bias=bias)
         qkv = ops.rope_qkv(qkv, position_ids, c.num_heads, c.num_kv_heads, c.head_dim, c.rope_theta)
         o = ops.varlen_attention_qkv(qkv, c.num_heads, c.num_kv_heads, c.head_dim, cu_seqlens, max_seqlen, causal=True)
         x = self.wo(o.reshape(T, c.num_heads * c.head_dim), residual=x)
-        h = ops.rms_norm(x, s.view(f"layers.{i}.mlp_norm.weight", (c.hidden_size,)), c.rms_eps)
+        h, x = ops.rms_norm_residual(x, s.view(f"layers.{i}.mlp_norm.weight", (c.hidden_size,)), c.rms_eps)
         return self.w_down(ops.swiglu(self.w_gate_up(h)), residual=x)
 
 

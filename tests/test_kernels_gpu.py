@@ -230,6 +230,10 @@ def test_gemm_cta_pair_layouts(ext, layout, M, N, K):
     torch.cuda.synchronize()
     assert ext.kernel_status()[0].item() == 0, ext.kernel_status().tolist()
     torch.testing.assert_close(c32, want + 1 + bias.float(), rtol=1e-2, atol=1e-2 * math.sqrt(K))
+    # fp32 output, plain store over whatever the buffer held
+    c32.fill_(float("nan"))
+    ext.gemm(a, b, c32, layout, None, False, None, 1)
+    torch.testing.assert_close(c32, want, rtol=1e-2, atol=1e-2 * math.sqrt(K))
 
 
 def test_linear_autograd_matches_reference():
@@ -512,3 +516,28 @@ def test_posted_counts_and_bounded_wait(ext):
     ext.wait_posted(slots, nprod, 2, ctr, 50, status, expected)
     torch.cuda.synchronize()
     assert status[:3].tolist() == [1, 0, sum(counts)] and int(expected[0]) == sum(counts) + nprod
+
+
+def test_rmsnorm_residual_backward_fuses_the_residual_gradient():
+    """(norm(x), x): the gradient of the pass-through output is added inside the norm's backward kernel."""
+    from odc_b200 import ops
+    rows, cols = 777, 2048
+    x = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_()
+    w = (1 + 0.1 * torch.randn(cols, device="cuda")).bfloat16().requires_grad_()
+    y, xr = ops.rms_norm_residual(x, w, 1e-5)
+    dy, dres = torch.randn_like(y), torch.randn_like(xr)
+    torch.autograd.backward([y, xr], [dy, dres])
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf
+    torch.autograd.backward([yf, xf * 1.0], [dy.float(), dres.float()])
+    torch.testing.assert_close(y.float(), yf, rtol=2e-2, atol=2e-2)
+    assert xr.data_ptr() == x.data_ptr()
+    torch.testing.assert_close(x.grad.float(), xf.grad, rtol=2e-2, atol=3e-2)
+    torch.testing.assert_close(w.grad.float(), wf.grad, rtol=2e-2, atol=rows ** 0.5 * 2e-2)
+    # only the normalised branch is used: the pass-through gradient is absent
+    x2 = x.detach().clone().requires_grad_()
+    y2, _ = ops.rms_norm_residual(x2, w.detach(), 1e-5)
+    y2.backward(dy)
+    xg = x.detach().float().requires_grad_()
+    (xg * torch.rsqrt(xg.pow(2).mean(-1, keepdim=True) + 1e-5) * w.detach().float()).backward(dy.float())
+    torch.testing.assert_close(x2.grad.float(), xg.grad, rtol=2e-2, atol=3e-2)
