@@ -12,7 +12,7 @@
 //   warps 2..5  : epilogue of this CTA's 128 rows (tcgen05.ld -> bias / residual -> swizzled staging -> TMA store),
 //                 then a (remote) arrive on the leader's "accumulator free" barrier
 // Two accumulators (all 512 TMEM columns of each CTA) alternate, so the epilogue of one tile overlaps the main
-// loop of the next.  No load in this file uses cluster multicast.  Every wait is bounded and reports through the
+// loop of the next.  Every copy in this file is an ordinary per-CTA TMA copy into that CTA's own shared memory.  Every wait is bounded and reports through the
 // status word; a pair whose partner gave up runs into its own bounded waits and leaves the same way.
 //
 // Operand layouts, edge handling and the epilogue are those of the single-CTA kernel (gemm_tcgen05.cu).
