@@ -1,6 +1,6 @@
 """LLM trainer on FSDP2 (counterpart of the reference's examples/llm_training/torch_fsdp2.py).
 
-Environment switches: ``ODC`` (default 1), ``HPZ``, ``HSDP``; ``TORCH_PROFILED=1`` writes a chrome
+Environment switches: ``ODC`` (default 1), ``HPZ``, ``HSDP``, ``ENGINE=fused`` (the fused-kernel decoder engine); ``TORCH_PROFILED=1`` writes a chrome
 trace per rank; ``CUDA_PROFILED=1`` brackets the last minibatch with cudaProfilerStart/Stop.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -24,6 +24,8 @@ from odc_b200.models import DecoderLM, get_config
 from odc_b200.utils.nvtx import nvtx_range
 
 ODC = os.environ.get("ODC", "1") == "1"
+# ENGINE=fused: the decoder on the fused gather+GEMM / weight-gradient+scatter kernels instead of the FSDP2 patch
+FUSED = os.environ.get("ENGINE", "fsdp2") == "fused"
 HPZ = os.environ.get("HPZ", "0") == "1"
 HSDP = os.environ.get("HSDP", "0") == "1"
 
@@ -33,6 +35,8 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = init_device(args, rank)
     cfg = get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)
+    if FUSED:
+        return main_fused(args, cfg, dev, rank, world)
     if ODC:
         odc.init_nvshmem(dev)
         fsdp2.patch_fsdp2(enable_hpz=HPZ)
@@ -117,6 +121,49 @@ def main():
     mark_done(args)
     if ODC:
         fsdp2.stop()
+    dist.destroy_process_group()
+
+
+def main_fused(args, cfg, dev, rank, world):
+    """The same loop on ``FusedDecoderLM``: start_minibatch / microbatches / finish_minibatch / optimizer step."""
+    from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
+    odc.init_nvshmem(dev)
+    model = FusedDecoderLM(cfg, device=dev, seed=0)
+    opt = FusedOptimizer(model, lr=args.lr, weight_decay=0.01)
+    data = make_dataset(args, cfg, rank, world, True)
+    steps = min(args.steps, len(data))
+    for step in range(steps):
+        times = {}
+        microbatches = data[step]
+        with Timer("minibatch_time", times):
+            model.start_minibatch()
+            total = torch.zeros((), device=dev)
+            tokens = 0
+            for mb in microbatches:
+                with nvtx_range("microbatch"):
+                    mb = to_device(mb, dev)
+                    tokens += mb["num_tokens"]
+                    with torch.set_grad_enabled(not args.forward_only):
+                        loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"],
+                                     labels=mb["labels"], loss_scale=mb["loss_scale"])
+                    if not args.forward_only:
+                        loss.backward()
+                    total += loss.detach()
+            grad_norm = 0.0
+            if not args.forward_only:
+                with Timer("sync_time", times):
+                    model.finish_minibatch()
+                with Timer("optimizer_step_time", times):
+                    grad_norm = float(opt.clip_grad_norm_(1.0))
+                    opt.step()
+        dist.all_reduce(total)
+        tok = torch.tensor([tokens], device=dev)
+        dist.all_reduce(tok)
+        log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
+                                 "tokens_per_s": int(tok) / times["minibatch_time"], "grad_norm": grad_norm, **times,
+                                 **memory_metrics()})
+    mark_done(args)
+    model.stop()
     dist.destroy_process_group()
 
 

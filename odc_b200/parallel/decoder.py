@@ -397,6 +397,11 @@ class FusedOptimizer:
 
     @torch.no_grad()
     def load_full_state_dict(self, sd: Dict) -> None:
+        if "exp_avg" not in sd:   # the layout a full torch.optim.AdamW state dict has (state by parameter name)
+            st = sd["state"]
+            sd = {"step": max((int(float(e["step"])) for e in st.values()), default=0),
+                  "exp_avg": {k: e["exp_avg"] for k, e in st.items()},
+                  "exp_avg_sq": {k: e["exp_avg_sq"] for k, e in st.items()}}
         self.step_count = int(sd["step"])
         for name, p in self.model.matrices().items():
             dev = p.master.device

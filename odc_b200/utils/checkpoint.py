@@ -1,5 +1,8 @@
 """Save / load full model and optimizer state of an FSDP2 model whose shards live in the symmetric heap.
 
+Also takes the fused-kernel decoder (:class:`odc_b200.parallel.FusedDecoderLM` + ``FusedOptimizer``), whose model
+file has the same names and shapes as ``DecoderLM``'s, so a model checkpoint moves between the two engines.
+
 Same capability as the reference's example ``Checkpointer`` (examples/FSDP2/checkpoint.py:38-210):
 two interchangeable back ends — the distributed-checkpoint state-dict API, or explicit DTensor
 ``full_tensor`` / ``distribute_tensor`` — writing ``model_state_dict.pt`` / ``optim_state_dict.pt``
@@ -43,6 +46,9 @@ class Checkpointer:
     def load_model(self, model) -> None:
         path = os.path.join(self.folder, self.last_training_time, MODEL_FILE)
         full = torch.load(path, mmap=True, weights_only=True, map_location="cpu")
+        if hasattr(model, "load_full_state_dict"):  # fused-kernel decoder: whole tensors under DecoderLM's names
+            model.load_full_state_dict(full)
+            return
         if self.dcp_api:
             set_model_state_dict(model, full, options=StateDictOptions(full_state_dict=True, broadcast_from_rank0=True))
             return
@@ -65,6 +71,8 @@ class Checkpointer:
 
     # ------------------------------------------------------------------ save
     def _model_state(self, model):
+        if hasattr(model, "full_state_dict"):  # fused-kernel decoder (collective); same names and shapes as DecoderLM
+            return {k: v.cpu() for k, v in model.full_state_dict().items()}
         if self.dcp_api:
             return get_model_state_dict(model, options=StateDictOptions(full_state_dict=True, cpu_offload=True))
         out = {}

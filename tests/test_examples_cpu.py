@@ -31,6 +31,7 @@ def test_fsdp2_example_cpu(env, tmp_path):
     ("train_fsdp2.py", {"ODC": "1"}, "DynamicDiffMicro"),      # ranks get different numbers of microbatches
     ("train_fsdp2.py", {"ODC": "0"}, "DynamicSameMicro"),      # lock-step baseline
     ("train_fsdp1.py", {"ODC": "1"}, "DynamicDiffMicro"),
+    ("train_fsdp2.py", {"ENGINE": "fused"}, "DynamicDiffMicro"),   # the fused-kernel decoder engine
 ])
 def test_llm_trainers_cpu(script, env, packing, tmp_path):
     e = dict(os.environ, **env, ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path))
@@ -51,10 +52,19 @@ def test_llm_trainers_cpu(script, env, packing, tmp_path):
 @pytest.mark.parametrize("script", ["all_gather.py", "reduce_scatter.py"])
 def test_primitive_benchmarks_cpu(script, tmp_path):
     """The two micro-benchmarks check their result against the library collective; run them small on CPU ranks."""
+    _run_prim_bench(script, tmp_path, [])
+
+
+def test_gather_random_subsets_cpu(tmp_path):
+    """``all_gather.py --peers=random``: every rank pulls random subsets of its peers (3 CPU ranks)."""
+    _run_prim_bench("all_gather.py", tmp_path, ["--peers=random"], world=3)
+
+
+def _run_prim_bench(script, tmp_path, extra, world=2):
     e = dict(os.environ, ODC_BENCH_CPU="1", ODC_SYMMETRIC_SIZE="64M", ODC_OUT_DIR=str(tmp_path))
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world), "--master-addr",
            "127.0.0.1", "--master-port", str(_free_port()), os.path.join(REPO, "examples", script),
-           "--size-min=4096", "--size-max=65536"]
+           "--size-min=4096", "--size-max=65536"] + extra
     r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     out = [f for f in os.listdir(tmp_path) if f.endswith(".json")]
