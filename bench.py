@@ -76,9 +76,10 @@ def reference_arm(args):
     """Run the unmodified reference from baseline/_ref through its own API, or say why not."""
     ref = os.path.join(REPO, "baseline", "_ref")
     line = {"impl": "reference"}
+    say = (lambda l: print(json.dumps(l))) if int(os.environ.get("RANK", "0")) == 0 else (lambda l: None)  # one line per job
     if not os.path.isdir(os.path.join(ref, "odc")):
         line["unavailable"] = "baseline/_ref/odc missing: the reference was not installed"
-        print(json.dumps(line)); return 0
+        say(line); return 0
     sys.path.insert(0, ref)
     try:
         import odc  # noqa: F401
@@ -86,12 +87,12 @@ def reference_arm(args):
     except Exception as e:  # the reference imports nvshmem4py (nvshmem.core) and cuda.core at import time
         line["unavailable"] = (f"reference installed with --no-deps but `import odc` fails: {type(e).__name__}: {e}; "
                                "nvshmem4py / cuda-core are not in the image or the offline wheelhouse")
-        print(json.dumps(line)); return 0
+        say(line); return 0
     try:
         return _run_reference(args, odc, ref_fsdp2, line)
     except Exception as e:
         line["unavailable"] = f"reference imported but its training step failed: {type(e).__name__}: {e}"[:400]
-        print(json.dumps(line)); return 0
+        say(line); return 0
 
 
 def _run_reference(args, odc, ref_fsdp2, line):
