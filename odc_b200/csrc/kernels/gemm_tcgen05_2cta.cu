@@ -163,9 +163,17 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       prefetch_tmap(&tmap_a);
       prefetch_tmap(&tmap_b);
       // gather mode: wait (bounded) until every chunk of 256-row group `g` of the gathered matrix is in local memory
-      uint32_t ready[16] = {0};   // groups already seen complete (the first 512; later ones are re-checked)
+      // groups already known complete: in address order a running count is enough (the reduction dimension is
+      // walked front to back); a rotated walk keeps a bitmask of the first 512 groups (later ones are re-checked)
+      int groups_ready = 0;
+      uint32_t ready[16] = {0};
+      const bool rotated = p.rot_kb != 0 || p.rot_n != 0;
       auto wait_group = [&](int g) -> bool {
-        if (g < 512 && ((ready[g >> 5] >> (g & 31)) & 1u)) return true;
+        if (!rotated) {
+          if (g < groups_ready) return true;
+        } else if (g < 512 && ((ready[g >> 5] >> (g & 31)) & 1u)) {
+          return true;
+        }
         const long long group_bytes = static_cast<long long>(min(BN, p.w_rows - g * BN)) * p.w_cols * 2;
         const unsigned int target =
             static_cast<unsigned int>((group_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes) * kFetchWarps;
@@ -183,7 +191,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           __nanosleep(64);
         }
         asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> visible to TMA reads
-        if (g < 512) ready[g >> 5] |= 1u << (g & 31);
+        if (!rotated) {
+          if (p.b_mn) groups_ready = g + 1;
+        } else if (g < 512) {
+          ready[g >> 5] |= 1u << (g & 31);
+        }
         return true;
       };
       uint32_t it = 0;
@@ -202,7 +214,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
           const uint32_t ph = (it / kStages) & 1;
           if constexpr (kMode == kModeGather) {
             // B MN-major (input gradient): the gathered rows are the reduction dimension, 4 k-blocks per group
-            if (p.b_mn && !(ok = wait_group((((kb + p.rot_kb) % k_blocks) * BK) / BN))) break;
+            if (p.b_mn && !(ok = wait_group(((p.rot_kb ? (kb + p.rot_kb) % k_blocks : kb) * BK) / BN))) break;
           }
           if (!(ok = mbar_wait(empty0 + 8 * s, ph ^ 1, wc, 11))) break;
           const uint32_t sa = base + s * kStageBytes;
@@ -273,7 +285,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const long long panel_bytes_full = static_cast<long long>(BN) * p.w_cols * 2;  // a multiple of the chunk size
     const long long n_chunks = (total_bytes + kFetchChunkBytes - 1) / kFetchChunkBytes;
     for (long long c0 = blockIdx.x; c0 < n_chunks; c0 += gridDim.x) {
-      const long long c = (c0 + p.fetch_rot) % n_chunks;   // this rank's own rows first, then the next owner's, ...
+      // rotated: this rank's own rows first, then the next owner's, ...
+      const long long c = p.fetch_rot ? (c0 + p.fetch_rot) % n_chunks : c0;
       const long long byte0 = c * kFetchChunkBytes + fw * kFetchWarpBytes;
       const long long last = min(byte0 + kFetchWarpBytes, total_bytes) - 1;
       const int owner0 = static_cast<int>(byte0 / shard_bytes);
