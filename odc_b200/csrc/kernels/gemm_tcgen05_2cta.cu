@@ -457,9 +457,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
 // ODC_GEMM_ROTATE: 0 (default) every rank walks the owners in address order; 1: the forward gather and the
 // weight-gradient scatter start at the rank's own rows and walk the owners from there; 2: the input-gradient
-// gather (rotated k loop) as well.  Measured on 8 GPUs, rotation makes the stand-alone forward kernels faster
-// (0.863 -> 0.799 ms and 1.247 -> 0.766 ms on the two widest weights) but the input-gradient kernel and the
-// whole training step slower (1162 -> 1234 ms per step), so it is off unless asked for.
+// gather (rotated k loop) as well.  Measured on 8 GPUs with all ranks launching the same kernel at once, rotation
+// makes the forward kernels faster (0.863 -> 0.799 ms and 1.247 -> 0.766 ms on the two widest weights) and the
+// input-gradient kernel slower; a whole training step, where ranks are not in lock-step anyway, measured slower with
+// it, so it is off unless asked for.
 static int rotate_mode() {
   static const int mode = [] {
     const char* e = getenv("ODC_GEMM_ROTATE");
