@@ -699,25 +699,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   }
 }
 
-// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d]; one warp per (token, head)
+// delta[h, t] = sum_d dO[t, h, d] * O[t, h, d].  A thread takes 16 bytes of both tensors; the D/8 threads of one
+// (token, head) pair are neighbours in a warp and combine with shuffles.  A CTA covers 256 / (D/8) consecutive
+// tokens and walks the heads, so the loads of a warp are whole 128-byte rows and the stores of one head form one
+// contiguous run of tokens.
+template <int D>
 __global__ void __launch_bounds__(256)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ o, float* __restrict__ delta,
-                  int total_tokens, int n_q, int d, long long do_stride, long long o_stride) {
-  const long long w = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (w >= static_cast<long long>(total_tokens) * n_q) return;
-  const int t = static_cast<int>(w / n_q), h = static_cast<int>(w % n_q);
-  const __nv_bfloat16* a = dout + t * do_stride + h * d;
-  const __nv_bfloat16* b = o + t * o_stride + h * d;
-  float s = 0.f;
-  for (int i = lane * 2; i < d; i += 64) {
-    const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(a + i);
-    const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(b + i);
-    s += __bfloat162float(x.x) * __bfloat162float(y.x) + __bfloat162float(x.y) * __bfloat162float(y.y);
-  }
+                  int total_tokens, int n_q, long long do_stride, long long o_stride) {
+  constexpr int kLanes = D / 8;               // threads per (token, head)
+  constexpr int kTokens = 256 / kLanes;       // tokens per CTA
+  const int part = threadIdx.x % kLanes;
+  const int t = blockIdx.x * kTokens + threadIdx.x / kLanes;
+  const bool live = t < total_tokens;
+  const __nv_bfloat16* a = dout + static_cast<long long>(live ? t : 0) * do_stride + part * 8;
+  const __nv_bfloat16* b = o + static_cast<long long>(live ? t : 0) * o_stride + part * 8;
+  for (int h = 0; h < n_q; ++h) {
+    float s = 0.f;
+    if (live) {
+      const uint4 x = *reinterpret_cast<const uint4*>(a + h * D);
+      const uint4 y = *reinterpret_cast<const uint4*>(b + h * D);
+      const uint32_t xs[4] = {x.x, x.y, x.z, x.w}, ys[4] = {y.x, y.y, y.z, y.w};
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) delta[static_cast<long long>(h) * total_tokens + t] = s;
+      for (int i = 0; i < 4; ++i) {
+        s += __uint_as_float(xs[i] << 16) * __uint_as_float(ys[i] << 16);
+        s += __uint_as_float(xs[i] & 0xffff0000u) * __uint_as_float(ys[i] & 0xffff0000u);
+      }
+    }
+#pragma unroll
+    for (int off = kLanes / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+    if (live && part == 0) delta[static_cast<long long>(h) * total_tokens + t] = s;
+  }
 }
 
 // acc is dense [tokens, width] fp32; dq rows are dq_stride elements apart
@@ -794,12 +806,14 @@ cudaError_t attn_bwd(const void* dout, const void* q, const void* k, const void*
     return cudaErrorInvalidValue;
   // dout is contiguous [T, n_q, D]; dq / dk / dv rows may be strided (views of one fused qkv gradient)
   const long long do_stride = static_cast<long long>(n_q) * head_dim;
-  {
-    const long long warps = static_cast<long long>(total_tokens) * n_q;
-    const int grid = static_cast<int>((warps * 32 + 255) / 256);
-    attn_delta_kernel<<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(dout),
-                                                static_cast<const __nv_bfloat16*>(o), delta, total_tokens, n_q,
-                                                head_dim, do_stride, o_stride);
+  if (head_dim == 64) {
+    attn_delta_kernel<64><<<(total_tokens + 31) / 32, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(o), delta, total_tokens, n_q,
+        do_stride, o_stride);
+  } else {
+    attn_delta_kernel<128><<<(total_tokens + 15) / 16, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(o), delta, total_tokens, n_q,
+        do_stride, o_stride);
   }
   cudaError_t e = cudaMemsetAsync(dq_acc, 0, sizeof(float) * static_cast<size_t>(total_tokens) * n_q * head_dim, stream);
   if (e != cudaSuccess) return e;

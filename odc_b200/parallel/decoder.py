@@ -321,6 +321,13 @@ class FusedDecoderLM(nn.Module):
         return _FusedLinearCrossEntropy.apply(h.contiguous(), labels.contiguous(), loss_scale, self, -100,
                                               self.cfg.ce_chunk)
 
+    @torch.no_grad()
+    def logits(self, input_ids, position_ids, cu_seqlens, max_seqlen):
+        """``[T, vocab]`` logits (inference helper; pulls the head matrix like a forward pass does)."""
+        h = self.hidden_states(input_ids, position_ids, cu_seqlens, max_seqlen)
+        p = self.head_param()
+        return ops.linear(h, self.head_full()[:p.out_features])
+
     # -- whole-model state (collective): the names and shapes DecoderLM.state_dict() has ------------------
     @torch.no_grad()
     def full_state_dict(self) -> Dict[str, torch.Tensor]:

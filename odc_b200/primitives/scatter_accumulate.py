@@ -169,6 +169,7 @@ class ReductionService:
                 self.transport.post_counts(self.posted, world, me, self.epoch,
                                            [self.dispatched.get(r, 0) for r in world])
                 self.transport.wait_posted(self.posted, self.counter, len(world), self.epoch)
+                self.expected_total = None  # summed on the device; not brought back to the host
                 gathered = [(None, None)] * len(world)
             else:
                 gathered = control.all_gather_object((dict(self.dispatched), payload))
