@@ -22,5 +22,8 @@ def get_args():
     p.add_argument("--lr", type=float, default=5e-4)
     p.add_argument("--activation-checkpointing", action="store_true")
     p.add_argument("--num-sequences", type=int, default=4096)
+    p.add_argument("--loss-head", default="ce", choices=["ce", "logprobs"],
+                   help="ce: fused linear + cross-entropy (one pass); logprobs: per-token log-probabilities, "
+                        "loss = -(logp * loss_scale).sum() as the reference's trainers form it")
     p.add_argument("--cpu", action="store_true", help="CPU ranks over gloo and the host-shm heap (functional runs)")
     return p.parse_args()

@@ -65,6 +65,15 @@ def make_dataset(args, cfg, rank, world, odc_enabled):
                           args.limit_dataset_token_len, cost, odc_enabled)
 
 
+def microbatch_loss(args, model, mb):
+    """Loss of one packed microbatch through the head ``--loss-head`` names (same value either way)."""
+    a = (mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"])
+    if getattr(args, "loss_head", "ce") == "logprobs":
+        logp = model(*a, labels=mb["labels"], return_logprobs=True)
+        return -(logp * mb["loss_scale"].float()).sum()
+    return model(*a, labels=mb["labels"], loss_scale=mb["loss_scale"])
+
+
 def log_metrics(rank, step, metrics):
     """Rank 0 prints one JSON line per minibatch (the reference logs the same fields to wandb)."""
     if rank == 0:

@@ -12,7 +12,7 @@ from torch.distributed.fsdp import MixedPrecision
 from torch.distributed.fsdp.wrap import ModuleWrapPolicy
 
 from args import get_args
-from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics
+from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics, microbatch_loss
 
 import odc_b200 as odc
 from odc_b200.data import to_device
@@ -50,8 +50,7 @@ def main():
             for mb in microbatches:
                 mb = to_device(mb, dev)
                 tokens += mb["num_tokens"]
-                loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"],
-                             loss_scale=mb["loss_scale"])
+                loss = microbatch_loss(args, model, mb)
                 if not args.forward_only:
                     loss.backward()
                 total += loss.detach()

@@ -15,7 +15,7 @@ from torch.distributed.device_mesh import init_device_mesh
 from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
 from args import get_args
-from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics
+from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics, microbatch_loss
 
 import odc_b200 as odc
 from odc_b200.data import to_device
@@ -78,8 +78,7 @@ def main():
                     mb = to_device(mb, dev)
                     tokens += mb["num_tokens"]
                     with torch.set_grad_enabled(not args.forward_only):
-                        loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"],
-                                     labels=mb["labels"], loss_scale=mb["loss_scale"])
+                        loss = microbatch_loss(args, model, mb)
                     if not args.forward_only:
                         loss.backward()
                     total += loss.detach()

@@ -172,11 +172,19 @@ class DecoderLM(nn.Module):
                 x = layer(x, position_ids, cu_seqlens, max_seqlen)
         return self.norm(x)
 
-    def forward(self, input_ids, position_ids, cu_seqlens, max_seqlen, labels=None, loss_scale=None):
-        """Summed (``loss_scale``-weighted) next-token loss if ``labels`` is given, else final hidden states."""
+    def forward(self, input_ids, position_ids, cu_seqlens, max_seqlen, labels=None, loss_scale=None,
+                return_logprobs: bool = False, temperature: float = 1.0):
+        """Summed (``loss_scale``-weighted) next-token loss if ``labels`` is given, else final hidden states.
+
+        With ``return_logprobs`` the per-token log-probabilities of ``labels`` come back instead of the loss
+        (fp32, 0 at ignored positions): what policy-gradient objectives weight by an advantage, and what the
+        reference's trainers build their loss from (examples/llm_training/torch_fsdp2.py:70-80).
+        """
         h = self.hidden_states(input_ids, position_ids, cu_seqlens, max_seqlen)
         if labels is None:
             return h
+        if return_logprobs:
+            return ops.linear_token_logprobs(h, self.head_weight(), labels, temperature)
         return ops.linear_cross_entropy(h, self.head_weight(), labels, loss_scale, chunk=self.cfg.ce_chunk)
 
     def logits(self, input_ids, position_ids, cu_seqlens, max_seqlen):

@@ -377,6 +377,95 @@ def linear_cross_entropy(h, w, labels, loss_scale=None, ignore_index: int = -100
     return _LinearCrossEntropy.apply(h.contiguous(), w, labels.contiguous(), loss_scale, ignore_index, chunk)
 
 
+class _LinearTokenLogProbs(torch.autograd.Function):
+    """Per-token log-probability of ``ids`` under ``softmax(h @ w.T / temperature)``, in token chunks.
+
+    The policy-gradient form of the chunked LM head (the reference's ``FusedLinearForPPOFunction``,
+    examples/llm_training/lm_head.py:62-190): the weights of the tokens are only known in backward, so
+    backward recomputes each chunk's logits, turns them in place into
+    ``dlogp / temperature * (onehot - softmax)`` with the cross-entropy kernel (its per-token scale is
+    ``-dlogp / temperature``) and feeds the two gradient GEMMs; ``[T, vocab]`` logits never exist.
+    """
+
+    @staticmethod
+    def forward(ctx, h, w, ids, temperature, ignore_index, chunk):
+        T = h.shape[0]
+        V = w.shape[0]
+        out = torch.zeros(T, dtype=torch.float32, device=h.device)
+        logits = torch.empty(min(chunk, T), V, dtype=torch.bfloat16, device=h.device)
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            lg = logits[: e - s]
+            gemm(h[s:e], w, "nt", out=lg)
+            if temperature != 1.0:
+                lg.mul_(1.0 / temperature)
+            tok = ids[s:e]
+            lg32 = lg.float()
+            picked = lg32.gather(-1, tok.clamp_min(0).unsqueeze(-1)).squeeze(-1) - torch.logsumexp(lg32, dim=-1)
+            out[s:e] = torch.where(tok != ignore_index, picked, torch.zeros_like(picked))
+        ctx.save_for_backward(h, w, ids)
+        ctx.args = (temperature, ignore_index, chunk)
+        return out
+
+    @staticmethod
+    def backward(ctx, dlogp):
+        h, w, ids = ctx.saved_tensors
+        temperature, ignore_index, chunk = ctx.args
+        T, H = h.shape
+        V = w.shape[0]
+        ext = _ext()
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dh = torch.empty_like(h) if need_dh else None
+        dw32 = torch.empty(V, H, dtype=torch.float32, device=h.device) if need_dw else None
+        if T == 0 and dw32 is not None:
+            dw32.zero_()
+        scale = (dlogp.reshape(-1).float() * (-1.0 / temperature)).contiguous()
+        sink = torch.zeros((), dtype=torch.float32, device=h.device)   # the kernel's loss output is not used here
+        logits = torch.empty(min(chunk, T), V, dtype=torch.bfloat16, device=h.device)
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            lg = logits[: e - s]
+            gemm(h[s:e], w, "nt", out=lg)
+            if temperature != 1.0:
+                lg.mul_(1.0 / temperature)
+            ext.ce_fwd_bwd(lg, ids[s:e], scale[s:e], sink, ignore_index)
+            _count()
+            if need_dh:
+                gemm(lg, w, "nn", out=dh[s:e])
+            if need_dw:
+                gemm(lg, h[s:e], "tn", out=dw32, accumulate=s > 0)
+        return dh, (dw32.to(w.dtype) if dw32 is not None else None), None, None, None, None
+
+
+def linear_token_logprobs(h, w, ids, temperature: float = 1.0, ignore_index: int = -100, chunk: int = 1024):
+    """``log_softmax(h @ w.T / temperature)[t, ids[t]]`` as fp32, for ``h`` of shape ``[T, H]`` or ``[B, S, H]``.
+
+    Positions whose id equals ``ignore_index`` give 0 and no gradient.
+    """
+    shape = ids.shape
+    h2 = h.reshape(-1, h.shape[-1])
+    flat = ids.reshape(-1).to(torch.int64)
+    if not h.is_cuda:
+        return ref.linear_token_logprobs(h2, w, flat, temperature, ignore_index, chunk).view(shape)
+    return _LinearTokenLogProbs.apply(h2.contiguous(), w, flat.contiguous(), float(temperature), ignore_index,
+                                      chunk).view(shape)
+
+
+class LinearTokenLogProbs(torch.nn.Module):
+    """Module form: ``forward(hidden_states, vocab_weights, input_ids, temperature) -> (log_probs, None)``.
+
+    The second value is the place of the entropy the reference's module leaves unset as well
+    (examples/llm_training/lm_head.py:193-214).
+    """
+
+    def __init__(self, chunk_size: int = 1024):
+        super().__init__()
+        self.chunk_size = chunk_size
+
+    def forward(self, hidden_states, vocab_weights, input_ids, temperature: float = 1.0):
+        return linear_token_logprobs(hidden_states, vocab_weights, input_ids, temperature, chunk=self.chunk_size), None
+
+
 # ------------------------------------------------------------------------------------------
 def fused_adamw_(p32, g, m, v, p_lowp, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0):
     """One AdamW step on a flat fp32 shard; also refreshes the low-precision copy that peers gather."""

@@ -93,6 +93,18 @@ def linear_cross_entropy(h, w, labels, loss_scale=None, ignore_index: int = -100
     return total
 
 
+def linear_token_logprobs(h, w, ids, temperature: float = 1.0, ignore_index: int = -100, chunk: int = 1024):
+    """``log_softmax(h @ w.T / temperature)[t, ids[t]]`` per token (0 where ``ids == ignore_index``)."""
+    out = []
+    for s in range(0, h.shape[0], chunk):
+        logits = (F.linear(h[s:s + chunk], w) / temperature).float()
+        tok = ids[s:s + chunk]
+        keep = tok != ignore_index
+        lp = logits.log_softmax(-1).gather(-1, tok.clamp_min(0).unsqueeze(-1)).squeeze(-1)
+        out.append(torch.where(keep, lp, torch.zeros_like(lp)))
+    return torch.cat(out) if out else h.new_zeros(0, dtype=torch.float32)
+
+
 def adamw_step(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step, grad_scale: float = 1.0):
     """In-place decoupled-weight-decay Adam on fp32 tensors (matches ``torch.optim.AdamW``)."""
     g = g.float() * grad_scale

@@ -187,6 +187,41 @@ class _FusedLinearCrossEntropy(torch.autograd.Function):
         return dh * dloss.to(dh.dtype), None, None, None, None, None
 
 
+class _FusedTokenLogProbs(torch.autograd.Function):
+    """Per-token log-probabilities against the gathered LM-head matrix (``ops.linear_token_logprobs`` with the
+    weight gradient going to the producing rank's fp32 buffer; the reference's policy-gradient head is
+    examples/llm_training/lm_head.py:62-190).  Backward recomputes the chunks' logits."""
+
+    @staticmethod
+    def forward(ctx, h, ids, model, temperature, ignore_index, chunk):
+        p = model.head_param()
+        w = model.head_full()[:p.out_features]
+        ctx.save_for_backward(h, ids)
+        ctx.model, ctx.args = model, (temperature, ignore_index, chunk)
+        with torch.no_grad():
+            return ops.linear_token_logprobs(h, w, ids, temperature, ignore_index, chunk)
+
+    @staticmethod
+    def backward(ctx, dlogp):
+        h, ids = ctx.saved_tensors
+        model = ctx.model
+        temperature, ignore_index, chunk = ctx.args
+        p = model.head_param()
+        w = model.head_full()[:p.out_features]
+        with torch.enable_grad():
+            h_ = h.detach().requires_grad_()
+            w_ = w.detach().requires_grad_()
+            lp = ops.linear_token_logprobs(h_, w_, ids, temperature, ignore_index, chunk)
+            dh, dw = torch.autograd.grad(lp, [h_, w_], dlogp)
+        p.wait_push()
+        buf = p.local_buffer()
+        buf[:p.out_features].add_(dw)
+        p.local_dirty = True
+        if p is not model.embed and L.requires_gradient_sync():
+            p.push_local(side_stream=True)
+        return dh, None, None, None, None, None
+
+
 class FusedDecoderLayer(nn.Module):
     def __init__(self, cfg: DecoderConfig, i: int, src, small: SmallGroup, pg, keep_weight, lowp_dtype):
         super().__init__()
@@ -312,10 +347,15 @@ class FusedDecoderLM(nn.Module):
                 x = layer(x, position_ids, cu_seqlens, max_seqlen)
         return ops.rms_norm(x, self.small.view("norm.weight", (self.cfg.hidden_size,)), self.cfg.rms_eps)
 
-    def forward(self, input_ids, position_ids, cu_seqlens, max_seqlen, labels=None, loss_scale=None):
+    def forward(self, input_ids, position_ids, cu_seqlens, max_seqlen, labels=None, loss_scale=None,
+                return_logprobs: bool = False, temperature: float = 1.0):
+        """Same contract as ``DecoderLM.forward``: hidden states, the summed weighted loss, or (``return_logprobs``)
+        the per-token log-probabilities of ``labels``."""
         h = self.hidden_states(input_ids, position_ids, cu_seqlens, max_seqlen)
         if labels is None:
             return h
+        if return_logprobs:
+            return _FusedTokenLogProbs.apply(h.contiguous(), labels.contiguous(), self, float(temperature), -100, 1024)
         if loss_scale is not None and loss_scale.dtype != torch.float32:
             loss_scale = loss_scale.float()
         return _FusedLinearCrossEntropy.apply(h.contiguous(), labels.contiguous(), loss_scale, self, -100,

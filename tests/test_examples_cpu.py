@@ -27,20 +27,20 @@ def test_fsdp2_example_cpu(env, tmp_path):
     assert "step 9 loss" in r.stdout
 
 
-@pytest.mark.parametrize("script,env,packing", [
-    ("train_fsdp2.py", {"ODC": "1"}, "DynamicDiffMicro"),      # ranks get different numbers of microbatches
-    ("train_fsdp2.py", {"ODC": "0"}, "DynamicSameMicro"),      # lock-step baseline
-    ("train_fsdp1.py", {"ODC": "1"}, "DynamicDiffMicro"),
-    ("train_fsdp2.py", {"ENGINE": "fused"}, "DynamicDiffMicro"),   # the fused-kernel decoder engine
+@pytest.mark.parametrize("script,env,packing,extra", [
+    ("train_fsdp2.py", {"ODC": "1"}, "DynamicDiffMicro", []),      # ranks get different numbers of microbatches
+    ("train_fsdp2.py", {"ODC": "0"}, "DynamicSameMicro", []),      # lock-step baseline
+    ("train_fsdp1.py", {"ODC": "1"}, "DynamicDiffMicro", ["--loss-head", "logprobs"]),   # per-token log-prob head
+    ("train_fsdp2.py", {"ENGINE": "fused"}, "DynamicDiffMicro", []),   # the fused-kernel decoder engine
 ])
-def test_llm_trainers_cpu(script, env, packing, tmp_path):
+def test_llm_trainers_cpu(script, env, packing, extra, tmp_path):
     e = dict(os.environ, **env, ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path))
     port = _free_port()
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "examples/llm_training", script), "--cpu",
            "--model_name", "tiny", "--steps", "2", "--minibatch_size", "4", "--num-sequences", "32",
            "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512",
-           "--packing_method", packing, "--run_name", "cpu_smoke"]
+           "--packing_method", packing, "--run_name", "cpu_smoke"] + extra
     r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]

@@ -62,8 +62,11 @@ def _train(rank, world, mode, steps, uneven, variant):
             mb = _make_batches(rank, step, mine)[i if real else 0]
             if mode == "odc" and "defer" in variant:
                 model.set_requires_gradient_sync(i == n_micro - 1)
-            loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"],
-                         labels=mb["labels"], loss_scale=mb["loss_scale"])
+            a = (mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"])
+            if mode == "odc" and "logprobs" in variant:   # the per-token log-probability head gives the same loss
+                loss = -(model(*a, labels=mb["labels"], return_logprobs=True) * mb["loss_scale"]).sum()
+            else:
+                loss = model(*a, labels=mb["labels"], loss_scale=mb["loss_scale"])
             if not real:
                 loss = loss * 0.0
             loss.backward()
@@ -93,8 +96,8 @@ def _train(rank, world, mode, steps, uneven, variant):
     return losses, full
 
 
-@pytest.mark.parametrize("uneven,variant", [(False, "plain,roundtrip"), (True, "defer,clip"), (False, "bias_tied,keep,ac"),
-                                            (True, "bias_tied,defer")])
+@pytest.mark.parametrize("uneven,variant", [(False, "plain,roundtrip"), (True, "defer,clip,logprobs"),
+                                            (False, "bias_tied,keep,ac"), (True, "bias_tied,defer,logprobs")])
 def test_fused_engine_matches_stock_fsdp2(uneven, variant):
     world = 2
     a, b = run_pair(_train, world, (3, uneven, variant))

@@ -271,6 +271,31 @@ def test_linear_cross_entropy_matches_reference():
     torch.testing.assert_close(w.grad.float(), wr.grad, rtol=5e-2, atol=2e-4)
 
 
+@pytest.mark.parametrize("temperature", [1.0, 0.7])
+def test_linear_token_logprobs_matches_reference(temperature):
+    """Per-token log-probabilities and both gradients against the fp32 statement of the same head; a 3-D input,
+    a ragged last chunk and ignored positions included."""
+    from odc_b200 import ops
+    from odc_b200.ops import reference as ref
+    B, S, H, V = 2, 333, 256, 1024
+    h = torch.randn(B, S, H, device="cuda").bfloat16().requires_grad_()
+    w = (0.05 * torch.randn(V, H, device="cuda")).bfloat16().requires_grad_()
+    ids = torch.randint(0, V, (B, S), device="cuda")
+    ids[0, :5] = -100
+    adv = torch.randn(B, S, device="cuda")
+    lp = ops.linear_token_logprobs(h, w, ids, temperature, chunk=256)
+    assert lp.shape == ids.shape and lp.dtype == torch.float32
+    (lp * adv).sum().backward()
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lpr = ref.linear_token_logprobs(hr.view(-1, H), wr, ids.view(-1), temperature).view(B, S)
+    (lpr * adv).sum().backward()
+    assert float(lp[0, :5].abs().max()) == 0.0
+    torch.testing.assert_close(lp, lpr.detach(), rtol=2e-2, atol=3e-2)
+    torch.testing.assert_close(h.grad.float(), hr.grad, rtol=5e-2, atol=3e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, rtol=5e-2, atol=5e-2)
+    assert float(h.grad[0, :5].float().abs().max()) == 0.0
+
+
 # ------------------------------------------------------------------------------------ fused compute + comm
 @pytest.mark.parametrize("world", [1, 2, 8])
 @pytest.mark.parametrize("T,n_out,k_in", [(512, 256, 256), (1000, 768, 264), (4096, 2048, 2048)])

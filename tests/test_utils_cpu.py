@@ -96,3 +96,52 @@ def test_inter_node_transport_needs_a_multi_node_job():
             InterNodeTransport(reg)
     finally:
         odc.finalize_distributed()
+
+
+def test_linear_token_logprobs_cpu_matches_plain_autograd():
+    """The chunked per-token log-probability head (policy-gradient losses) equals log_softmax + gather, with a
+    temperature, ignored positions, a 3-D input and a ragged last chunk; the module form returns (log_probs, None)."""
+    from odc_b200 import ops
+    torch.manual_seed(0)
+    B, S, H, V = 2, 37, 16, 50
+    h = torch.randn(B, S, H, requires_grad=True)
+    w = torch.randn(V, H, requires_grad=True)
+    ids = torch.randint(0, V, (B, S))
+    ids[1, 3] = -100
+    adv = torch.randn(B, S)
+    lp, ent = ops.LinearTokenLogProbs(chunk_size=16)(h, w, ids, temperature=0.5)
+    assert ent is None and lp.shape == (B, S)
+    (lp * adv).sum().backward()
+    h2, w2 = h.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+    full = ((h2 @ w2.t()) / 0.5).log_softmax(-1).gather(-1, ids.clamp_min(0).unsqueeze(-1)).squeeze(-1)
+    full = torch.where(ids != -100, full, torch.zeros_like(full))
+    (full * adv).sum().backward()
+    torch.testing.assert_close(lp, full.detach())
+    torch.testing.assert_close(h.grad, h2.grad)
+    torch.testing.assert_close(w.grad, w2.grad)
+    assert float(lp.detach()[1, 3]) == 0.0 and float(h.grad[1, 3].abs().max()) == 0.0
+
+
+def test_decoder_logprob_head_gives_the_same_loss_and_gradients():
+    """``DecoderLM(..., return_logprobs=True)`` weighted by ``loss_scale`` is the fused cross-entropy loss."""
+    from odc_b200.data import LengthSpec, make_minibatch
+    from odc_b200.models import DecoderConfig, DecoderLM
+    cfg = DecoderConfig(vocab_size=97, hidden_size=32, intermediate_size=64, num_layers=1, num_heads=2, num_kv_heads=1,
+                        head_dim=16)
+    mb = make_minibatch(0, 0, cfg.vocab_size, LengthSpec("uniform", lo=8, hi=40), 1, 128)[0]
+    a = (mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"])
+    grads = []
+    losses = []
+    for head in ("ce", "logprobs"):
+        model = DecoderLM(cfg)
+        model.reset_parameters(seed=1)
+        if head == "ce":
+            loss = model(*a, labels=mb["labels"], loss_scale=mb["loss_scale"])
+        else:
+            loss = -(model(*a, labels=mb["labels"], return_logprobs=True) * mb["loss_scale"]).sum()
+        loss.backward()
+        losses.append(loss.detach())
+        grads.append({n: p.grad.clone() for n, p in model.named_parameters()})
+    torch.testing.assert_close(losses[0], losses[1])
+    for n in grads[0]:
+        torch.testing.assert_close(grads[0][n], grads[1][n], rtol=1e-4, atol=1e-6)
