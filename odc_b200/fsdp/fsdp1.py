@@ -14,9 +14,11 @@ How it works here:
   refreshed once per minibatch; ``_all_gather_flat_param`` becomes one ``gather`` launch that pulls
   compute-precision bytes (the reference pulls the original dtype and casts after the transfer,
   odc/fsdp/fsdp1.py:189-223).  The per-unshard low-precision copy of stock FSDP is skipped.
-* ``_reduce_grad`` pads the unsharded gradient and ``scatter_accumulate``-s it, folding the
-  pre/post divide factors into the kernel's scale; nothing is attached to ``flat_param.grad``
-  until ``pre_optimizer_step`` has waited for all contributions.
+* ``_reduce_grad`` ``scatter_accumulate``-s the unsharded gradient where it lies (a flat gradient
+  that does not divide by the group size is reduced as ragged pieces instead of being padded with
+  a copy), folding the pre/post divide factors into the kernel's scale; nothing is attached to
+  ``flat_param.grad`` until ``pre_optimizer_step`` has waited for all contributions, and then it
+  is the accumulator itself (or its cast to the shard's dtype), not a copy.
 """
 from __future__ import annotations
 
@@ -25,10 +27,12 @@ from typing import Any, Dict, List, Optional
 
 import torch
 import torch.distributed.fsdp._runtime_utils as _ru
+import torch.nn.functional as F
 import torch.distributed.fsdp._traversal_utils as _tu
 from torch.distributed.fsdp._common_utils import _FSDPState
 from torch.distributed.fsdp._flat_param import FlatParamHandle, HandleShardingStrategy
 
+from .. import config
 from ..primitives import GatherService, ReductionService
 from ..runtime import control
 from ..runtime.registry import SymmBufferRegistry
@@ -159,11 +163,22 @@ def _reduce_grad(state: _FSDPState, handle: FlatParamHandle) -> None:
     flat_param = handle.flat_param
     unsharded_grad = flat_param.grad.data
     flat_param.grad = None
-    padded, _unused = _ru._get_reduce_scatter_tensors(state, unsharded_grad)
     factor = float(state._gradient_predivide_factor) * float(state._gradient_postdivide_factor)
+    world = state.world_size
+    flat = unsharded_grad.reshape(-1)
+    shard = (flat.numel() + world - 1) // world      # FSDP1's shard size: the first chunk of ``chunk(world)``
     if not reduction.has_accumulation(handle._odc_key):
-        reduction.register(handle._odc_key, padded.numel() // state.world_size, padded.dtype, state.process_group)
-    reduction.scatter_accumulate(handle._odc_key, padded, state.process_group, scale=1.0 / factor)
+        reduction.register(handle._odc_key, shard, flat.dtype, state.process_group)
+    done = False
+    if shard * world != flat.numel() and config.reduce_from_segments() and flat.is_contiguous():
+        # A flat gradient that does not divide by the group size: the last owners' pieces are short or empty.  Stock
+        # FSDP1 pads with a full-size copy first; the segmented reduction reads the ragged pieces in place.
+        done = reduction.scatter_accumulate_segments(handle._odc_key, [flat], [shard], [0], state.process_group,
+                                                     scale=1.0 / factor)
+    if not done:
+        if shard * world != flat.numel():
+            flat = F.pad(flat, [0, shard * world - flat.numel()])
+        reduction.scatter_accumulate(handle._odc_key, flat, state.process_group, scale=1.0 / factor)
     _S.touched.add(handle._odc_key)
     # marks "a gradient was produced" for stock bookkeeping; the real value is assigned in pre_optimizer_step
     flat_param._saved_grad_shard = reduction.get_accumulation(handle._odc_key)
@@ -241,7 +256,9 @@ def pre_optimizer_step(fsdp_model) -> None:
         acc = reduction.get_accumulation(h._odc_key)
         fp = h.flat_param
         shard = fp._local_shard if hasattr(fp, "_local_shard") else fp.data
-        g = acc.to(shard.dtype) if acc.dtype != shard.dtype else acc.clone()
+        # Same dtype: the optimizer reads (and a clip may scale) the accumulator itself.  Nothing adds into it
+        # between this synchronisation and the barrier of the next pre_minibatch_start, which clears it anyway.
+        g = acc.to(shard.dtype)
         if fp.data.data_ptr() != shard.data_ptr():
             fp.data = shard  # the optimizer must see the sharded flat parameter
         fp.grad = g.view_as(shard)

@@ -100,9 +100,17 @@ def _train_zero(rank, world, mode):
     import odc_b200 as odc
     from odc_b200.fsdp import fsdp1
 
+    ragged = []
     if mode == "odc":
         fsdp1.patch_fsdp1(reduce_dtype=None)
         odc.init_nvshmem("cpu", 64 << 20)
+        stock_segments = odc.ReductionService.scatter_accumulate_segments
+
+        def recording_segments(self, key, grads, chunks, offsets, *a, **k):
+            ragged.append((grads[0].numel(), chunks[0]))
+            return stock_segments(self, key, grads, chunks, offsets, *a, **k)
+
+        odc.ReductionService.scatter_accumulate_segments = recording_segments
     torch.manual_seed(0)
     net = nn.Sequential(nn.Linear(20, 32), nn.Tanh(), nn.Linear(32, 3))
     model = FSDP(net, device_id=torch.device("cpu"), use_orig_params=False)
@@ -129,10 +137,13 @@ def _train_zero(rank, world, mode):
         full = {k: v.detach().clone() for k, v in model.named_parameters()}
     if mode == "odc":
         fsdp1.stop()
-    return full
+        odc.ReductionService.scatter_accumulate_segments = stock_segments
+    return full, ragged
 
 
 def test_fsdp1_rank_with_zero_microbatches():
     a, b = run_pair(_train_zero, 2)
-    for k in a[0]:
-        torch.testing.assert_close(a[0][k], b[0][k], rtol=1e-5, atol=1e-6)
+    for k in a[0][0]:
+        torch.testing.assert_close(a[0][0][k], b[0][0][k], rtol=1e-5, atol=1e-6)
+    # 771 parameters over 2 ranks: the flat gradient is reduced as ragged pieces (386 + 385), never padded with a copy
+    assert b[0][1] and set(b[0][1]) == {(771, 386)}

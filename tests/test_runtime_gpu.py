@@ -105,6 +105,46 @@ def test_fsdp2_single_gpu_training_step(single_rank_pg, monkeypatch):
         fsdp2.stop()
 
 
+@pytest.mark.parametrize("head", ["ce", "logprobs"])
+def test_fused_engine_single_gpu_training_step(single_rank_pg, head):
+    """Tiny decoder on the fused-kernel engine, world 1: the loss goes down with either LM head, the clip norm is
+    finite, and the whole-model state has ``DecoderLM``'s names."""
+    import odc_b200 as odc
+    from odc_b200.data import LengthSpec, make_minibatch, to_device
+    from odc_b200.models import DecoderLM, get_config
+    from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
+
+    dev = torch.device("cuda", 0)
+    cfg = get_config("tiny")
+    odc.init_nvshmem(dev, 2 << 30)
+    model = FusedDecoderLM(cfg, device=dev, seed=0)
+    opt = FusedOptimizer(model, lr=3e-3)
+    mbs = [to_device(mb, dev) for mb in make_minibatch(0, 0, cfg.vocab_size, LengthSpec("uniform", lo=16, hi=128), 2, 512)]
+    losses = []
+    try:
+        for step in range(6):
+            model.start_minibatch()
+            tot = 0.0
+            for mb in mbs:
+                a = (mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"])
+                if head == "ce":
+                    loss = model(*a, labels=mb["labels"], loss_scale=mb["loss_scale"])
+                else:
+                    loss = -(model(*a, labels=mb["labels"], return_logprobs=True) * mb["loss_scale"]).sum()
+                loss.backward()
+                tot += float(loss.detach())
+            model.finish_minibatch()
+            assert torch.isfinite(opt.clip_grad_norm_(1.0))
+            opt.step()
+            losses.append(tot)
+        assert losses[-1] < losses[0] - 0.05, losses
+        with torch.device("meta"):
+            names = set(DecoderLM(cfg).state_dict())
+        assert set(model.full_state_dict()) == names
+    finally:
+        model.stop()
+
+
 def test_deterministic_reduction_mode_gpu(monkeypatch):
     import odc_b200 as odc
     monkeypatch.setenv("ODC_DETERMINISTIC", "1")
