@@ -37,7 +37,9 @@ def main():
     mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, buffer_dtype=torch.bfloat16)
     model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=dev, use_orig_params=False,
                  mixed_precision=mp)
-    opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
+    use_fused = ODC and os.environ.get("FUSED_OPTIMIZER", "1") == "1"
+    opt = fsdp1.FusedAdamW(model, lr=args.lr, weight_decay=0.01) if use_fused else \
+        torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
     data = make_dataset(args, cfg, rank, world, ODC)
     if ODC:
         fsdp1.pre_minibatch_start(model)
@@ -57,9 +59,9 @@ def main():
             if not args.forward_only:
                 with Timer("sync_time", times):
                     if ODC:
-                        fsdp1.pre_optimizer_step(model)
+                        fsdp1.pre_optimizer_step(model, materialize_grads=not use_fused)
                 with Timer("optimizer_step_time", times):
-                    grad_norm = model.clip_grad_norm_(1.0)
+                    grad_norm = opt.clip_grad_norm_(1.0) if use_fused else model.clip_grad_norm_(1.0)
                     opt.step()
                     opt.zero_grad()
                 if ODC:

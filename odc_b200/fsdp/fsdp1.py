@@ -50,6 +50,7 @@ class _State:
     next_index = 0
     in_shard: Optional[FlatParamHandle] = None
     touched: set = set()   # keys of flat parameters this rank reduced a gradient for in this minibatch
+    used: set = set()      # keys some rank reduced a gradient for, as of the last pre_optimizer_step
 
 
 _S = _State
@@ -232,15 +233,21 @@ def pre_minibatch_start(fsdp_model) -> None:
                 if _replica(h) is None:
                     h._odc_replica = reg.allocate_symm_buffer(f"fsdp_params_lowp_{h._odc_key}", shard.shape,
                                                               h._fwd_bwd_param_dtype)
-                h._odc_replica.copy_(shard)
+                if getattr(h, "_odc_replica_fresh", False):
+                    h._odc_replica_fresh = False      # FusedAdamW wrote the compute-precision copy itself
+                else:
+                    h._odc_replica.copy_(shard)
         reduction.clear_accumulations()
         _device_sync()
         control.host_barrier()
 
 
 @torch.no_grad()
-def pre_optimizer_step(fsdp_model) -> None:
-    """Wait for every contribution (collective) and expose the summed gradient as ``flat_param.grad``."""
+def pre_optimizer_step(fsdp_model, materialize_grads: bool = True) -> None:
+    """Wait for every contribution (collective) and expose the summed gradient as ``flat_param.grad``.
+
+    ``materialize_grads=False`` leaves ``.grad`` alone: :class:`FusedAdamW` reads the accumulators directly.
+    """
     _require_patched()
     if not isinstance(fsdp_model, _FSDPState):
         raise AssertionError("pass the root FSDP module")
@@ -250,6 +257,9 @@ def pre_optimizer_step(fsdp_model) -> None:
     for other in reduction.sync(payload=sorted(_S.touched, key=str)):
         used.update(other or ())
     _S.touched = set()
+    _S.used = used
+    if not materialize_grads:
+        return
     for h in _handles(fsdp_model):
         if not reduction.has_accumulation(h._odc_key) or h._odc_key not in used:
             continue
@@ -262,6 +272,89 @@ def pre_optimizer_step(fsdp_model) -> None:
         if fp.data.data_ptr() != shard.data_ptr():
             fp.data = shard  # the optimizer must see the sharded flat parameter
         fp.grad = g.view_as(shard)
+
+
+# ------------------------------------------------------------------------------------------
+class FusedAdamW:
+    """AdamW over the flat shards, read straight from the accumulators (FSDP1 counterpart of ``fsdp2.FusedAdamW``).
+
+    The reference steps ``torch.optim.AdamW`` over flat parameters whose ``.grad`` is a cast of the accumulator
+    (odc/fsdp/fsdp1.py:317-335, examples/llm_training/torch_fsdp.py).  Here one kernel per flat parameter reads
+    the summed gradient from its accumulator (the clipping scale folded in), updates the fp32 shard and the
+    moments, and writes the compute-precision copy that the peers gather in the next minibatch, so no ``.grad``
+    and no separate cast pass exist.  Use with ``pre_optimizer_step(model, materialize_grads=False)``; flat
+    parameters that no rank produced a gradient for are skipped, as ``torch.optim.AdamW`` skips ``grad is None``.
+    """
+
+    def __init__(self, fsdp_model, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01):
+        self.model, self.lr, self.betas, self.eps, self.weight_decay = fsdp_model, lr, betas, eps, weight_decay
+        self.state: Dict[str, Dict[str, Any]] = {}    # heap key of the flat parameter -> {"step", "m", "v"}
+        self._clip_scale = 1.0
+
+    def _live(self):
+        """``(handle, fp32 shard, accumulator)`` of every flat parameter that received a gradient."""
+        reduction, _ = _services()
+        out = []
+        for h in _handles(self.model):
+            if h._odc_key not in _S.used or not reduction.has_accumulation(h._odc_key):
+                continue
+            fp = h.flat_param
+            shard = fp._local_shard if hasattr(fp, "_local_shard") else fp.data
+            acc = reduction.get_accumulation(h._odc_key)
+            if shard.dtype != torch.float32 or acc.dtype != torch.float32:
+                raise NotImplementedError("FusedAdamW keeps fp32 shards and fp32 accumulators "
+                                          "(patch_fsdp1(reduce_dtype=torch.float32))")
+            out.append((h, shard.view(-1), acc.view(-1)))
+        return out
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: float) -> torch.Tensor:
+        """Global L2 norm of the summed gradient; the clipping scale is applied inside the next ``step``."""
+        live = self._live()
+        dev = SymmBufferRegistry.get_instance().heap.device
+        total = torch.zeros((), dtype=torch.float32, device=dev)
+        for _, _, acc in live:
+            if acc.is_cuda:
+                from .. import _ext
+                part = torch.zeros((), dtype=torch.float32, device=dev)
+                _ext.load().sumsq(acc, part)
+                total += part
+            else:
+                total += acc.pow(2).sum()
+        if control.world_size() > 1:
+            torch.distributed.all_reduce(total)   # shards are disjoint across the ranks (FULL_SHARD over all of them)
+        norm = total.sqrt()
+        self._clip_scale = float(min(1.0, max_norm / (float(norm) + 1e-6)))
+        return norm
+
+    @torch.no_grad()
+    def step(self) -> None:
+        from .. import ops
+        for h, shard, acc in self._live():
+            st = self.state.get(h._odc_key)
+            if st is None:
+                st = self.state[h._odc_key] = {"step": 0, "m": torch.zeros_like(shard), "v": torch.zeros_like(shard)}
+            st["step"] += 1
+            rep = _replica(h)
+            ops.fused_adamw_(shard, acc, st["m"], st["v"], None if rep is None else rep.view(-1), self.lr,
+                             self.betas[0], self.betas[1], self.eps, self.weight_decay, st["step"], self._clip_scale)
+            if rep is not None:
+                h._odc_replica_fresh = True
+        self._clip_scale = 1.0
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for p in self.model.parameters():
+            p.grad = None
+
+    def state_dict(self) -> Dict[str, Any]:
+        """This rank's moments by heap key (same sharding on load: same model, same number of ranks)."""
+        return {"state": {k: {"step": v["step"], "m": v["m"].clone(), "v": v["v"].clone()} for k, v in self.state.items()},
+                "hyper": dict(lr=self.lr, betas=self.betas, eps=self.eps, weight_decay=self.weight_decay)}
+
+    def load_state_dict(self, sd: Dict[str, Any]) -> None:
+        self.state = {k: {"step": v["step"], "m": v["m"].clone(), "v": v["v"].clone()} for k, v in sd["state"].items()}
+        for k, v in sd.get("hyper", {}).items():
+            setattr(self, k, v)
 
 
 # ------------------------------------------------------------------------------------------
@@ -312,6 +405,7 @@ def unpatch_fsdp1() -> None:
     _S.reduction = _S.gather = None
     _S.next_index = 0
     _S.touched = set()
+    _S.used = set()
 
 
 def stop() -> None:

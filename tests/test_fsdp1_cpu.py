@@ -5,7 +5,7 @@ import torch
 from _mp import assert_mostly_close, run_pair
 
 
-def _train(rank, world, mode, uneven, mp=False):
+def _train(rank, world, mode, uneven, mp=False, fused_opt=False):
     import functools
 
     import torch.distributed as dist
@@ -35,7 +35,8 @@ def _train(rank, world, mode, uneven, mp=False):
     policy = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32) if mp else None
     model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=torch.device("cpu"),
                  use_orig_params=False, mixed_precision=policy)
-    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    fused_opt = fused_opt and mode == "odc"
+    opt = fsdp1.FusedAdamW(model, lr=1e-3) if fused_opt else torch.optim.AdamW(model.parameters(), lr=1e-3)
     if mode == "odc":
         fsdp1.pre_minibatch_start(model)
     losses = []
@@ -53,7 +54,11 @@ def _train(rank, world, mode, uneven, mp=False):
             loss.backward()
             total += loss.detach()
         if mode == "odc":
-            fsdp1.pre_optimizer_step(model)
+            fsdp1.pre_optimizer_step(model, materialize_grads=not fused_opt)
+        if fused_opt:
+            opt.clip_grad_norm_(0.5)
+        elif mp:
+            model.clip_grad_norm_(0.5)
         opt.step()
         opt.zero_grad()
         if mode == "odc":
@@ -87,6 +92,15 @@ def test_fsdp1_mixed_precision_reduces_bf16_gradients_into_fp32_accumulators():
     a, b = run_pair(_train, 2, (True, True))
     # the unsharded gradients reach the reduction in bf16 (stock's widening pass is skipped) and land in fp32
     assert b[0][2] == {(torch.bfloat16, torch.float32)}
+    assert a[0][0] == pytest.approx(b[0][0], rel=2e-2), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        assert_mostly_close(a[0][1][k].float(), b[0][1][k].float(), rtol=2e-2, atol=3e-3, outlier_atol=1e-2)
+
+
+def test_fsdp1_fused_adamw_matches_torch_adamw_with_clipping():
+    """``fsdp1.FusedAdamW`` on the accumulators (mixed precision, unequal microbatch counts, clip at 0.5) against
+    stock FSDP1 with ``torch.optim.AdamW`` and ``model.clip_grad_norm_``."""
+    a, b = run_pair(_train, 2, (True, True, True))
     assert a[0][0] == pytest.approx(b[0][0], rel=2e-2), (a[0][0], b[0][0])
     for k in a[0][1]:
         assert_mostly_close(a[0][1][k].float(), b[0][1][k].float(), rtol=2e-2, atol=3e-3, outlier_atol=1e-2)

@@ -374,6 +374,21 @@ def test_fsdp1_unequal_microbatch_counts_over_nvlink():
     _launch(FSDP1_UNEVEN, 2, timeout=600)
 
 
+FSDP1_FUSED_OPT = FSDP1_UNEVEN.replace(
+    "opt = torch.optim.AdamW(model.parameters(), lr=1e-3)",
+    "opt = fsdp1.FusedAdamW(model, lr=1e-3) if use_odc else torch.optim.AdamW(model.parameters(), lr=1e-3)").replace(
+    "fsdp1.pre_optimizer_step(model)", "fsdp1.pre_optimizer_step(model, materialize_grads=False)")
+
+
+def test_fsdp1_fused_adamw_over_nvlink():
+    """``fsdp1.FusedAdamW`` (accumulators -> fp32 shards + the bf16 copies the peers pull next) against stock FSDP1
+    with ``torch.optim.AdamW``, unequal microbatch counts."""
+    if _ngpu() < 2:
+        pytest.skip("needs 2 GPUs")
+    assert "fsdp1.FusedAdamW" in FSDP1_FUSED_OPT and "materialize_grads=False" in FSDP1_FUSED_OPT
+    _launch(FSDP1_FUSED_OPT, 2, timeout=600)
+
+
 GATHER_SUBSET = """
 import random
 reg = odc.init_nvshmem(dev, 2 << 30)
