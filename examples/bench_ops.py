@@ -5,6 +5,7 @@
     python examples/bench_ops.py comm            # gather / scatter_accumulate with peers emulated on one GPU
     python examples/bench_ops.py attention       # varlen attention fwd/bwd vs flash-attn
     python examples/bench_ops.py attention_mix   # the same on packs of log-normal sequence lengths (the headline workload)
+    python examples/bench_ops.py lm_head         # fused loss head / log-probability head vs the same mathematics in eager PyTorch
 
 Timing: CUDA events on the launching stream, >= 3 warm-up runs, an L2 flush (256 MB write) between
 timed iterations, median of the timed runs.  Fractions are of the measured peaks in MEASURED_PEAKS.json
@@ -185,6 +186,62 @@ def bench_attention_mix():
               f"[flash-attn {t_rb:.3f} ms, {t_rb / t_b:.2f}x] | fwd+bwd {(t_r + t_rb) / (t_f + t_b):.2f}x")
 
 
+def bench_lm_head():
+    """Forward + backward of the LM head at the headline shapes: the one-pass fused linear + cross-entropy, the per-token
+    log-probability head (logits recomputed in backward), and the same mathematics in eager PyTorch (bf16 matmuls
+    through cuBLAS, fp32 log-softmax, 512-token chunks with recomputation in backward: how the reference's chunked
+    head is written, examples/llm_training/lm_head.py:7-59)."""
+    from odc_b200 import ops
+    T, H, V = 16384, 2048, 128256
+    torch.manual_seed(0)
+    h = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    w = (0.02 * torch.randn(V, H, device="cuda")).bfloat16().requires_grad_()
+    ids = torch.randint(0, V, (T,), device="cuda")
+    scale = torch.full((T,), 1.0 / T, device="cuda")
+
+    class Eager(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, h, w, ids):
+            out = torch.empty(T, dtype=torch.float32, device=h.device)
+            for s in range(0, T, 512):
+                lg = (h[s:s + 512] @ w.t()).float()
+                out[s:s + 512] = lg.log_softmax(-1).gather(-1, ids[s:s + 512, None]).squeeze(-1)
+            ctx.save_for_backward(h, w, ids)
+            return out
+
+        @staticmethod
+        def backward(ctx, dlp):
+            h, w, ids = ctx.saved_tensors
+            dh, dw = torch.empty_like(h), torch.zeros_like(w)
+            for s in range(0, T, 512):
+                p = (h[s:s + 512] @ w.t()).float().softmax(-1)
+                d = -p * dlp[s:s + 512, None]
+                d.scatter_add_(-1, ids[s:s + 512, None], dlp[s:s + 512, None])
+                d = d.to(h.dtype)
+                dh[s:s + 512] = d @ w
+                dw += d.t() @ h[s:s + 512]
+            return dh, dw, None
+
+    def run(kind):
+        h.grad = w.grad = None
+        if kind == "ce":
+            loss = ops.linear_cross_entropy(h, w, ids, scale)
+        elif kind == "logprobs":
+            loss = -(ops.linear_token_logprobs(h, w, ids) * scale).sum()
+        else:
+            loss = -(Eager.apply(h, w, ids) * scale).sum()
+        loss.backward()
+        return loss
+
+    flops = 6.0 * T * H * V
+    vals = {}
+    for kind in ("ce", "logprobs", "eager"):
+        vals[kind] = float(run(kind))
+        t = timed(lambda: run(kind), iters=5, warmup=2)
+        print(f"lm_head {kind:9} T={T} H={H} V={V}: fwd+bwd {t:8.2f} ms  ({flops / t / 1e9:6.0f} TFLOP/s on 6*T*H*V)  loss {vals[kind]:.4f}")
+    assert abs(vals["ce"] - vals["eager"]) < 2e-2 and abs(vals["logprobs"] - vals["eager"]) < 2e-2, vals
+
+
 def small_gemm():
     """One forward-shaped GEMM, a few launches: the small case used for ncu captures (operands + output > L2)."""
     from odc_b200 import _ext
@@ -272,5 +329,5 @@ def small_fused():
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
     {"gemm": bench_gemm, "elementwise": bench_elementwise, "comm": bench_comm, "attention": bench_attention, "attention_mix": bench_attention_mix,
-     "small_gemm": small_gemm, "small_attention": small_attention, "small_comm": small_comm,
+     "lm_head": bench_lm_head, "small_gemm": small_gemm, "small_attention": small_attention, "small_comm": small_comm,
      "small_fused": small_fused}[which]()

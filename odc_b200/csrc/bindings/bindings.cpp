@@ -290,6 +290,20 @@ void ce_fwd_bwd(Tensor logits, Tensor labels, c10::optional<Tensor> loss_scale, 
         "ce_fwd_bwd");
 }
 
+void token_logprobs(Tensor logits, Tensor labels, Tensor out, int64_t ignore_index) {
+  c10::cuda::CUDAGuard g(logits.device());
+  odc::bind_device(logits.get_device());
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous() && logits.scalar_type() == at::kBFloat16, "token_logprobs: logits bf16");
+  TORCH_CHECK(labels.scalar_type() == at::kLong && labels.is_contiguous() && labels.numel() == logits.size(0),
+              "token_logprobs: one int64 label per row");
+  TORCH_CHECK(out.scalar_type() == at::kFloat && out.is_contiguous() && out.numel() == logits.size(0) && out.is_cuda(),
+              "token_logprobs: one fp32 output per row");
+  check(odc::launch_token_logprobs(logits.data_ptr(), reinterpret_cast<const long long*>(labels.data_ptr<int64_t>()),
+                                   out.data_ptr<float>(), static_cast<int>(logits.size(0)),
+                                   static_cast<int>(logits.size(1)), ignore_index, cur_stream()),
+        "token_logprobs");
+}
+
 void adamw_step(Tensor p, Tensor g, Tensor m, Tensor v, c10::optional<Tensor> p_lowp, double lr, double beta1,
                 double beta2, double eps, double wd, int64_t step, double grad_scale) {
   c10::cuda::CUDAGuard guard(p.device());
@@ -597,6 +611,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("ce_fwd_bwd", &ce_fwd_bwd);
+  m.def("token_logprobs", &token_logprobs);
   m.def("adamw_step", &adamw_step);
   m.def("cast_f32_to_bf16", &cast_f32_to_bf16);
   m.def("sumsq", &sumsq);

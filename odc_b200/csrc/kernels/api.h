@@ -81,6 +81,9 @@ cudaError_t launch_swiglu_bwd(const void* dy, const void* gate_up, void* dgate_u
 // logits [rows, vocab] bf16 are overwritten by scale * (softmax - onehot); loss += sum scale * nll
 cudaError_t launch_ce_fwd_bwd(void* logits, const long long* labels, const float* loss_scale, float* loss,
                               int rows, int vocab, long long ignore_index, cudaStream_t stream);
+// per_token[row] = log_softmax(logits[row])[labels[row]] (0 where the label is ignore_index); logits are only read
+cudaError_t launch_token_logprobs(const void* logits, const long long* labels, float* per_token, int rows, int vocab,
+                                  long long ignore_index, cudaStream_t stream);
 cudaError_t launch_adamw(float* p, const void* g, int g_kind, float* m, float* v, void* p_lowp, size_t n, float lr,
                          float beta1, float beta2, float eps, float wd, float bc1, float bc2, float grad_scale,
                          int sm_count, cudaStream_t stream);

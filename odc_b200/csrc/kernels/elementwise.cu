@@ -331,21 +331,28 @@ swiglu_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ gu, bf16
 
 // ------------------------------------------------------------------------- cross-entropy ----
 // one CTA per row; pass 1: online max / sum-exp; pass 2: logits <- scale * (softmax - onehot)
+// kForwardOnly: pass 1 only, the logits stay as they are and the row's log-probability of its label
+// (0 for an ignored row) goes to per_token[row]; the scale and the summed loss are not used.
 constexpr int kCeThreads = 1024;
+template <bool kForwardOnly>
 __global__ void __launch_bounds__(kCeThreads)
 ce_fwd_bwd_kernel(bf16* __restrict__ logits, const long long* __restrict__ labels, const float* __restrict__ loss_scale,
-                  float* __restrict__ loss, int vocab, long long ignore_index) {
+                  float* __restrict__ loss, int vocab, long long ignore_index, float* __restrict__ per_token) {
   __shared__ float red[32];
   const int row = blockIdx.x;
   bf16* lr = logits + size_t(row) * vocab;
   const long long label = labels[row];
-  const float scale = loss_scale ? loss_scale[row] : 1.f;
+  const float scale = (!kForwardOnly && loss_scale) ? loss_scale[row] : 1.f;
   const bool ignored = (label == ignore_index) || scale == 0.f;
   const int nvec = vocab / 8;
   uint4* lv = reinterpret_cast<uint4*>(lr);
   if (ignored) {
-    for (int v = threadIdx.x; v < nvec; v += blockDim.x) lv[v] = make_uint4(0, 0, 0, 0);
-    for (int j = nvec * 8 + threadIdx.x; j < vocab; j += blockDim.x) lr[j] = __float2bfloat16(0.f);
+    if constexpr (kForwardOnly) {
+      if (threadIdx.x == 0) per_token[row] = 0.f;
+    } else {
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) lv[v] = make_uint4(0, 0, 0, 0);
+      for (int j = nvec * 8 + threadIdx.x; j < vocab; j += blockDim.x) lr[j] = __float2bfloat16(0.f);
+    }
     return;
   }
   float m = -INFINITY, s = 0.f;
@@ -374,6 +381,10 @@ ce_fwd_bwd_kernel(bf16* __restrict__ logits, const long long* __restrict__ label
   s = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
   const float gs = block_sum(s, red);
   const float lse = gm + logf(gs);
+  if constexpr (kForwardOnly) {
+    if (threadIdx.x == 0) per_token[row] = __bfloat162float(lr[label]) - lse;
+    return;
+  }
   if (threadIdx.x == 0) atomicAdd(loss, scale * (lse - __bfloat162float(lr[label])));
   __syncthreads();  // the label logit is read above before anyone overwrites it
   const float inv = 1.f / gs;
@@ -549,8 +560,18 @@ cudaError_t launch_ce_fwd_bwd(void* logits, const long long* labels, const float
                               int rows, int vocab, long long ignore_index, cudaStream_t stream) {
   if (rows == 0) return cudaSuccess;
   if (vocab % 8 != 0) return cudaErrorInvalidValue;  // rows must stay 16-byte aligned
-  ce_fwd_bwd_kernel<<<rows, kCeThreads, 0, stream>>>(static_cast<bf16*>(logits), labels, loss_scale, loss, vocab,
-                                                     ignore_index);
+  ce_fwd_bwd_kernel<false><<<rows, kCeThreads, 0, stream>>>(static_cast<bf16*>(logits), labels, loss_scale, loss, vocab,
+                                                            ignore_index, nullptr);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_token_logprobs(const void* logits, const long long* labels, float* per_token, int rows, int vocab,
+                                  long long ignore_index, cudaStream_t stream) {
+  if (rows == 0) return cudaSuccess;
+  if (vocab % 8 != 0 || per_token == nullptr) return cudaErrorInvalidValue;
+  // the forward-only instantiation never writes through the logits pointer
+  ce_fwd_bwd_kernel<true><<<rows, kCeThreads, 0, stream>>>(static_cast<bf16*>(const_cast<void*>(logits)), labels, nullptr,
+                                                           nullptr, vocab, ignore_index, per_token);
   return cudaGetLastError();
 }
 

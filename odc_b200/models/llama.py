@@ -184,7 +184,7 @@ class DecoderLM(nn.Module):
         if labels is None:
             return h
         if return_logprobs:
-            return ops.linear_token_logprobs(h, self.head_weight(), labels, temperature)
+            return ops.linear_token_logprobs(h, self.head_weight(), labels, temperature, chunk=self.cfg.ce_chunk)
         return ops.linear_cross_entropy(h, self.head_weight(), labels, loss_scale, chunk=self.cfg.ce_chunk)
 
     def logits(self, input_ids, position_ids, cu_seqlens, max_seqlen):

@@ -391,6 +391,7 @@ class _LinearTokenLogProbs(torch.autograd.Function):
     def forward(ctx, h, w, ids, temperature, ignore_index, chunk):
         T = h.shape[0]
         V = w.shape[0]
+        ext = _ext()
         out = torch.zeros(T, dtype=torch.float32, device=h.device)
         logits = torch.empty(min(chunk, T), V, dtype=torch.bfloat16, device=h.device)
         for s in range(0, T, chunk):
@@ -399,10 +400,8 @@ class _LinearTokenLogProbs(torch.autograd.Function):
             gemm(h[s:e], w, "nt", out=lg)
             if temperature != 1.0:
                 lg.mul_(1.0 / temperature)
-            tok = ids[s:e]
-            lg32 = lg.float()
-            picked = lg32.gather(-1, tok.clamp_min(0).unsqueeze(-1)).squeeze(-1) - torch.logsumexp(lg32, dim=-1)
-            out[s:e] = torch.where(tok != ignore_index, picked, torch.zeros_like(picked))
+            ext.token_logprobs(lg, ids[s:e], out[s:e], ignore_index)   # one pass over the chunk's logits
+            _count()
         ctx.save_for_backward(h, w, ids)
         ctx.args = (temperature, ignore_index, chunk)
         return out
@@ -437,7 +436,7 @@ class _LinearTokenLogProbs(torch.autograd.Function):
         return dh, (dw32.to(w.dtype) if dw32 is not None else None), None, None, None, None
 
 
-def linear_token_logprobs(h, w, ids, temperature: float = 1.0, ignore_index: int = -100, chunk: int = 1024):
+def linear_token_logprobs(h, w, ids, temperature: float = 1.0, ignore_index: int = -100, chunk: int = 4096):
     """``log_softmax(h @ w.T / temperature)[t, ids[t]]`` as fp32, for ``h`` of shape ``[T, H]`` or ``[B, S, H]``.
 
     Positions whose id equals ``ignore_index`` give 0 and no gradient.
@@ -458,7 +457,7 @@ class LinearTokenLogProbs(torch.nn.Module):
     (examples/llm_training/lm_head.py:193-214).
     """
 
-    def __init__(self, chunk_size: int = 1024):
+    def __init__(self, chunk_size: int = 4096):
         super().__init__()
         self.chunk_size = chunk_size
 

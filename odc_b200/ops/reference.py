@@ -93,7 +93,7 @@ def linear_cross_entropy(h, w, labels, loss_scale=None, ignore_index: int = -100
     return total
 
 
-def linear_token_logprobs(h, w, ids, temperature: float = 1.0, ignore_index: int = -100, chunk: int = 1024):
+def linear_token_logprobs(h, w, ids, temperature: float = 1.0, ignore_index: int = -100, chunk: int = 4096):
     """``log_softmax(h @ w.T / temperature)[t, ids[t]]`` per token (0 where ``ids == ignore_index``)."""
     out = []
     for s in range(0, h.shape[0], chunk):

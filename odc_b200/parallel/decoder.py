@@ -355,7 +355,8 @@ class FusedDecoderLM(nn.Module):
         if labels is None:
             return h
         if return_logprobs:
-            return _FusedTokenLogProbs.apply(h.contiguous(), labels.contiguous(), self, float(temperature), -100, 1024)
+            return _FusedTokenLogProbs.apply(h.contiguous(), labels.contiguous(), self, float(temperature), -100,
+                                             self.cfg.ce_chunk)
         if loss_scale is not None and loss_scale.dtype != torch.float32:
             loss_scale = loss_scale.float()
         return _FusedLinearCrossEntropy.apply(h.contiguous(), labels.contiguous(), loss_scale, self, -100,

@@ -161,6 +161,22 @@ def test_ce_fwd_bwd(ext, T, V):
     assert float(logits[~keep].abs().sum()) == 0.0
 
 
+def test_token_logprobs_kernel_reads_only(ext):
+    """Forward-only instantiation of the cross-entropy kernel: per-row log-probability of the label, 0 for ignored
+    rows, logits left untouched."""
+    T, V = 300, 1000
+    logits = (3 * torch.randn(T, V, device="cuda")).bfloat16()
+    keep = logits.clone()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::7] = -100
+    out = torch.full((T,), 7.0, device="cuda")
+    ext.token_logprobs(logits, labels, out, -100)
+    want = logits.float().log_softmax(-1).gather(-1, labels.clamp_min(0)[:, None]).squeeze(-1)
+    want = torch.where(labels != -100, want, torch.zeros_like(want))
+    torch.testing.assert_close(out, want, rtol=1e-4, atol=2e-4)
+    assert torch.equal(logits, keep)
+
+
 def test_adamw_matches_torch(ext):
     n = 100003
     p = torch.randn(n, device="cuda")
