@@ -381,7 +381,8 @@ class _LinearTokenLogProbs(torch.autograd.Function):
     """Per-token log-probability of ``ids`` under ``softmax(h @ w.T / temperature)``, in token chunks.
 
     The policy-gradient form of the chunked LM head (the reference's ``FusedLinearForPPOFunction``,
-    examples/llm_training/lm_head.py:62-190): the weights of the tokens are only known in backward, so
+    examples/llm_training/lm_head.py:62-190).  Forward is one GEMM and one read-only pass of the cross-entropy
+    kernel per chunk (one number per token comes out).  The weights of the tokens are only known in backward, so
     backward recomputes each chunk's logits, turns them in place into
     ``dlogp / temperature * (onehot - softmax)`` with the cross-entropy kernel (its per-token scale is
     ``-dlogp / temperature``) and feeds the two gradient GEMMs; ``[T, vocab]`` logits never exist.
