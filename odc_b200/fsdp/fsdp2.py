@@ -15,8 +15,10 @@ How this integration works (it is a different design from the reference's patch 
   mixed precision a second flat buffer holds the shards in ``param_dtype``; it is refreshed
   once per minibatch, so ``gather`` moves compute-precision bytes instead of fp32 masters
   (the reference gathers the original dtype and casts afterwards, odc/fsdp/fsdp2.py:339-351).
-* ``foreach_reduce`` flattens the unsharded gradients rank-major and ``scatter_accumulate``-s
-  them into the owners' accumulators; no gradient is attached to a parameter until
+* ``foreach_reduce`` adds the unsharded gradients into the owners' accumulators: straight from
+  the per-parameter tensors in one segmented ``scatter_accumulate`` launch where the transport
+  can (no rank-major staging copy), otherwise flattened rank-major first; no gradient is
+  attached to a parameter until
   ``pre_optimizer_step``, which waits for the arrivals (the one synchronisation per
   minibatch), applies the divide factor, runs the HSDP replicate-dimension all-reduce once
   per group and assigns ``sharded_param.grad``.  Ranks may run different numbers of
