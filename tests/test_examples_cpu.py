@@ -71,3 +71,20 @@ def _run_prim_bench(script, tmp_path, extra, world=2):
     assert len(out) == 1
     rows = json.load(open(tmp_path / out[0]))
     assert [row["shard_bytes"] for row in rows] == [4096, 8192, 16384, 32768, 65536]
+
+
+def test_bench_reference_arm_reports_one_json_line():
+    """``bench.py --impl reference`` either runs the reference or prints why it cannot, as one JSON line, exit code 0
+    (no GPU is needed to get as far as the reference's import)."""
+    r = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "1",
+                        "--warmup", "1"], capture_output=True, text=True, timeout=600,
+                       env=dict(os.environ, RANK="0", WORLD_SIZE="1"))
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1 and lines[0]["impl"] == "reference"
+    assert "unavailable" in lines[0] or {"metric", "value", "n_gpus"} <= set(lines[0])
+    # a rank other than 0 prints nothing: the driver reads one line per job
+    r1 = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--impl", "reference", "--gpus", "2"],
+                        capture_output=True, text=True, timeout=600, env=dict(os.environ, RANK="1", WORLD_SIZE="2"))
+    if "unavailable" in lines[0]:
+        assert r1.returncode == 0 and not [l for l in r1.stdout.splitlines() if l.startswith("{")]
