@@ -74,11 +74,41 @@ def microbatch_loss(args, model, mb):
     return model(*a, labels=mb["labels"], loss_scale=mb["loss_scale"])
 
 
+_wandb_run = None
+
+
+def init_logging(args, rank):
+    """``ODC_WANDB=1`` and an importable ``wandb``: rank 0 also logs every minibatch's metrics there (project and
+    run name from ``--project_name`` / ``--run_name``), as the reference's trainers do."""
+    global _wandb_run
+    if rank != 0 or os.environ.get("ODC_WANDB", "0") != "1":
+        return
+    try:
+        import wandb
+        _wandb_run = wandb.init(project=args.project_name, name=args.run_name, config=vars(args))
+    except Exception as e:  # not installed, no API key, no network: training goes on with stdout metrics
+        print(f"ODC_WANDB=1 but wandb is unavailable ({type(e).__name__}): metrics go to stdout only", flush=True)
+        _wandb_run = None
+
+
 def log_metrics(rank, step, metrics):
-    """Rank 0 prints one JSON line per minibatch (the reference logs the same fields to wandb)."""
+    """Rank 0 prints one JSON line per minibatch (and mirrors it to wandb when :func:`init_logging` set that up)."""
     if rank == 0:
         print(json.dumps({"step": step, **{k: (round(v, 5) if isinstance(v, float) else v) for k, v in metrics.items()}}),
               flush=True)
+        if _wandb_run is not None:
+            _wandb_run.log(dict(metrics), step=step)
+
+
+def log_packing(dataset, rank):
+    """``ODC_DEBUG_PACKING=1``: every rank's microbatch composition of the last minibatch, printed by rank 0."""
+    if os.environ.get("ODC_DEBUG_PACKING", "0") != "1":
+        return
+    import torch.distributed as dist
+    lines = [None] * dist.get_world_size()
+    dist.all_gather_object(lines, dataset.last_debug)
+    if rank == 0:
+        print("\n".join(lines), flush=True)
 
 
 def memory_metrics():

@@ -12,7 +12,8 @@ from torch.distributed.fsdp import MixedPrecision
 from torch.distributed.fsdp.wrap import ModuleWrapPolicy
 
 from args import get_args
-from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics, microbatch_loss
+from common import (Timer, init_device, init_logging, log_metrics, log_packing, make_dataset, mark_done,
+                    memory_metrics, microbatch_loss)
 
 import odc_b200 as odc
 from odc_b200.data import to_device
@@ -41,11 +42,13 @@ def main():
     opt = fsdp1.FusedAdamW(model, lr=args.lr, weight_decay=0.01) if use_fused else \
         torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
     data = make_dataset(args, cfg, rank, world, ODC)
+    init_logging(args, rank)
     if ODC:
         fsdp1.pre_minibatch_start(model)
     for step in range(min(args.steps, len(data))):
         times = {}
         microbatches = data[step]
+        log_packing(data, rank)
         with Timer("minibatch_time", times):
             total = torch.zeros((), device=dev)
             tokens = 0

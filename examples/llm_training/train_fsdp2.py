@@ -15,7 +15,8 @@ from torch.distributed.device_mesh import init_device_mesh
 from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
 from args import get_args
-from common import Timer, init_device, log_metrics, make_dataset, mark_done, memory_metrics, microbatch_loss
+from common import (Timer, init_device, init_logging, log_metrics, log_packing, make_dataset, mark_done,
+                    memory_metrics, microbatch_loss)
 
 import odc_b200 as odc
 from odc_b200.data import to_device
@@ -57,6 +58,7 @@ def main():
     opt = fsdp2.FusedAdamW(model, lr=args.lr, weight_decay=0.01) if use_fused else \
         torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
     data = make_dataset(args, cfg, rank, world, ODC)
+    init_logging(args, rank)
     prof = None
     if os.environ.get("TORCH_PROFILED", "0") == "1":
         prof = torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA])
@@ -67,6 +69,7 @@ def main():
         if os.environ.get("CUDA_PROFILED", "0") == "1" and step == steps - 1:
             torch.cuda.cudart().cudaProfilerStart()
         microbatches = data[step]
+        log_packing(data, rank)
         with Timer("minibatch_time", times):
             if ODC:
                 fsdp2.pre_minibatch_start(model)
@@ -130,10 +133,12 @@ def main_fused(args, cfg, dev, rank, world):
     model = FusedDecoderLM(cfg, device=dev, seed=0)
     opt = FusedOptimizer(model, lr=args.lr, weight_decay=0.01)
     data = make_dataset(args, cfg, rank, world, True)
+    init_logging(args, rank)
     steps = min(args.steps, len(data))
     for step in range(steps):
         times = {}
         microbatches = data[step]
+        log_packing(data, rank)
         with Timer("minibatch_time", times):
             model.start_minibatch()
             total = torch.zeros((), device=dev)

@@ -29,7 +29,7 @@ def test_fsdp2_example_cpu(env, tmp_path):
 
 @pytest.mark.parametrize("script,env,packing,extra", [
     ("train_fsdp2.py", {"ODC": "1"}, "DynamicDiffMicro", []),      # ranks get different numbers of microbatches
-    ("train_fsdp2.py", {"ODC": "0"}, "DynamicSameMicro", []),      # lock-step baseline
+    ("train_fsdp2.py", {"ODC": "0", "ODC_DEBUG_PACKING": "1", "ODC_WANDB": "1", "WANDB_MODE": "disabled"}, "DynamicSameMicro", []),  # lock-step baseline
     ("train_fsdp1.py", {"ODC": "1"}, "DynamicDiffMicro", ["--loss-head", "logprobs"]),   # per-token log-prob head
     ("train_fsdp2.py", {"ENGINE": "fused"}, "DynamicDiffMicro", []),   # the fused-kernel decoder engine
 ])
@@ -47,6 +47,8 @@ def test_llm_trainers_cpu(script, env, packing, extra, tmp_path):
     assert [l["step"] for l in lines] == [0, 1]
     assert all(l["loss"] == l["loss"] and l["tokens"] > 0 for l in lines)
     assert (tmp_path / "cpu_smoke.done").exists()
+    if env.get("ODC_DEBUG_PACKING") == "1":   # every rank's microbatch composition, printed by rank 0
+        assert "rank 0 " in r.stdout and "rank 1 " in r.stdout
 
 
 @pytest.mark.parametrize("script", ["all_gather.py", "reduce_scatter.py"])
