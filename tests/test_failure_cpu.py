@@ -18,6 +18,7 @@ def _dropped_contribution(rank, world):
     red.scatter_accumulate("g", torch.ones(world * 64))
     if rank == 1:
         red.note_dispatch(list(range(world)))  # the message itself is "dropped": counted but never sent
+    control.host_barrier()   # both ranks enter sync together, so the short wait below measures the missing arrival only
     timed_out = False
     try:
         red.sync()
@@ -37,7 +38,7 @@ def _dropped_contribution(rank, world):
 
 
 def test_wait_reports_a_missing_contribution():
-    res = run_ranks(_dropped_contribution, 2, env={"ODC_WAIT_TIMEOUT_MS": "400"})
+    res = run_ranks(_dropped_contribution, 2, env={"ODC_WAIT_TIMEOUT_MS": "1500"})
     assert all(res)  # every owner was told to expect one more arrival than it received
 
 
