@@ -99,13 +99,13 @@ def _left_between_steps(rank, world):
     control.host_barrier()
     if rank == 1:
         control.heartbeat().mark_leaving()
-        time.sleep(1.5)
+        time.sleep(3.0)
         return "left"
-    time.sleep(0.5)
+    time.sleep(1.0)
     t0 = time.monotonic()
     with pytest.raises(PeerFailure, match="stopped publishing"):
         red.sync()
-    assert time.monotonic() - t0 < 1.0   # no wait budget was spent
+    assert time.monotonic() - t0 < 5.0   # none of the 20 s wait budget was spent
     return "detected"
 
 
