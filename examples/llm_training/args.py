@@ -12,6 +12,11 @@ def get_args():
     p.add_argument("--max_token_len", type=int, default=65536)
     p.add_argument("--limit_dataset_token_len", type=int, default=None)
     p.add_argument("--model_name", default="qwen2.5-1.5b")
+    p.add_argument("--hf-checkpoint", default=None,
+                   help="folder of a Hugging Face Llama / Qwen2 checkpoint (config.json + safetensors): its "
+                        "architecture and weights replace --model_name and the seeded initialisation")
+    p.add_argument("--save-hf-checkpoint", default=None,
+                   help="after the last step, write the model to this folder in the Hugging Face layout")
     p.add_argument("--packing_method", default="DynamicDiffMicro",
                    choices=["None", "DynamicSameMicro", "DynamicDiffMicro", "LocalSort", "DebugUneven"])
     p.add_argument("--cost_model", default="linear", choices=["linear", "fit", "flops"])

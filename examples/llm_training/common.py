@@ -42,6 +42,32 @@ def init_device(args, rank):
     return dev
 
 
+def model_config(args):
+    """The decoder configuration: a preset name, or (``--hf-checkpoint``) the one of a Hugging Face Llama / Qwen2
+    checkpoint folder, the way the reference's trainers start from ``from_pretrained`` weights."""
+    from odc_b200.models import get_config
+    if args.hf_checkpoint:
+        import json
+        from odc_b200.models.hf import config_from_hf
+        with open(os.path.join(args.hf_checkpoint, "config.json")) as f:
+            return config_from_hf(json.load(f), activation_checkpointing=args.activation_checkpointing)
+    return get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)
+
+
+def build_decoder(args, cfg, dev):
+    """An unsharded ``DecoderLM`` on ``dev`` with the run's initial weights (seeded, or the checkpoint's)."""
+    from odc_b200.models import DecoderLM
+    with torch.device(dev):
+        model = DecoderLM(cfg)
+    if args.hf_checkpoint:
+        from odc_b200.models.hf import load_hf_checkpoint
+        _, sd = load_hf_checkpoint(args.hf_checkpoint)
+        model.load_state_dict(sd)   # copies into the parameters on ``dev``, keeps their fp32 dtype
+    else:
+        model.reset_parameters(seed=0)
+    return model
+
+
 def build_sequences(args, vocab):
     if args.dataset != "synthetic":
         return torch.load(args.dataset)
@@ -118,6 +144,13 @@ def memory_metrics():
     symm = SymmBufferRegistry.get_instance().memory_allocated() / 2**30 if SymmBufferRegistry.is_initialized() else 0.0
     return {"torch_mem_gib": torch.cuda.memory_allocated() / 2**30, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2**30,
             "symm_mem_gib": symm}
+
+
+def export_model(args, model, cfg):
+    """``--save-hf-checkpoint``: the trained weights as a Hugging Face checkpoint folder (collective)."""
+    if args.save_hf_checkpoint:
+        from odc_b200.utils.checkpoint import Checkpointer
+        Checkpointer(args.save_hf_checkpoint).export_hf(model, cfg, args.save_hf_checkpoint)
 
 
 def mark_done(args):

@@ -12,13 +12,13 @@ from torch.distributed.fsdp import MixedPrecision
 from torch.distributed.fsdp.wrap import ModuleWrapPolicy
 
 from args import get_args
-from common import (Timer, init_device, init_logging, log_metrics, log_packing, make_dataset, mark_done,
-                    memory_metrics, microbatch_loss)
+from common import (Timer, build_decoder, export_model, init_device, init_logging, log_metrics, log_packing,
+                    make_dataset, mark_done, memory_metrics, microbatch_loss, model_config)
 
 import odc_b200 as odc
 from odc_b200.data import to_device
 from odc_b200.fsdp import fsdp1
-from odc_b200.models import DecoderLayer, DecoderLM, get_config
+from odc_b200.models import DecoderLayer
 
 ODC = os.environ.get("ODC", "1") == "1"
 if ODC:
@@ -31,10 +31,8 @@ def main():
     dev = init_device(args, rank)
     if ODC:
         odc.init_nvshmem(dev)
-    cfg = get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)
-    with torch.device(dev):
-        model = DecoderLM(cfg)
-    model.reset_parameters(seed=0)
+    cfg = model_config(args)
+    model = build_decoder(args, cfg, dev)
     mp = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, buffer_dtype=torch.bfloat16)
     model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({DecoderLayer}), device_id=dev, use_orig_params=False,
                  mixed_precision=mp)
@@ -74,6 +72,7 @@ def main():
         dist.all_reduce(tok)
         log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
                                  "tokens_per_s": int(tok) / times["minibatch_time"], **times, **memory_metrics()})
+    export_model(args, model, cfg)
     mark_done(args)
     if ODC:
         fsdp1.stop()

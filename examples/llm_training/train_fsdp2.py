@@ -15,13 +15,12 @@ from torch.distributed.device_mesh import init_device_mesh
 from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
 from args import get_args
-from common import (Timer, init_device, init_logging, log_metrics, log_packing, make_dataset, mark_done,
-                    memory_metrics, microbatch_loss)
+from common import (Timer, build_decoder, export_model, init_device, init_logging, log_metrics, log_packing,
+                    make_dataset, mark_done, memory_metrics, microbatch_loss, model_config)
 
 import odc_b200 as odc
 from odc_b200.data import to_device
 from odc_b200.fsdp import fsdp2
-from odc_b200.models import DecoderLM, get_config
 from odc_b200.utils.nvtx import nvtx_range
 
 ODC = os.environ.get("ODC", "1") == "1"
@@ -35,15 +34,13 @@ def main():
     args = get_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = init_device(args, rank)
-    cfg = get_config(args.model_name, activation_checkpointing=args.activation_checkpointing)
+    cfg = model_config(args)
     if FUSED:
         return main_fused(args, cfg, dev, rank, world)
     if ODC:
         odc.init_nvshmem(dev)
         fsdp2.patch_fsdp2(enable_hpz=HPZ)
-    with torch.device(dev):
-        model = DecoderLM(cfg)
-    model.reset_parameters(seed=0)
+    model = build_decoder(args, cfg, dev)
     mesh = init_device_mesh(dev.type, (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard")) if HSDP \
         else init_device_mesh(dev.type, (world,))
     mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
@@ -120,6 +117,7 @@ def main():
         out_dir = os.environ.get("ODC_OUT_DIR", "bench_out")
         os.makedirs(out_dir, exist_ok=True)
         prof.export_chrome_trace(f"{out_dir}/trace_{args.run_name}_rank{rank}.json")
+    export_model(args, model, cfg)
     mark_done(args)
     if ODC:
         fsdp2.stop()
@@ -130,7 +128,9 @@ def main_fused(args, cfg, dev, rank, world):
     """The same loop on ``FusedDecoderLM``: start_minibatch / microbatches / finish_minibatch / optimizer step."""
     from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
     odc.init_nvshmem(dev)
-    model = FusedDecoderLM(cfg, device=dev, seed=0)
+    source = build_decoder(args, cfg, dev) if args.hf_checkpoint else None   # else: the seeded initial weights
+    model = FusedDecoderLM(cfg, device=dev, seed=0, source=source)
+    del source
     opt = FusedOptimizer(model, lr=args.lr, weight_decay=0.01)
     data = make_dataset(args, cfg, rank, world, True)
     init_logging(args, rank)
@@ -166,6 +166,7 @@ def main_fused(args, cfg, dev, rank, world):
         log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
                                  "tokens_per_s": int(tok) / times["minibatch_time"], "grad_norm": grad_norm, **times,
                                  **memory_metrics()})
+    export_model(args, model, cfg)
     mark_done(args)
     model.stop()
     dist.destroy_process_group()

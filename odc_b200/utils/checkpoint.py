@@ -73,6 +73,10 @@ class Checkpointer:
     def _model_state(self, model):
         if hasattr(model, "full_state_dict"):  # fused-kernel decoder (collective); same names and shapes as DecoderLM
             return {k: v.cpu() for k, v in model.full_state_dict().items()}
+        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP1
+        if isinstance(model, FSDP1):  # flat parameters: unshard, read the original parameters under their own names
+            with FSDP1.summon_full_params(model, writeback=False):
+                return {k: v.detach().cpu().clone() for k, v in model.named_parameters()}
         if self.dcp_api:
             return get_model_state_dict(model, options=StateDictOptions(full_state_dict=True, cpu_offload=True))
         out = {}
@@ -81,6 +85,19 @@ class Checkpointer:
             if not dist.is_initialized() or dist.get_rank() == 0:
                 out[name] = full.cpu()
         return out
+
+    def export_hf(self, model, cfg, path: str, dtype: torch.dtype = torch.bfloat16) -> None:
+        """Write the model as a Hugging Face Llama / Qwen2 checkpoint folder (collective; rank 0 writes).
+
+        ``cfg`` is the model's ``DecoderConfig``.  The result loads with ``AutoModelForCausalLM.from_pretrained``
+        and with :func:`odc_b200.models.hf.load_hf_checkpoint`.
+        """
+        from ..models.hf import save_hf_checkpoint
+        sd = self._model_state(model)
+        if not dist.is_initialized() or dist.get_rank() == 0:
+            save_hf_checkpoint(path, sd, cfg, dtype=dtype)
+        if dist.is_initialized():
+            dist.barrier()
 
     def save(self, model, optim=None) -> str:
         model_sd = self._model_state(model)

@@ -28,7 +28,7 @@ def test_fsdp2_example_cpu(env, tmp_path):
 
 
 @pytest.mark.parametrize("script,env,packing,extra", [
-    ("train_fsdp2.py", {"ODC": "1"}, "DynamicDiffMicro", []),      # ranks get different numbers of microbatches
+    ("train_fsdp2.py", {"ODC": "1"}, "DynamicDiffMicro", ["--save-hf-checkpoint", "{tmp}/hf_out"]),  # unequal microbatch counts
     ("train_fsdp2.py", {"ODC": "0", "ODC_DEBUG_PACKING": "1", "ODC_WANDB": "1", "WANDB_MODE": "disabled"}, "DynamicSameMicro", []),  # lock-step baseline
     ("train_fsdp1.py", {"ODC": "1"}, "DynamicDiffMicro", ["--loss-head", "logprobs"]),   # per-token log-prob head
     ("train_fsdp2.py", {"ENGINE": "fused"}, "DynamicDiffMicro", []),   # the fused-kernel decoder engine
@@ -40,13 +40,19 @@ def test_llm_trainers_cpu(script, env, packing, extra, tmp_path):
            "127.0.0.1", "--master-port", str(port), os.path.join(REPO, "examples/llm_training", script), "--cpu",
            "--model_name", "tiny", "--steps", "2", "--minibatch_size", "4", "--num-sequences", "32",
            "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512",
-           "--packing_method", packing, "--run_name", "cpu_smoke"] + extra
+           "--packing_method", packing, "--run_name", "cpu_smoke"] + [x.replace("{tmp}", str(tmp_path)) for x in extra]
     r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
     assert [l["step"] for l in lines] == [0, 1]
     assert all(l["loss"] == l["loss"] and l["tokens"] > 0 for l in lines)
     assert (tmp_path / "cpu_smoke.done").exists()
+    if "--save-hf-checkpoint" in extra:   # FSDP2 shards gathered into a Hugging Face checkpoint folder by rank 0
+        sys.path.insert(0, REPO)
+        from odc_b200.models import get_config
+        from odc_b200.models.hf import load_hf_checkpoint
+        cfg, sd = load_hf_checkpoint(str(tmp_path / "hf_out"))
+        assert cfg == get_config("tiny") and tuple(sd["layers.1.mlp.w_down"].shape) == (cfg.hidden_size, cfg.intermediate_size)
     if env.get("ODC_DEBUG_PACKING") == "1":   # every rank's microbatch composition, printed by rank 0
         assert "rank 0 " in r.stdout and "rank 1 " in r.stdout
 
@@ -90,3 +96,36 @@ def test_bench_reference_arm_reports_one_json_line():
                         capture_output=True, text=True, timeout=600, env=dict(os.environ, RANK="1", WORLD_SIZE="2"))
     if "unavailable" in lines[0]:
         assert r1.returncode == 0 and not [l for l in r1.stdout.splitlines() if l.startswith("{")]
+
+
+@pytest.mark.parametrize("script,env", [("train_fsdp2.py", {"ENGINE": "fused"}), ("train_fsdp1.py", {"ODC": "1"})])
+def test_trainers_start_from_a_hugging_face_checkpoint(script, env, tmp_path):
+    """``--hf-checkpoint``: architecture and initial weights come from a checkpoint folder (written here in the
+    Hugging Face layout from a tiny Qwen2-style decoder), not from a preset and a seed."""
+    import torch
+    sys.path.insert(0, REPO)
+    from odc_b200.models import DecoderLM, get_config
+    from odc_b200.models.hf import save_hf_checkpoint
+    cfg = get_config("tiny", qkv_bias=True, tie_embeddings=True, vocab_size=512)
+    src = DecoderLM(cfg)
+    src.reset_parameters(seed=3)
+    ckpt = tmp_path / "ckpt"
+    save_hf_checkpoint(str(ckpt), src.state_dict(), cfg, dtype=torch.float32)
+    e = dict(os.environ, **env, ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(REPO, "examples/llm_training", script), "--cpu",
+           "--hf-checkpoint", str(ckpt), "--steps", "1", "--minibatch_size", "4", "--num-sequences", "16",
+           "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512",
+           "--run_name", "from_hf", "--save-hf-checkpoint", str(tmp_path / "out")]
+    r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    # the trained model was written back in the same layout: same architecture, same names, moved weights
+    from odc_b200.models.hf import load_hf_checkpoint
+    cfg2, sd2 = load_hf_checkpoint(str(tmp_path / "out"))
+    assert cfg2 == cfg and set(sd2) == set(src.state_dict())
+    moved = (sd2["layers.0.attn.wqkv"].float() - src.state_dict()["layers.0.attn.wqkv"]).abs().max()
+    assert 0 < float(moved) < 0.1
+    # the default --model_name is a 1.5B preset: finishing at all means the checkpoint's tiny architecture was used;
+    # near-uniform predictions over its 512 words bound the (sequence-count weighted) loss by ln(512) = 6.24
+    assert len(lines) == 1 and 0.0 < lines[0]["loss"] < 6.5 and lines[0]["tokens"] > 0, lines
