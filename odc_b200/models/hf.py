@@ -12,9 +12,11 @@ converts by renaming and concatenating; nothing is permuted.
     cfg, sd = load_hf_checkpoint("/path/to/Qwen2.5-1.5B")
     FusedDecoderLM(cfg, source=model)  /  fused_model.load_full_state_dict(sd)  /  Checkpointer
 
-Not covered: rotary scaling (``rope_type`` other than ``default``, e.g. the ``llama3`` frequency rescaling of
-Llama 3.1 / 3.2), sliding-window layers, MLP biases: :func:`config_from_hf` refuses them instead of converting
-to a model that computes something else.
+Rotary scaling: ``linear`` and ``llama3`` (Llama 3.1 / 3.2) are carried over as ``DecoderConfig.rope_scaling``; such
+models apply the rotation with PyTorch statements, since the rotary kernel derives its frequencies from
+``rope_theta`` alone.  Not covered: other rotary scalings (yarn, dynamic, longrope), sliding-window layers, MLP
+biases, a bias on ``o_proj``: :func:`config_from_hf` refuses them instead of converting to a model that computes
+something else.
 """
 from __future__ import annotations
 
@@ -43,9 +45,13 @@ def config_from_hf(hf_config, **overrides) -> DecoderConfig:
         raise NotImplementedError(f"model_type {kind!r}: supported are {_SUPPORTED}")
     rope = _get(hf_config, "rope_parameters") or _get(hf_config, "rope_scaling") or {}
     rope_type = rope.get("rope_type", rope.get("type", "default")) if isinstance(rope, Mapping) else "default"
-    if rope_type not in (None, "default"):
-        raise NotImplementedError(f"rotary scaling {rope_type!r} is not implemented (the kernels derive the "
-                                  "frequencies from rope_theta alone)")
+    scaling = None
+    if rope_type in ("llama3", "linear"):
+        keys = ("factor",) if rope_type == "linear" else ("factor", "low_freq_factor", "high_freq_factor",
+                                                          "original_max_position_embeddings")
+        scaling = {"rope_type": rope_type, **{k: float(rope[k]) for k in keys}}
+    elif rope_type not in (None, "default"):
+        raise NotImplementedError(f"rotary scaling {rope_type!r} is not implemented (supported: default, linear, llama3)")
     theta = _get(hf_config, "rope_theta")
     if theta is None and isinstance(rope, Mapping):
         theta = rope.get("rope_theta")
@@ -68,7 +74,7 @@ def config_from_hf(hf_config, **overrides) -> DecoderConfig:
                         rms_eps=float(_get(hf_config, "rms_norm_eps", 1e-6)),
                         rope_theta=float(theta if theta is not None else 10000.0),
                         tie_embeddings=bool(_get(hf_config, "tie_word_embeddings", False)), qkv_bias=qkv_bias,
-                        init_std=float(_get(hf_config, "initializer_range", 0.02)))
+                        init_std=float(_get(hf_config, "initializer_range", 0.02)), rope_scaling=scaling)
     for k, v in overrides.items():
         setattr(cfg, k, v)
     return cfg
@@ -78,7 +84,8 @@ def config_to_hf(cfg: DecoderConfig, model_type: str = None) -> Dict:
     """The ``config.json`` fields of the Hugging Face model with this architecture."""
     model_type = model_type or ("qwen2" if cfg.qkv_bias else "llama")
     arch = {"llama": "LlamaForCausalLM", "qwen2": "Qwen2ForCausalLM", "mistral": "MistralForCausalLM"}[model_type]
-    return {"model_type": model_type, "architectures": [arch], "vocab_size": cfg.vocab_size,
+    extra = {"rope_scaling": dict(cfg.rope_scaling)} if cfg.rope_scaling else {}
+    return {**extra, "model_type": model_type, "architectures": [arch], "vocab_size": cfg.vocab_size,
             "hidden_size": cfg.hidden_size, "intermediate_size": cfg.intermediate_size,
             "num_hidden_layers": cfg.num_layers, "num_attention_heads": cfg.num_heads,
             "num_key_value_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim, "rms_norm_eps": cfg.rms_eps,

@@ -38,6 +38,20 @@ class DecoderConfig:
     init_std: float = 0.02
     activation_checkpointing: bool = False
     ce_chunk: int = 4096
+    # rescaled rotary frequencies ({"rope_type": "llama3" | "linear", "factor": ...}, see ops.reference.rope_inv_freq);
+    # None = plain theta^(-2i/d), which is what the rotary kernel computes itself
+    rope_scaling: Optional[dict] = None
+
+    def rope_inv_freq(self, device) -> Optional[torch.Tensor]:
+        """The rescaled frequencies on ``device`` (cached), or None when the kernel's own frequencies apply."""
+        if not self.rope_scaling or self.rope_scaling.get("rope_type", "default") == "default":
+            return None
+        cache = self.__dict__.setdefault("_inv_freq_cache", {})
+        key = str(device)
+        if key not in cache:
+            from ..ops.reference import rope_inv_freq
+            cache[key] = rope_inv_freq(self.head_dim, self.rope_theta, self.rope_scaling, device=device)
+        return cache[key]
 
     @property
     def qkv_dim(self) -> int:
@@ -106,7 +120,8 @@ class Attention(nn.Module):
         c = self.cfg
         T = x.shape[0]
         qkv = ops.linear(x, self.wqkv, self.bqkv)
-        qkv = ops.rope_qkv(qkv, position_ids, c.num_heads, c.num_kv_heads, c.head_dim, c.rope_theta)
+        qkv = ops.rope_qkv(qkv, position_ids, c.num_heads, c.num_kv_heads, c.head_dim, c.rope_theta,
+                           c.rope_inv_freq(qkv.device))
         nq = c.num_heads * c.head_dim
         o = ops.varlen_attention_qkv(qkv, c.num_heads, c.num_kv_heads, c.head_dim, cu_seqlens, max_seqlen, causal=True)
         return ops.linear(o.reshape(T, nq), self.wo, residual=residual)

@@ -213,13 +213,18 @@ class _Rope(torch.autograd.Function):
         return dqkv, None, None, None, None, None
 
 
-def rope_qkv(qkv, position_ids, n_q: int, n_kv: int, head_dim: int, theta: float):
-    """Rotate the q and k parts of a fused qkv activation; v passes through."""
-    if not qkv.is_cuda:
+def rope_qkv(qkv, position_ids, n_q: int, n_kv: int, head_dim: int, theta: float,
+             inv_freq: Optional[torch.Tensor] = None):
+    """Rotate the q and k parts of a fused qkv activation; v passes through.
+
+    ``inv_freq`` (rescaled rotary frequencies, ``ops.reference.rope_inv_freq``) selects the PyTorch statements on
+    any device: the kernel derives its frequencies from ``theta`` alone.
+    """
+    if not qkv.is_cuda or inv_freq is not None:
         T = qkv.shape[0]
         q, k, v = qkv.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], dim=-1)
-        q = ref.rope(q.reshape(T, n_q, head_dim), position_ids, theta).reshape(T, -1)
-        k = ref.rope(k.reshape(T, n_kv, head_dim), position_ids, theta).reshape(T, -1)
+        q = ref.rope(q.reshape(T, n_q, head_dim), position_ids, theta, inv_freq=inv_freq).reshape(T, -1)
+        k = ref.rope(k.reshape(T, n_kv, head_dim), position_ids, theta, inv_freq=inv_freq).reshape(T, -1)
         return torch.cat([q, k, v], dim=-1)
     return _Rope.apply(qkv, position_ids, n_q, n_kv, head_dim, theta)
 

@@ -28,16 +28,41 @@ def layer_norm(x, weight, bias, eps: float):
                         eps).to(x.dtype)
 
 
-def rope_tables(position_ids: torch.Tensor, head_dim: int, theta: float):
-    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=position_ids.device) / head_dim))
-    ang = position_ids.float()[:, None] * inv[None, :]
+def rope_inv_freq(head_dim: int, theta: float, scaling: Optional[dict] = None, device=None) -> torch.Tensor:
+    """Rotary frequencies ``theta^(-2i/d)``, optionally rescaled.
+
+    ``scaling``: ``{"rope_type": "linear", "factor": f}`` divides every frequency by ``f``;
+    ``{"rope_type": "llama3", "factor", "low_freq_factor", "high_freq_factor",
+    "original_max_position_embeddings"}`` is the Llama 3.1 / 3.2 rule: components whose wavelength is longer than
+    ``original / low_freq_factor`` are slowed down by ``factor``, those shorter than ``original / high_freq_factor``
+    are kept, and the band in between is interpolated linearly in ``original / wavelength``.
+    """
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    if not scaling or scaling.get("rope_type", "default") == "default":
+        return inv
+    kind, factor = scaling["rope_type"], float(scaling["factor"])
+    if kind == "linear":
+        return inv / factor
+    if kind != "llama3":
+        raise NotImplementedError(f"rotary scaling {kind!r}")
+    lo, hi = float(scaling["low_freq_factor"]), float(scaling["high_freq_factor"])
+    orig = float(scaling["original_max_position_embeddings"])
+    turns = orig * inv / (2.0 * math.pi)                 # rotations completed over the original context
+    blend = ((turns - lo) / (hi - lo)).clamp(0.0, 1.0)   # 0: long wavelengths (slowed), 1: short ones (kept)
+    return inv * (blend + (1.0 - blend) / factor)
+
+
+def rope_tables(position_ids: torch.Tensor, head_dim: int, theta: float, inv_freq: Optional[torch.Tensor] = None):
+    inv = inv_freq if inv_freq is not None else rope_inv_freq(head_dim, theta, device=position_ids.device)
+    ang = position_ids.float()[:, None] * inv.to(position_ids.device)[None, :]
     return ang.cos(), ang.sin()
 
 
-def rope(x: torch.Tensor, position_ids: torch.Tensor, theta: float, inverse: bool = False):
+def rope(x: torch.Tensor, position_ids: torch.Tensor, theta: float, inverse: bool = False,
+         inv_freq: Optional[torch.Tensor] = None):
     """Rotate-half rotary embedding on ``x`` of shape ``[T, H, D]`` (HF Llama/Qwen convention)."""
     d = x.shape[-1]
-    cos, sin = rope_tables(position_ids, d, theta)
+    cos, sin = rope_tables(position_ids, d, theta, inv_freq)
     if inverse:
         sin = -sin
     xf = x.float()

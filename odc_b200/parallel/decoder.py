@@ -239,7 +239,8 @@ class FusedDecoderLayer(nn.Module):
         h, x = ops.rms_norm_residual(x, s.view(f"layers.{i}.attn_norm.weight", (c.hidden_size,)), c.rms_eps)
         bias = s.view(f"layers.{i}.attn.bqkv", (c.qkv_dim,)) if c.qkv_bias else None
         qkv = self.wqkv(h, bias=bias)
-        qkv = ops.rope_qkv(qkv, position_ids, c.num_heads, c.num_kv_heads, c.head_dim, c.rope_theta)
+        qkv = ops.rope_qkv(qkv, position_ids, c.num_heads, c.num_kv_heads, c.head_dim, c.rope_theta,
+                           c.rope_inv_freq(qkv.device))
         o = ops.varlen_attention_qkv(qkv, c.num_heads, c.num_kv_heads, c.head_dim, cu_seqlens, max_seqlen, causal=True)
         x = self.wo(o.reshape(T, c.num_heads * c.head_dim), residual=x)
         h, x = ops.rms_norm_residual(x, s.view(f"layers.{i}.mlp_norm.weight", (c.hidden_size,)), c.rms_eps)

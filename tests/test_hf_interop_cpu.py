@@ -6,7 +6,16 @@ transformers = pytest.importorskip("transformers")
 
 
 def _tiny(kind):
-    if kind == "llama":
+    if kind == "llama3_scaled":   # Llama 3.1 / 3.2: rescaled rotary frequencies; 16 original positions put the 8
+        # frequencies of a 16-wide head into all three bands of the rule
+        conf = transformers.LlamaConfig(vocab_size=211, hidden_size=64, intermediate_size=112, num_hidden_layers=2,
+                                        num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5,
+                                        tie_word_embeddings=True,
+                                        rope_parameters={"rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0,
+                                                         "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                                         "original_max_position_embeddings": 16})
+        cls = transformers.LlamaForCausalLM
+    elif kind == "llama":
         conf = transformers.LlamaConfig(vocab_size=211, hidden_size=64, intermediate_size=112, num_hidden_layers=2,
                                         num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5,
                                         rope_theta=50000.0, tie_word_embeddings=False)
@@ -26,14 +35,15 @@ def _tiny(kind):
     return conf, model
 
 
-@pytest.mark.parametrize("kind", ["llama", "qwen2"])
+@pytest.mark.parametrize("kind", ["llama", "qwen2", "llama3_scaled"])
 def test_hf_checkpoint_gives_the_same_logits(kind, tmp_path):
     from odc_b200.models import DecoderLM
     from odc_b200.models import hf
     conf, hf_model = _tiny(kind)
     cfg = hf.config_from_hf(conf)
-    assert cfg.qkv_bias == (kind == "qwen2") and cfg.tie_embeddings == (kind == "qwen2")
-    assert cfg.head_dim == 16 and cfg.num_kv_heads == (2 if kind == "llama" else 1)
+    assert cfg.qkv_bias == (kind == "qwen2") and cfg.tie_embeddings == (kind != "llama")
+    assert cfg.head_dim == 16 and cfg.num_kv_heads == (1 if kind == "qwen2" else 2)
+    assert (cfg.rope_scaling is not None) == (kind == "llama3_scaled")
     sd = hf.state_dict_from_hf(hf_model.state_dict(), cfg)
     model = DecoderLM(cfg)
     model.load_state_dict(sd)
@@ -71,7 +81,7 @@ def test_unsupported_hf_configs_are_refused():
     base = dict(model_type="llama", vocab_size=128, hidden_size=64, intermediate_size=96, num_hidden_layers=1,
                 num_attention_heads=4, num_key_value_heads=2)
     with pytest.raises(NotImplementedError, match="rotary scaling"):
-        hf.config_from_hf(dict(base, rope_scaling={"rope_type": "llama3", "factor": 32.0}))
+        hf.config_from_hf(dict(base, rope_scaling={"rope_type": "yarn", "factor": 32.0}))
     with pytest.raises(NotImplementedError, match="model_type"):
         hf.config_from_hf(dict(base, model_type="gpt2"))
     with pytest.raises(NotImplementedError, match="o_proj"):
