@@ -88,3 +88,120 @@ def test_unsupported_hf_configs_are_refused():
         hf.config_from_hf(dict(base, attention_bias=True))
     cfg = hf.config_from_hf(dict(base, rope_theta=5e5, activation_checkpointing=None), activation_checkpointing=True)
     assert cfg.rope_theta == 5e5 and cfg.activation_checkpointing and cfg.head_dim == 16
+
+
+def _train_hf_model(rank, world, mode):
+    """The reference's own usage: a Hugging Face causal LM, ``fully_shard`` per decoder layer + root, the patch
+    calls in the order its README gives, packed sequences through ``position_ids``; ranks run 2 and 3 microbatches."""
+    import torch.distributed as dist
+    from torch.distributed.fsdp import fully_shard
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp2
+
+    conf = transformers.Qwen2Config(vocab_size=257, hidden_size=64, intermediate_size=112, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
+    conf._attn_implementation = "eager"
+    torch.manual_seed(0)
+    model = transformers.Qwen2ForCausalLM(conf).float()
+    if mode == "odc":
+        odc.init_nvshmem("cpu", 256 << 20)
+        fsdp2.patch_fsdp2()
+    for layer in model.model.layers:
+        fully_shard(layer)
+    fully_shard(model)
+    if mode == "odc":
+        for layer in model.model.layers:
+            fsdp2.patch_lazy_init(layer)
+        fsdp2.patch_lazy_init(model)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for step in range(3):
+        if mode == "odc":
+            fsdp2.pre_minibatch_start(model)
+        mine = 2 + rank
+        n_micro = mine if mode == "odc" else 2 + world - 1   # lock-step FSDP pads the short rank with zero-weight work
+        total = torch.zeros(())
+        for i in range(n_micro):
+            g = torch.Generator().manual_seed(1000 * step + 10 * (i if i < mine else 0) + rank)
+            ids = torch.randint(0, 257, (1, 24), generator=g)
+            out = model(input_ids=ids, labels=ids)
+            loss = out.loss / 4.0 * (1.0 if i < mine else 0.0)
+            loss.backward()
+            total += loss.detach()
+        if mode == "odc":
+            fsdp2.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+        dist.all_reduce(total)
+        losses.append(float(total))
+    full = {k: v.full_tensor().clone() for k, v in model.state_dict().items()}
+    if mode == "odc":
+        fsdp2.stop()
+    return losses, full
+
+
+def test_patch_works_on_a_hugging_face_model_as_in_the_reference_readme():
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from _mp import assert_mostly_close, run_pair
+    a, b = run_pair(_train_hf_model, 2)
+    assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        assert_mostly_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
+
+
+def _train_hf_model_fsdp1(rank, world, mode):
+    """The same with FSDP1 flat parameters, in the reference README's order (patch before ``FSDP(...)``)."""
+    import torch.distributed as dist
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+    from torch.distributed.fsdp.wrap import ModuleWrapPolicy
+    from transformers.models.qwen2.modeling_qwen2 import Qwen2DecoderLayer
+
+    import odc_b200 as odc
+    from odc_b200.fsdp import fsdp1
+
+    if mode == "odc":
+        fsdp1.patch_fsdp1()
+        odc.init_nvshmem("cpu", 256 << 20)
+    conf = transformers.Qwen2Config(vocab_size=257, hidden_size=64, intermediate_size=112, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, tie_word_embeddings=False)
+    conf._attn_implementation = "eager"
+    torch.manual_seed(0)
+    model = FSDP(transformers.Qwen2ForCausalLM(conf).float(), auto_wrap_policy=ModuleWrapPolicy({Qwen2DecoderLayer}),
+                 device_id=torch.device("cpu"), use_orig_params=False)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-3)
+    losses = []
+    for step in range(3):
+        if mode == "odc":
+            fsdp1.pre_minibatch_start(model)
+        mine = 2 + rank
+        n_micro = mine if mode == "odc" else 2 + world - 1
+        total = torch.zeros(())
+        for i in range(n_micro):
+            g = torch.Generator().manual_seed(1000 * step + 10 * (i if i < mine else 0) + rank)
+            ids = torch.randint(0, 257, (1, 24), generator=g)
+            loss = model(input_ids=ids, labels=ids).loss / 4.0 * (1.0 if i < mine else 0.0)
+            loss.backward()
+            total += loss.detach()
+        if mode == "odc":
+            fsdp1.pre_optimizer_step(model)
+        opt.step()
+        opt.zero_grad()
+        dist.all_reduce(total)
+        losses.append(float(total))
+    with FSDP.summon_full_params(model):
+        full = {k: v.detach().clone() for k, v in model.named_parameters()}
+    if mode == "odc":
+        fsdp1.stop()
+    return losses, full
+
+
+def test_fsdp1_patch_works_on_a_hugging_face_model():
+    import sys, os
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from _mp import assert_mostly_close, run_pair
+    a, b = run_pair(_train_hf_model_fsdp1, 2)
+    assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
+    for k in a[0][1]:
+        assert_mostly_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
