@@ -178,3 +178,14 @@ def save_hf_checkpoint(path: str, sd: Mapping[str, torch.Tensor], cfg: DecoderCo
     conf["torch_dtype"] = str(dtype).replace("torch.", "")
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(conf, f, indent=2)
+
+
+def decoder_from_hf(path: str, device=None, **config_overrides):
+    """An unsharded ``DecoderLM`` (fp32 parameters on ``device``) holding the checkpoint folder's weights: wrap it
+    with ``fully_shard`` / ``FSDP(...)``, or hand it to ``FusedDecoderLM(cfg, source=...)``."""
+    from .llama import DecoderLM
+    cfg, sd = load_hf_checkpoint(path, **config_overrides)
+    with torch.device(device or "cpu"):
+        model = DecoderLM(cfg)
+    model.load_state_dict(sd)
+    return model

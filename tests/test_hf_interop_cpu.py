@@ -74,6 +74,9 @@ def test_hf_checkpoint_gives_the_same_logits(kind, tmp_path):
         torch.testing.assert_close(again(input_ids=ids[None]).logits[0], want, rtol=1e-4, atol=1e-4)
     cfg2, sd2 = hf.load_hf_checkpoint(str(tmp_path))
     assert cfg2 == cfg and set(sd2) == set(sd) and all(torch.equal(sd2[k], sd[k]) for k in sd)
+    loaded = hf.decoder_from_hf(str(tmp_path))
+    with torch.no_grad():
+        torch.testing.assert_close(loaded.logits(ids, torch.arange(T), torch.tensor([0, T], dtype=torch.int32), T), got)
 
 
 def test_unsupported_hf_configs_are_refused():
