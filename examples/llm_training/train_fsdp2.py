@@ -129,7 +129,8 @@ def main_fused(args, cfg, dev, rank, world):
     from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
     odc.init_nvshmem(dev)
     source = build_decoder(args, cfg, dev) if args.hf_checkpoint else None   # else: the seeded initial weights
-    model = FusedDecoderLM(cfg, device=dev, seed=0, source=source)
+    mesh = init_device_mesh(dev.type, (2, world // 2), mesh_dim_names=("dp_replicate", "dp_shard")) if HSDP else None
+    model = FusedDecoderLM(cfg, device=dev, seed=0, source=source, mesh=mesh)
     del source
     opt = FusedOptimizer(model, lr=args.lr, weight_decay=0.01)
     data = make_dataset(args, cfg, rank, world, True)

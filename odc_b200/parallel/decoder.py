@@ -68,7 +68,7 @@ class SmallGroup:
         self.v = torch.zeros_like(self.master)
         self.full = torch.zeros(self.shard * self.world, dtype=lowp_dtype, device=device, requires_grad=True)
         self.grad32 = torch.zeros(self.shard * self.world, dtype=torch.float32, device=device)
-        self.grad_scale = 1.0 / self.world
+        self.grad_scale = 1.0 / (self.world * L.replicas())
         self.dirty = False
         self.full.register_post_accumulate_grad_hook(self._fold)
 
@@ -251,8 +251,15 @@ class FusedDecoderLM(nn.Module):
     """``DecoderLM`` with every matrix sharded by rows and every matrix product fused with its transfer."""
 
     def __init__(self, cfg: DecoderConfig, device=None, seed: Optional[int] = 0, pg=None, keep_weight: bool = False,
-                 lowp_dtype: Optional[torch.dtype] = None, source: Optional[DecoderLM] = None):
+                 lowp_dtype: Optional[torch.dtype] = None, source: Optional[DecoderLM] = None, replicate_pg=None,
+                 mesh=None):
+        """``pg``: the group the rows are sharded over (default: all ranks).  ``replicate_pg``: hybrid sharding, the
+        ranks that hold the same rows as this one; or pass a 2-D ``mesh`` with dimensions
+        ``("dp_replicate", "dp_shard")`` as for ``fully_shard``."""
         super().__init__()
+        if mesh is not None:
+            pg, replicate_pg = mesh.get_group("dp_shard"), mesh.get_group("dp_replicate")
+        L.set_replicate_group(replicate_pg)
         reg = SymmBufferRegistry.get_instance()
         device = torch.device(device) if device is not None else reg.heap.device
         if lowp_dtype is None:

@@ -37,6 +37,7 @@ _params: List["ShardedParameter"] = []
 _reduction: Optional[ReductionService] = None
 _next_id = 0
 _sync_grads = True
+_replicate_pg = None   # HSDP: the group of ranks that hold the same rows as this one (None: no replication)
 
 
 def _service() -> ReductionService:
@@ -44,6 +45,19 @@ def _service() -> ReductionService:
     if _reduction is None:
         _reduction = ReductionService(accumulation_dtype=torch.float32)
     return _reduction
+
+
+def set_replicate_group(pg) -> None:
+    """Hybrid sharding: parameters are sharded over their own group and replicated over ``pg``.  Gradients are
+    pushed to the owners inside the shard group during the minibatch and summed over ``pg`` once, after the
+    per-minibatch synchronisation (the reference defers the replicate-dimension all-reduce the same way,
+    odc/fsdp/fsdp2.py:849-882).  Set before the parameters are created."""
+    global _replicate_pg
+    _replicate_pg = pg
+
+
+def replicas() -> int:
+    return 1 if _replicate_pg is None else dist.get_world_size(_replicate_pg)
 
 
 def set_requires_gradient_sync(flag: bool) -> None:
@@ -89,7 +103,7 @@ class ShardedParameter:
         self.acc = _service().register(self.key, self.rows_per_rank * self.in_features, torch.float32, pg)
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
-        self.grad_scale = 1.0 / self.world
+        self.grad_scale = 1.0 / (self.world * replicas())
         # deferred synchronisation: unsharded fp32 gradient of this rank's own microbatches
         self.local_grad: Optional[torch.Tensor] = None
         self.local_dirty = False
@@ -277,6 +291,9 @@ def finish_minibatch(lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, we
     """Wait for all contributions (collective), then AdamW on every layer's own rows."""
     flush_local_grads()
     _service().sync()
+    if _replicate_pg is not None and replicas() > 1:
+        for acc in _service().accumulations.values():   # one all-reduce per matrix and minibatch
+            dist.all_reduce(acc, group=_replicate_pg)
     if not optimizer_step:
         return
     for layer in _layers:
@@ -285,9 +302,10 @@ def finish_minibatch(lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, we
 
 
 def reset() -> None:
-    global _reduction, _next_id, _sync_grads
+    global _reduction, _next_id, _sync_grads, _replicate_pg
     _layers.clear()
     _params.clear()
     _reduction = None
     _next_id = 0
     _sync_grads = True
+    _replicate_pg = None

@@ -487,3 +487,21 @@ def test_fused_engine_matches_stock_fsdp2_over_nvlink(defer):
     if _ngpu() < 2:
         pytest.skip("needs 2 GPUs")
     _launch(FUSED_ENGINE.replace("__DEFER__", str(defer)), 2, timeout=600)
+
+
+FUSED_ENGINE_HSDP = FUSED_ENGINE.replace(
+    "DEFER = __DEFER__",
+    "DEFER = False\nfrom torch.distributed.device_mesh import init_device_mesh\n"
+    "MESH = init_device_mesh('cuda', (2, world // 2), mesh_dim_names=('dp_replicate', 'dp_shard'))").replace(
+    "FusedDecoderLM(cfg, device=dev, seed=0)", "FusedDecoderLM(cfg, device=dev, seed=0, mesh=MESH)").replace(
+    "fully_shard(layer, mp_policy=mp)", "fully_shard(layer, mp_policy=mp, mesh=MESH)").replace(
+    "fully_shard(model, mp_policy=mp)", "fully_shard(model, mp_policy=mp, mesh=MESH)")
+
+
+def test_fused_engine_hybrid_sharding_over_nvlink():
+    """2 replicas x 2 shards: the fused kernels pull and push inside each shard pair, the replicate-dimension sum runs
+    once per minibatch over NCCL; against stock FSDP2 on the same 2-D mesh, unequal microbatch counts."""
+    if _ngpu() < 4:
+        pytest.skip("needs 4 GPUs")
+    assert FUSED_ENGINE_HSDP.count("mesh=MESH") == 3
+    _launch(FUSED_ENGINE_HSDP, 4, timeout=600)
