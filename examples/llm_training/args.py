@@ -17,6 +17,10 @@ def get_args():
                         "architecture and weights replace --model_name and the seeded initialisation")
     p.add_argument("--save-hf-checkpoint", default=None,
                    help="after the last step, write the model to this folder in the Hugging Face layout")
+    p.add_argument("--checkpoint-dir", default=None,
+                   help="train_fsdp2.py: resume from the newest checkpoint in this folder if there is one, and save there")
+    p.add_argument("--checkpoint-every", type=int, default=0,
+                   help="save model + optimizer every N minibatches (0: only after the last one)")
     p.add_argument("--packing_method", default="DynamicDiffMicro",
                    choices=["None", "DynamicSameMicro", "DynamicDiffMicro", "LocalSort", "DebugUneven"])
     p.add_argument("--cost_model", default="linear", choices=["linear", "fit", "flops"])

@@ -146,6 +146,49 @@ def memory_metrics():
             "symm_mem_gib": symm}
 
 
+def open_checkpoint(args):
+    """``--checkpoint-dir``: the checkpoint folder handle (``None`` without the flag)."""
+    if not args.checkpoint_dir:
+        return None
+    from odc_b200.utils.checkpoint import Checkpointer
+    return Checkpointer(args.checkpoint_dir)
+
+
+def maybe_save(args, ck, model, opt, next_step, last):
+    """Save after every ``--checkpoint-every`` minibatches and after the last one (collective)."""
+    if ck is None or args.forward_only:
+        return
+    if last or (args.checkpoint_every > 0 and next_step % args.checkpoint_every == 0):
+        ck.save(model, opt, meta={"next_step": next_step})
+
+
+def run_guarded(rank, body):
+    """Run the training loop; a peer that left or a wait that ran out ends this rank with exit code 75 (temporary
+    failure) and one JSON line, so that a launcher can restart the job, which resumes from ``--checkpoint-dir``."""
+    from odc_b200.runtime.status import OdcTimeoutError, PeerFailure
+    try:
+        return body()
+    except (PeerFailure, OdcTimeoutError) as e:
+        print(json.dumps({"event": "failure", "rank": rank, "kind": type(e).__name__, "message": str(e)[:300]}), flush=True)
+        os._exit(75)   # no collective shutdown: the peers are not all there
+
+
+def inject_leave(rank, step):
+    """Failure drill, made on the host: ``ODC_INJECT_LEAVE="<rank>:<step>"`` lets that rank leave the job right before
+    that minibatch, between steps, with nothing of its own in flight.  The others report it (``run_guarded``)."""
+    spec = os.environ.get("ODC_INJECT_LEAVE")
+    if not spec:
+        return
+    r, s = (int(x) for x in spec.split(":"))
+    if r == rank and s == step:
+        from odc_b200.runtime import control
+        hb = control.heartbeat()
+        if hb is not None:
+            hb.mark_leaving()
+        print(json.dumps({"event": "leaving", "rank": rank, "step": step}), flush=True)
+        os._exit(0)
+
+
 def export_model(args, model, cfg):
     """``--save-hf-checkpoint``: the trained weights as a Hugging Face checkpoint folder (collective)."""
     if args.save_hf_checkpoint:

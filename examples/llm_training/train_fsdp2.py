@@ -1,7 +1,13 @@
 """LLM trainer on FSDP2 (counterpart of the reference's examples/llm_training/torch_fsdp2.py).
 
-Environment switches: ``ODC`` (default 1), ``HPZ``, ``HSDP``, ``ENGINE=fused`` (the fused-kernel decoder engine); ``TORCH_PROFILED=1`` writes a chrome
-trace per rank; ``CUDA_PROFILED=1`` brackets the last minibatch with cudaProfilerStart/Stop.
+Environment switches: ``ODC`` (default 1), ``HPZ``, ``HSDP``, ``ENGINE=fused`` (the fused-kernel decoder engine);
+``TORCH_PROFILED=1`` writes a chrome trace per rank; ``CUDA_PROFILED=1`` brackets the last minibatch with
+cudaProfilerStart/Stop.
+
+``--checkpoint-dir`` / ``--checkpoint-every``: model + optimizer + next step are saved there and a restarted job
+resumes from the newest one.  A peer that left or a bounded wait that ran out ends a rank with exit code 75 and one
+JSON line (``ODC_HEARTBEAT_S`` > 0 makes a departed rank visible at the next host barrier instead of after the wait
+budget); ``ODC_INJECT_LEAVE="<rank>:<step>"`` rehearses that on the host.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         examples/llm_training/train_fsdp2.py --model_name llama3.2-1b --packing_method DynamicDiffMicro --max_token_len 16384
@@ -15,8 +21,9 @@ from torch.distributed.device_mesh import init_device_mesh
 from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
 
 from args import get_args
-from common import (Timer, build_decoder, export_model, init_device, init_logging, log_metrics, log_packing,
-                    make_dataset, mark_done, memory_metrics, microbatch_loss, model_config)
+from common import (Timer, build_decoder, export_model, init_device, init_logging, inject_leave, log_metrics, log_packing,
+                    make_dataset, mark_done, maybe_save, memory_metrics, microbatch_loss, model_config, open_checkpoint,
+                    run_guarded)
 
 import odc_b200 as odc
 from odc_b200.data import to_device
@@ -48,12 +55,20 @@ def main():
     for layer in model.layers:
         fully_shard(layer, mesh=mesh, mp_policy=mp, reshard_after_forward=raf)
     fully_shard(model, mesh=mesh, mp_policy=mp, reshard_after_forward=raf)
+    ck = open_checkpoint(args)
+    resume = ck is not None and not ck.is_empty()
+    if resume:
+        ck.load_model(model)   # before the shards move into the symmetric heap (first forward after patch_lazy_init)
     if ODC:
         for m in list(model.layers) + [model]:
             fsdp2.patch_lazy_init(m)
     use_fused = ODC and os.environ.get("FUSED_OPTIMIZER", "1") == "1"
     opt = fsdp2.FusedAdamW(model, lr=args.lr, weight_decay=0.01) if use_fused else \
         torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
+    first_step = 0
+    if resume:
+        ck.load_optim(model, opt)
+        first_step = int(ck.load_meta().get("next_step", 0))
     data = make_dataset(args, cfg, rank, world, ODC)
     init_logging(args, rank)
     prof = None
@@ -61,8 +76,9 @@ def main():
         prof = torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA])
         prof.start()
     steps = min(args.steps, len(data))
-    for step in range(steps):
+    for step in range(first_step, steps):
         times = {}
+        inject_leave(rank, step)
         if os.environ.get("CUDA_PROFILED", "0") == "1" and step == steps - 1:
             torch.cuda.cudart().cudaProfilerStart()
         microbatches = data[step]
@@ -110,6 +126,7 @@ def main():
         log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
                                  "tokens_per_s": int(tok) / times["minibatch_time"],
                                  "grad_norm": float(grad_norm) if not args.forward_only else 0.0, **times, **memory_metrics()})
+        maybe_save(args, ck, model, opt, step + 1, last=step == steps - 1)
     if os.environ.get("CUDA_PROFILED", "0") == "1":
         torch.cuda.cudart().cudaProfilerStop()
     if prof is not None:
@@ -133,11 +150,18 @@ def main_fused(args, cfg, dev, rank, world):
     model = FusedDecoderLM(cfg, device=dev, seed=0, source=source, mesh=mesh)
     del source
     opt = FusedOptimizer(model, lr=args.lr, weight_decay=0.01)
+    ck = open_checkpoint(args)
+    first_step = 0
+    if ck is not None and not ck.is_empty():
+        ck.load_model(model)
+        ck.load_optim(model, opt)
+        first_step = int(ck.load_meta().get("next_step", 0))
     data = make_dataset(args, cfg, rank, world, True)
     init_logging(args, rank)
     steps = min(args.steps, len(data))
-    for step in range(steps):
+    for step in range(first_step, steps):
         times = {}
+        inject_leave(rank, step)
         microbatches = data[step]
         log_packing(data, rank)
         with Timer("minibatch_time", times):
@@ -167,6 +191,7 @@ def main_fused(args, cfg, dev, rank, world):
         log_metrics(rank, step, {"loss": float(total) / world, "tokens": int(tok), "microbatches": len(microbatches),
                                  "tokens_per_s": int(tok) / times["minibatch_time"], "grad_norm": grad_norm, **times,
                                  **memory_metrics()})
+        maybe_save(args, ck, model, opt, step + 1, last=step == steps - 1)
     export_model(args, model, cfg)
     mark_done(args)
     model.stop()
@@ -174,4 +199,4 @@ def main_fused(args, cfg, dev, rank, world):
 
 
 if __name__ == "__main__":
-    main()
+    run_guarded(int(os.environ.get("RANK", "0")), main)

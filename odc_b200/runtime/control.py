@@ -75,11 +75,11 @@ def heartbeat():
     return _heartbeat
 
 
-def check_peers_alive() -> None:
+def check_peers_alive(missing_is_dead: bool = True) -> None:
     """Raise ``PeerFailure`` if a peer stopped publishing heartbeats (no-op unless ``ODC_HEARTBEAT_S`` is set)."""
     hb = heartbeat()
     if hb is not None:
-        hb.assert_alive(config.heartbeat_s())
+        hb.assert_alive(config.heartbeat_s(), missing_is_dead)
 
 
 def all_gather_object(obj: Any) -> List[Any]:
@@ -107,8 +107,16 @@ def broadcast_object(obj: Any, src: int = 0) -> Any:
 def host_barrier() -> None:
     """Barrier on the control group: orders host code only, touches no CUDA stream."""
     pg = control_group()
-    if pg is not None:
+    if pg is None:
+        return
+    # with heartbeats on, a rank that left is reported here instead of timing the barrier out (a peer that has not
+    # published yet is still starting up: barriers run during start-up too)
+    check_peers_alive(missing_is_dead=False)
+    try:
         dist.barrier(group=pg)
+    except (RuntimeError, dist.DistBackendError) as e:
+        from .status import PeerFailure
+        raise PeerFailure(f"rank {rank()}: host barrier failed, a peer did not take part: {e}") from e
 
 
 def group_ranks(pg: Optional[dist.ProcessGroup]) -> List[int]:

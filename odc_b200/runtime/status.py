@@ -114,18 +114,22 @@ class Heartbeat:
                 out[r] = None
         return out
 
-    def dead_peers(self, max_age_s: float) -> List[int]:
-        """Peers that never published, said they were leaving, or whose last beat is older than ``max_age_s``."""
+    def dead_peers(self, max_age_s: float, missing_is_dead: bool = True) -> List[int]:
+        """Peers that never published (unless ``missing_is_dead`` is off: a job that is still starting up), said they
+        were leaving, or whose last beat is older than ``max_age_s``."""
         now = time.time()
         dead = []
         for r, v in self.read().items():
             if r == self.rank:
                 continue
-            if v is None or v[0] == "gone" or now - v[1] > max_age_s:
+            if v is None:
+                if missing_is_dead:
+                    dead.append(r)
+            elif v[0] == "gone" or now - v[1] > max_age_s:
                 dead.append(r)
         return dead
 
-    def assert_alive(self, max_age_s: float) -> None:
-        dead = self.dead_peers(max_age_s)
+    def assert_alive(self, max_age_s: float, missing_is_dead: bool = True) -> None:
+        dead = self.dead_peers(max_age_s, missing_is_dead)
         if dead:
             raise PeerFailure(f"rank {self.rank}: peers {dead} stopped publishing heartbeats")

@@ -13,6 +13,7 @@ after a later ``load_state_dict(assign=True)`` call :func:`odc_b200.fsdp.fsdp2.r
 """
 from __future__ import annotations
 
+import json
 import os
 import time
 from typing import Optional
@@ -25,6 +26,7 @@ from torch.distributed.tensor import DTensor, distribute_tensor
 
 MODEL_FILE = "model_state_dict.pt"
 OPTIM_FILE = "optim_state_dict.pt"
+META_FILE = "meta.json"
 
 
 class Checkpointer:
@@ -43,6 +45,16 @@ class Checkpointer:
         return self.last_training_time is None
 
     # ------------------------------------------------------------------ load
+    def load_meta(self) -> dict:
+        """What ``save(..., meta=...)`` stored next to the newest checkpoint (e.g. the next step to run), or ``{}``."""
+        if self.last_training_time is None:
+            return {}
+        path = os.path.join(self.folder, self.last_training_time, META_FILE)
+        if not os.path.exists(path):
+            return {}
+        with open(path) as f:
+            return json.load(f)
+
     def load_model(self, model) -> None:
         path = os.path.join(self.folder, self.last_training_time, MODEL_FILE)
         full = torch.load(path, mmap=True, weights_only=True, map_location="cpu")
@@ -99,7 +111,7 @@ class Checkpointer:
         if dist.is_initialized():
             dist.barrier()
 
-    def save(self, model, optim=None) -> str:
+    def save(self, model, optim=None, meta: Optional[dict] = None) -> str:
         model_sd = self._model_state(model)
         optim_sd = None
         if optim is not None and hasattr(optim, "full_state_dict"):
@@ -118,6 +130,9 @@ class Checkpointer:
             torch.save(model_sd, os.path.join(folder, MODEL_FILE))
             if optim_sd is not None:
                 torch.save(optim_sd, os.path.join(folder, OPTIM_FILE))
+            if meta is not None:
+                with open(os.path.join(folder, META_FILE), "w") as f:
+                    json.dump(meta, f)
         if dist.is_initialized():
             dist.barrier()
         self.last_training_time = stamp

@@ -129,3 +129,55 @@ def test_trainers_start_from_a_hugging_face_checkpoint(script, env, tmp_path):
     # the default --model_name is a 1.5B preset: finishing at all means the checkpoint's tiny architecture was used;
     # near-uniform predictions over its 512 words bound the (sequence-count weighted) loss by ln(512) = 6.24
     assert len(lines) == 1 and 0.0 < lines[0]["loss"] < 6.5 and lines[0]["tokens"] > 0, lines
+
+
+@pytest.mark.parametrize("env", [{"ENGINE": "fused"}, {"ODC": "1"}])
+def test_trainer_resumes_from_its_checkpoint(env, tmp_path):
+    """Two minibatches, stop, start again with ``--steps 3``: the job runs only the third minibatch, from the saved
+    model, optimizer state and step, and its loss is the one an uninterrupted run sees."""
+    def run(steps, ckpt):
+        e = dict(os.environ, **env, ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path))
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), os.path.join(REPO, "examples/llm_training/train_fsdp2.py"),
+               "--cpu", "--model_name", "tiny", "--steps", str(steps), "--minibatch_size", "4", "--num-sequences", "32",
+               "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512", "--lr", "1e-3",
+               "--run_name", "resume"] + (["--checkpoint-dir", str(ckpt), "--checkpoint-every", "1"] if ckpt else [])
+        r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+        return {l["step"]: l["loss"] for l in (json.loads(x) for x in r.stdout.splitlines() if x.startswith("{"))}
+
+    whole = run(3, None)
+    first = run(2, tmp_path / "ck")
+    second = run(3, tmp_path / "ck")
+    assert sorted(whole) == [0, 1, 2] and sorted(first) == [0, 1] and sorted(second) == [2]
+    assert first[1] == pytest.approx(whole[1], rel=1e-4)
+    assert second[2] == pytest.approx(whole[2], rel=1e-3)
+    assert second[2] != pytest.approx(whole[0], rel=1e-3)   # not a fresh start
+
+
+def test_trainer_failure_drill_and_restart(tmp_path):
+    """A rank leaves between minibatches (made on the host); the other reports it and exits with the temporary-failure
+    code instead of waiting; the restarted job resumes from the checkpoint and finishes."""
+    def run(steps, extra_env):
+        e = dict(os.environ, ENGINE="fused", ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path), ODC_HEARTBEAT_S="30",
+                 ODC_WAIT_TIMEOUT_MS="20000", **extra_env)
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), os.path.join(REPO, "examples/llm_training/train_fsdp2.py"),
+               "--cpu", "--model_name", "tiny", "--steps", str(steps), "--minibatch_size", "4", "--num-sequences", "32",
+               "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512",
+               "--run_name", "drill", "--checkpoint-dir", str(tmp_path / "ck"), "--checkpoint-every", "1"]
+        r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
+        return r, [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+
+    r, lines = run(3, {"ODC_INJECT_LEAVE": "1:2"})
+    assert r.returncode != 0
+    events = [l for l in lines if "event" in l]
+    assert {"event": "leaving", "rank": 1, "step": 2} in events
+    failures = [l for l in events if l["event"] == "failure"]
+    assert len(failures) == 1 and failures[0]["rank"] == 0 and failures[0]["kind"] == "PeerFailure", events
+    assert [l["step"] for l in lines if "step" in l and "event" not in l] == [0, 1]
+    assert "exitcode  : 75" in r.stderr or "exitcode: 75" in r.stderr
+    r2, lines2 = run(3, {})
+    assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-3000:]
+    assert [l["step"] for l in lines2 if "step" in l] == [2]
+    assert (tmp_path / "drill.done").exists()
