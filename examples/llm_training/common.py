@@ -177,8 +177,8 @@ def inject_leave(rank, step):
     """Failure drill, made on the host: ``ODC_INJECT_LEAVE="<rank>:<step>"`` lets that rank leave the job right before
     that minibatch, between steps, with nothing of its own in flight.  The others report it (``run_guarded``)."""
     spec = os.environ.get("ODC_INJECT_LEAVE")
-    if not spec:
-        return
+    if not spec or os.environ.get("ODC_LAUNCH_ATTEMPT", "0") != "0":
+        return   # only the first attempt of a job leaves; one that launch.sh restarted runs through
     r, s = (int(x) for x in spec.split(":"))
     if r == rank and s == step:
         from odc_b200.runtime import control

@@ -181,3 +181,21 @@ def test_trainer_failure_drill_and_restart(tmp_path):
     assert r2.returncode == 0, r2.stdout[-2000:] + r2.stderr[-3000:]
     assert [l["step"] for l in lines2 if "step" in l] == [2]
     assert (tmp_path / "drill.done").exists()
+
+
+def test_launcher_restarts_a_failed_job_which_resumes(tmp_path):
+    """``MAX_RESTARTS=1 bash launch.sh ...``: the drill's failure ends the first attempt, the launcher starts all ranks
+    again, and the second attempt resumes from the checkpoint and completes."""
+    e = dict(os.environ, ENGINE="fused", ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path), ODC_HEARTBEAT_S="30",
+             ODC_WAIT_TIMEOUT_MS="20000", ODC_INJECT_LEAVE="1:1", MAX_RESTARTS="1", GPUS_PER_NODE="2",
+             MASTER_PORT=str(_free_port()))
+    cmd = ["bash", os.path.join(REPO, "launch.sh"), os.path.join(REPO, "examples/llm_training/train_fsdp2.py"),
+           "--cpu", "--model_name", "tiny", "--steps", "3", "--minibatch_size", "4", "--num-sequences", "32",
+           "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512",
+           "--run_name", "restart", "--checkpoint-dir", str(tmp_path / "ck"), "--checkpoint-every", "1"]
+    r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    lines = [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+    assert [l["step"] for l in lines if "event" not in l] == [0, 1, 2]
+    assert [l["event"] for l in lines if "event" in l] == ["leaving", "failure"]
+    assert (tmp_path / "restart.done").exists()
