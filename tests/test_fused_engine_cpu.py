@@ -243,3 +243,58 @@ def test_fused_engine_hybrid_sharding_matches_stock_hsdp():
     for r in (0, 3):   # a rank of each replica
         for k in a[r][1]:
             assert_mostly_close(b[r][1][k], a[r][1][k], rtol=5e-3, atol=2e-4)
+
+
+def _save_small(rank, world, folder):
+    import odc_b200 as odc
+    from odc_b200.models import get_config
+    from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
+    from odc_b200.utils.checkpoint import Checkpointer
+    odc.init_nvshmem("cpu", 256 << 20)
+    model = FusedDecoderLM(get_config("tiny"), device="cpu", seed=1)
+    opt = FusedOptimizer(model, lr=1e-3)
+    mb = _make_batches(rank, 0, 1)[0]
+    model.start_minibatch()
+    model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"],
+          loss_scale=mb["loss_scale"]).backward()
+    model.finish_minibatch()
+    opt.step()
+    Checkpointer(folder).save(model, opt, meta={"next_step": 1})
+    model.stop()
+    return True
+
+
+def _load_small(rank, world, folder):
+    import odc_b200 as odc
+    from odc_b200.models import get_config
+    from odc_b200.parallel import FusedDecoderLM, FusedOptimizer
+    from odc_b200.utils.checkpoint import MODEL_FILE, OPTIM_FILE, Checkpointer
+    odc.init_nvshmem("cpu", 256 << 20)
+    model = FusedDecoderLM(get_config("tiny"), device="cpu", seed=2)
+    opt = FusedOptimizer(model, lr=1e-3)
+    ck = Checkpointer(folder)
+    ck.load_model(model)
+    ck.load_optim(model, opt)
+    saved = torch.load(os.path.join(folder, ck.last_training_time, MODEL_FILE), weights_only=True)
+    saved_opt = torch.load(os.path.join(folder, ck.last_training_time, OPTIM_FILE), weights_only=True)
+    now, now_opt = model.full_state_dict(), opt.full_state_dict()
+    same = all(torch.equal(now[k], saved[k]) for k in saved) and ck.load_meta() == {"next_step": 1}
+    same_opt = all(torch.equal(now_opt["exp_avg"][k], saved_opt["exp_avg"][k]) for k in saved_opt["exp_avg"])
+    # and the resharded job trains on
+    mb = _make_batches(rank, 1, 1)[0]
+    model.start_minibatch()
+    loss = model(mb["input_ids"], mb["position_ids"], mb["cu_seqlens"], mb["max_seqlen"], labels=mb["labels"],
+                 loss_scale=mb["loss_scale"])
+    loss.backward()
+    model.finish_minibatch()
+    opt.step()
+    model.stop()
+    return same, same_opt, float(loss.detach())
+
+
+def test_checkpoint_written_on_two_ranks_resumes_on_three(tmp_path):
+    """Checkpoints hold whole tensors, so a job can come back with a different number of ranks (rows are re-split)."""
+    from _mp import run_ranks
+    assert all(run_ranks(_save_small, 2, str(tmp_path)))
+    for same, same_opt, loss in run_ranks(_load_small, 3, str(tmp_path)):
+        assert same and same_opt and loss == loss
