@@ -208,3 +208,25 @@ def test_fsdp1_patch_works_on_a_hugging_face_model():
     assert a[0][0] == pytest.approx(b[0][0], rel=1e-4), (a[0][0], b[0][0])
     for k in a[0][1]:
         assert_mostly_close(a[0][1][k], b[0][1][k], rtol=5e-3, atol=2e-4)
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_rescaled_rotary_frequencies_match_transformers(seed):
+    """``rope_inv_freq`` (llama3 and linear rules) against ``transformers``' own frequency initialisers."""
+    import random
+
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+
+    from odc_b200.ops.reference import rope_inv_freq
+    rnd = random.Random(seed)
+    head_dim = rnd.choice([32, 64, 128])
+    theta = rnd.choice([10000.0, 500000.0, 1000000.0])
+    for kind in ("llama3", "linear"):
+        params = {"rope_type": kind, "rope_theta": theta, "factor": rnd.choice([2.0, 8.0, 32.0])}
+        if kind == "llama3":
+            params.update(low_freq_factor=1.0, high_freq_factor=rnd.choice([2.0, 4.0]),
+                          original_max_position_embeddings=rnd.choice([64, 2048, 8192]))
+        conf = transformers.LlamaConfig(hidden_size=head_dim * 4, num_attention_heads=4, rope_parameters=dict(params))
+        want, _ = ROPE_INIT_FUNCTIONS[kind](conf, "cpu")
+        got = rope_inv_freq(head_dim, theta, params)
+        torch.testing.assert_close(got, want.float(), rtol=1e-6, atol=0)
