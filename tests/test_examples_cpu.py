@@ -178,3 +178,36 @@ def test_launcher_restarts_a_failed_job_which_resumes(tmp_path):
     assert events[1]["rank"] == 0 and events[1]["kind"] == "PeerFailure"      # reported on the host, no wait budget spent
     assert "exitcode  : 75" in r.stderr and "launch.sh: attempt 1 of 1" in r.stderr
     assert (tmp_path / "restart.done").exists()
+
+
+def test_hugging_face_model_trainer_agrees_with_the_converted_decoder(tmp_path):
+    """``train_hf.py`` (the reference's recipe: a ``transformers`` model class under ``fully_shard`` + the patch, the
+    chunked log-probability head) and ``train_fsdp2.py --hf-checkpoint`` (the same weights converted to this package's
+    decoder) see the same first-minibatch loss on the same packed data."""
+    pytest.importorskip("transformers")
+    import torch
+    sys.path.insert(0, REPO)
+    from odc_b200.models import DecoderLM, get_config
+    from odc_b200.models.hf import save_hf_checkpoint
+    cfg = get_config("tiny", qkv_bias=True, tie_embeddings=False, vocab_size=512)
+    src = DecoderLM(cfg)
+    src.reset_parameters(seed=3)
+    ckpt = tmp_path / "ckpt"
+    save_hf_checkpoint(str(ckpt), src.state_dict(), cfg, dtype=torch.float32)
+
+    def first_loss(script):
+        e = dict(os.environ, ODC="1", ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path), FUSED_OPTIMIZER="0")
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+               "127.0.0.1", "--master-port", str(_free_port()), os.path.join(REPO, "examples/llm_training", script), "--cpu",
+               "--hf-checkpoint", str(ckpt), "--steps", "2", "--minibatch_size", "4", "--num-sequences", "16",
+               "--length-dist", "uniform", "--limit_dataset_token_len", "200", "--max_token_len", "512",
+               "--run_name", "hf_ab"]
+        r = subprocess.run(cmd, env=e, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+        return [json.loads(x)["loss"] for x in r.stdout.splitlines() if x.startswith("{")]
+
+    hf_losses = first_loss("train_hf.py")
+    own_losses = first_loss("train_fsdp2.py")
+    # both compute in bf16 (fp32 master weights), in different operation orders
+    assert len(hf_losses) == 2 and hf_losses[0] == pytest.approx(own_losses[0], rel=5e-3)
+    assert hf_losses[1] == pytest.approx(own_losses[1], rel=2e-2)   # after one AdamW step of each
