@@ -10,7 +10,9 @@ Hugging Face's, the FSDP2 patch of this package replaces the all-gather / reduce
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \\
         examples/llm_training/train_hf.py --hf-checkpoint /path/to/Qwen2.5-1.5B --max_token_len 16384
 
-``ODC=0`` trains the same model with stock FSDP2 (lock-step microbatch counts: use ``DynamicSameMicro``).
+``ODC=0`` trains the same model with stock FSDP (lock-step microbatch counts: use ``DynamicSameMicro``);
+``FSDP1=1`` wraps with ``FullyShardedDataParallel`` flat parameters instead of ``fully_shard`` (the reference's
+examples/llm_training/torch_fsdp.py).
 On GPUs the attention implementation is ``flash_attention_2`` (the library the reference uses); ``--cpu`` uses eager
 attention with an explicit block-diagonal causal mask.
 """
@@ -27,10 +29,13 @@ from common import Timer, init_device, init_logging, log_metrics, log_packing, m
 import odc_b200 as odc
 from odc_b200 import ops
 from odc_b200.data import to_device
-from odc_b200.fsdp import fsdp2
+from odc_b200.fsdp import fsdp1, fsdp2
 from odc_b200.models.hf import config_from_hf
 
 ODC = os.environ.get("ODC", "1") == "1"
+FSDP1 = os.environ.get("FSDP1", "0") == "1"
+if ODC and FSDP1:
+    fsdp1.patch_fsdp1(reduce_dtype=torch.float32)   # before any FSDP(...) is constructed
 
 
 def block_causal_mask(cu_seqlens: torch.Tensor, T: int, dtype: torch.dtype) -> torch.Tensor:
@@ -68,7 +73,9 @@ def main():
     dev = init_device(args, rank)
     if ODC:
         odc.init_nvshmem(dev)
-        fsdp2.patch_fsdp2()
+        if not FSDP1:
+            fsdp2.patch_fsdp2()
+    engine = fsdp1 if FSDP1 else fsdp2
     flash = dev.type == "cuda"
     hf = transformers.AutoModelForCausalLM.from_pretrained(
         args.hf_checkpoint, attn_implementation="flash_attention_2" if flash else "eager",
@@ -77,13 +84,21 @@ def main():
         hf.gradient_checkpointing_enable()
     cfg = config_from_hf(hf.config)          # only for the dataset's vocabulary size and the cost model
     model = PackedCausalLM(hf, flash)
-    mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)   # as the reference's trainer
-    for layer in hf.model.layers:
-        fully_shard(layer, mp_policy=mp)
-    fully_shard(model, mp_policy=mp)
-    if ODC:
-        for m in list(hf.model.layers) + [model]:
-            fsdp2.patch_lazy_init(m)
+    if FSDP1:
+        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+        from torch.distributed.fsdp import MixedPrecision
+        from torch.distributed.fsdp.wrap import ModuleWrapPolicy
+        mp1 = MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32, buffer_dtype=torch.bfloat16)
+        model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({type(hf.model.layers[0])}), device_id=dev,
+                     use_orig_params=False, mixed_precision=mp1)
+    else:
+        mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)   # as the reference's trainer
+        for layer in hf.model.layers:
+            fully_shard(layer, mp_policy=mp)
+        fully_shard(model, mp_policy=mp)
+        if ODC:
+            for m in list(hf.model.layers) + [model]:
+                fsdp2.patch_lazy_init(m)
     opt = torch.optim.AdamW(model.parameters(), lr=args.lr, weight_decay=0.01)
     data = make_dataset(args, cfg, rank, world, ODC)
     init_logging(args, rank)
@@ -93,7 +108,7 @@ def main():
         log_packing(data, rank)
         with Timer("minibatch_time", times):
             if ODC:
-                fsdp2.pre_minibatch_start(model)
+                engine.pre_minibatch_start(model)
             total = torch.zeros((), device=dev)
             tokens = 0
             for mb in microbatches:
@@ -107,9 +122,9 @@ def main():
             if not args.forward_only:
                 with Timer("sync_time", times):
                     if ODC:
-                        fsdp2.pre_optimizer_step(model)
+                        engine.pre_optimizer_step(model)
                 with Timer("optimizer_step_time", times):
-                    grad_norm = torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+                    grad_norm = model.clip_grad_norm_(1.0) if FSDP1 else torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
                     opt.step()
                     opt.zero_grad()
         dist.all_reduce(total)
@@ -120,7 +135,7 @@ def main():
                                  "grad_norm": float(grad_norm) if not args.forward_only else 0.0, **times, **memory_metrics()})
     mark_done(args)
     if ODC:
-        fsdp2.stop()
+        engine.stop()
     dist.destroy_process_group()
 
 

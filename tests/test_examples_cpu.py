@@ -195,8 +195,8 @@ def test_hugging_face_model_trainer_agrees_with_the_converted_decoder(tmp_path):
     ckpt = tmp_path / "ckpt"
     save_hf_checkpoint(str(ckpt), src.state_dict(), cfg, dtype=torch.float32)
 
-    def first_loss(script):
-        e = dict(os.environ, ODC="1", ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path), FUSED_OPTIMIZER="0")
+    def first_loss(script, **env):
+        e = dict(os.environ, ODC="1", ODC_SYMMETRIC_SIZE="256M", ODC_OUT_DIR=str(tmp_path), FUSED_OPTIMIZER="0", **env)
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
                "127.0.0.1", "--master-port", str(_free_port()), os.path.join(REPO, "examples/llm_training", script), "--cpu",
                "--hf-checkpoint", str(ckpt), "--steps", "2", "--minibatch_size", "4", "--num-sequences", "16",
@@ -211,3 +211,5 @@ def test_hugging_face_model_trainer_agrees_with_the_converted_decoder(tmp_path):
     # both compute in bf16 (fp32 master weights), in different operation orders
     assert len(hf_losses) == 2 and hf_losses[0] == pytest.approx(own_losses[0], rel=5e-3)
     assert hf_losses[1] == pytest.approx(own_losses[1], rel=2e-2)   # after one AdamW step of each
+    flat_losses = first_loss("train_hf.py", FSDP1="1")                 # the same model under FSDP1 flat parameters
+    assert flat_losses[0] == pytest.approx(hf_losses[0], rel=5e-3) and flat_losses[1] == pytest.approx(hf_losses[1], rel=2e-2)
